@@ -1,0 +1,290 @@
+"""Benchmark of the tmq_b200 hot paths on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--n ELEMS]
+
+Headline workload (N=1): the standalone soft-staircase pass of the baseline configuration "Standalone soft-staircase
+transfer, fp32, 64M elements": one step = ONE fused kernel doing forward + backward + quantization-loss
+reduction + clamp over a 2^26-element weight tensor (w uniform in [-1.5,1.5), upstream grad N(0,1), hardness
+cycling through {0.1, 0.5, 0.9, 1.0}).  Algorithmic traffic 20 B/element (read w, g; write y, grad, clamped w).
+
+Prints one JSON line (rank 0).  `value` is device-resident throughput; `e2e` is the same pass through the public
+operator call with pinned HOST buffers (H2D of w and g, D2H of the three outputs and the loss, every step).
+With --gpus N every rank processes its own 2^26-element shard (weak scaling) and the loss scalar is all-reduced
+over NCCL inside the step.  `--impl reference` times the reference's CPU path (PyTorch CPU eager op sequence,
+restated in oracle/softstep_torch.py) on the host cores, on a bounded sample.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HARDNESS = [0.1, 0.5, 0.9, 1.0]
+SHARPNESS, STRENGTH, LO, HI = 5.0, 5e-4, -1.0, 1.0
+BYTES_PER_ELEM = 20
+METRIC = "softstep_fwd_bwd_loss_clamp_GBps"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return dist, rank, local, world
+    return None, 0, 0, 1
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+
+def cpu_softstep_baseline(sample_elems, reps):
+    """Reference CPU path (PyTorch eager op sequence) on all host threads; returns GB/s at 20 B/elem."""
+    from oracle import softstep_torch as OT
+    gen = torch.Generator().manual_seed(0)
+    w = torch.rand(sample_elems, generator=gen) * 3 - 1.5
+    g = torch.randn(sample_elems, generator=gen)
+    OT.qat_element_pass(w, g, HARDNESS[0], SHARPNESS, STRENGTH, LO, HI)       # warm
+    t0 = time.perf_counter()
+    for i in range(reps):
+        OT.qat_element_pass(w, g, HARDNESS[i % 4], SHARPNESS, STRENGTH, LO, HI)
+    dt = (time.perf_counter() - t0) / reps
+    return sample_elems * BYTES_PER_ELEM / dt / 1e9, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 1 << 24
+    cores = torch.get_num_threads()
+    for i in range(args.warmup):
+        cpu_softstep_baseline(sample, 1)
+    gbs, dt = cpu_softstep_baseline(sample, args.steps)
+    n_full = args.n
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3 * (n_full / sample), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "softstep_fused_2^26_f32", "elements": n_full, "hardness": HARDNESS,
+                   "bytes_per_element": BYTES_PER_ELEM},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"2^24 of 2^26 elements per step; PyTorch CPU eager op sequence of the reference "
+                                   f"(forward, loss mean, both backwards, clamp); ms_per_step scaled x4"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+
+def run_ours(args):
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the tmq_b200 kernels have no CPU fallback")
+    dist, rank, local, world = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    from tmq_b200 import ops
+
+    n = args.n
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    w = torch.rand(n, generator=gen, device=dev) * 3 - 1.5
+    g = torch.randn(n, generator=gen, device=dev)
+    out = (torch.empty_like(w), torch.empty_like(w), torch.empty_like(w),
+           torch.empty((), dtype=torch.float64, device=dev))
+    gq = 1.0 / n
+
+    def step(i):
+        res = ops.fused_step(w, g, HARDNESS[i % 4], SHARPNESS, STRENGTH, LO, HI, gq=gq, out=out)
+        if dist is not None:
+            dist.all_reduce(res[3])
+        return res
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = world * n * BYTES_PER_ELEM / (ms_per_step * 1e-3) / 1e9
+
+    # kernel-only duration for the roofline (no collective in between), same launches, same stream
+    barrier()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for i in range(args.steps):
+        ops.fused_step(w, g, HARDNESS[i % 4], SHARPNESS, STRENGTH, LO, HI, gq=gq, out=out)
+    k1.record()
+    torch.cuda.synchronize()
+    kernel_ms = k0.elapsed_time(k1) / args.steps
+
+    # end to end: pinned host buffers in, results out, every step
+    hw, hg = w.cpu().pin_memory(), g.cpu().pin_memory()
+    hy, hgw, hwc = (torch.empty(n, dtype=torch.float32).pin_memory() for _ in range(3))
+    hloss = torch.empty((), dtype=torch.float64).pin_memory()
+    dw, dg = torch.empty_like(w), torch.empty_like(g)
+
+    def e2e_step(i):
+        dw.copy_(hw, non_blocking=True)
+        dg.copy_(hg, non_blocking=True)
+        y, gw, wc, loss = ops.fused_step(dw, dg, HARDNESS[i % 4], SHARPNESS, STRENGTH, LO, HI, gq=gq, out=out)
+        if dist is not None:
+            dist.all_reduce(loss)
+        hy.copy_(y, non_blocking=True)
+        hgw.copy_(gw, non_blocking=True)
+        hwc.copy_(wc, non_blocking=True)
+        hloss.copy_(loss, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 10)) if not args.no_e2e else 0
+    for i in range(2 if e2e_steps else 0):
+        e2e_step(i)
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    s1.record()
+    barrier()
+    t = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / max(e2e_steps, 1)
+    e2e_value = world * n * BYTES_PER_ELEM / (e2e_ms * 1e-3) / 1e9 if e2e_steps else None
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    achieved = n * BYTES_PER_ELEM / (kernel_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "softstep_fused_2^26_f32", "elements_per_gpu": n, "hardness": HARDNESS,
+                   "sharpness": SHARPNESS, "strength": STRENGTH, "bytes_per_element": BYTES_PER_ELEM,
+                   "l2": "inputs (w, g: 2 x 256 MiB) exceed the 126 MB L2; no flush needed",
+                   "sharding": "one shard per GPU, fp64 loss scalar all-reduced (NCCL)" if world > 1 else "single GPU"},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 2 * n * 4, "d2h_bytes_per_step": 3 * n * 4 + 8,
+                "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "softstep_kernel<FWD|BWD|QSUM|QGRAD|CLAMP>", "kernel_ms": kernel_ms,
+                     "algorithmic_bytes": n * BYTES_PER_ELEM},
+    }
+    if world == 1 and not args.no_cpu:
+        gbs, dt = cpu_softstep_baseline(1 << 24, 3)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": "3 passes over 2^24 of the 2^26 elements; PyTorch CPU eager op sequence of "
+                                          "the reference (tmq/tmq.py:417-493, :696-699)"}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--n", type=int, default=1 << 26, help="elements per GPU (default: the baseline's 2^26)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

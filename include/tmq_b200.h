@@ -1,0 +1,121 @@
+/* tmq_b200 -- C ABI of the B200 (sm_100a) kernels behind TMQ's two data-parallel hot paths.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*, a cudaStream_t),
+ * returns an int status (0 = TMQ_OK, negative = error), never allocates device memory, never synchronises
+ * and never throws.  Work is enqueued on the given stream; outputs are valid once that stream reaches them.
+ *
+ * "replaces:" names the reference interface an entry point stands in for, as file:line of the reference
+ * project (mtnwrw/tmq).
+ */
+#ifndef TMQ_B200_H
+#define TMQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TMQ_OK 0
+#define TMQ_ERR_ARG (-1)         /* null pointer, bad size, unsupported combination              */
+#define TMQ_ERR_ALIGN (-2)       /* a pointer misses the alignment the entry point documents      */
+#define TMQ_ERR_LAUNCH (-3)      /* the CUDA runtime refused the launch (see tmq_last_cuda_error) */
+#define TMQ_ERR_TIMEOUT (-4)     /* a bounded device-side wait ran out                            */
+#define TMQ_ERR_SCRATCH (-5)     /* scratch buffer too small                                      */
+#define TMQ_ERR_UNSUPPORTED (-6) /* shape outside what the kernel family covers                   */
+
+const char *tmq_status_string(int status);
+int tmq_last_cuda_error(void);  /* cudaError_t of the most recent failed runtime call on this thread, 0 if none */
+int tmq_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Hot path 1: soft-staircase transfer function, fp32, flat contiguous tensors of n elements.
+ * Arithmetic follows the reference's PyTorch-CPU-eager formulas operation by operation (one IEEE
+ * rounding each, no FMA contraction); the host scalars d, d/2 and 2*sigma(d/2) are derived from the
+ * double `digamma` exactly as Python derives them.  Pointers need 4-byte alignment; 16-byte aligned
+ * pointers take the 128-bit vector path.
+ * ------------------------------------------------------------------------------------------------ */
+
+/* y = softstep(w; digamma).  replaces: fwd_softstep, tmq/tmq_cuda.cu:740-764 (kernel :80-92), tmq/tmq.py:404-419 */
+int tmq_softstep_fwd(const float *w, float *y, size_t n, double digamma, void *stream);
+
+/* gw = scale * g * softstep'(w).  replaces: bwd_softstep, tmq/tmq_cuda.cu:768-794 (kernel :95-110), tmq/tmq.py:422-438 */
+int tmq_softstep_bwd(const float *w, const float *g, float *gw, size_t n, double digamma, double scale, void *stream);
+
+/* o = strength * softstep'(w; digamma)  (the quantization-loss integrand).
+ * replaces: fwd_softstep_derivative, tmq/tmq_cuda.cu:690-709 (kernel :45-59), tmq/tmq.py:456-473 */
+int tmq_softstep_deriv_fwd(const float *w, float *o, size_t n, double digamma, double strength, void *stream);
+
+/* gw = g * strength * softstep''(w; digamma).
+ * replaces: bwd_softstep_derivative, tmq/tmq_cuda.cu:713-735 (kernel :63-77), tmq/tmq.py:475-493 */
+int tmq_softstep_deriv_bwd(const float *w, const float *g, float *gw, size_t n, double digamma, double strength,
+                           void *stream);
+
+/* out = min(max(w, lo), hi); out may alias w.  replaces: torch.clamp in Linear.clamp / Conv2d.clamp, tmq/tmq.py:691-696, :874-879 */
+int tmq_clamp(const float *w, float *out, size_t n, float lo, float hi, void *stream);
+
+/* Scratch for the deterministic two-stage reductions below: tmq_reduce_scratch_bytes() bytes of device memory,
+ * 256-byte aligned, zero-filled ONCE before first use (the kernels leave it zeroed again).  Calls that share
+ * one scratch buffer must be ordered on one stream. */
+size_t tmq_reduce_scratch_bytes(void);
+
+/* *sum_out (device, fp64) = sum_i strength * softstep'(w_i; sharpness), without materialising the integrand.
+ * replaces: torch.mean(SoftStepDerivative.apply(...)) numerator, tmq/tmq.py:698-699, :889-891 */
+int tmq_qloss_sum(const float *w, size_t n, double sharpness, double strength, double *sum_out, void *scratch,
+                  size_t scratch_bytes, void *stream);
+
+/* One pass over a weight tensor doing everything the QAT step does to it elementwise:
+ *   y   = softstep(w; digamma)                                         (forward,            tmq/tmq.py:417-419)
+ *   gw  = scale*g*softstep'(w; digamma) + gq*strength*softstep''(w; sharpness)
+ *                                                                      (both backward terms, tmq/tmq.py:434-438, :488-493)
+ *   *loss_sum = sum_i strength*softstep'(w_i; sharpness)               (loss numerator,     tmq/tmq.py:469-473, :698-699)
+ *   wc  = clamp(w, lo, hi)                                             (tmq/tmq.py:696)
+ * gq is the upstream gradient of the mean (1/n for a plain sum of layer losses).  Reads 8 and writes 12 bytes per element. */
+int tmq_softstep_fused_step(const float *w, const float *g, float *y, float *gw, float *wc, double *loss_sum, size_t n,
+                            double digamma, double scale, double sharpness, double strength, float gq, float lo,
+                            float hi, void *scratch, size_t scratch_bytes, void *stream);
+
+/* Multi-tensor forms: one launch over every registered layer (tmq/tmq.py:263-272, :298-310 loop over layers).
+ * A plan is a host-built table the caller uploads once to device memory (8-byte aligned) and reuses. */
+typedef struct {
+    const float *w; /* weights (device)                                         */
+    float *out;     /* per-tensor output (gradient for qloss_bwd, unused else)  */
+    uint64_t n;     /* elements                                                 */
+} tmq_mt_tensor;
+
+size_t tmq_mt_plan_bytes(const tmq_mt_tensor *tensors, int ntensors);
+/* Fills host_plan (tmq_mt_plan_bytes bytes); *nchunks receives the launch extent to pass back below. */
+int tmq_mt_plan_build(const tmq_mt_tensor *tensors, int ntensors, void *host_plan, size_t plan_bytes, int *nchunks);
+/* *loss_out (device fp64) = sum_l mean_i(strength*softstep'(w_li; sharpness)) */
+int tmq_mt_qloss(const void *d_plan, int ntensors, int nchunks, double sharpness, double strength, double *loss_out,
+                 void *scratch, size_t scratch_bytes, void *stream);
+/* out_l = (upstream / n_l) * strength * softstep''(w_l; sharpness); d_upstream: device fp32 scalar or NULL (= 1) */
+int tmq_mt_qloss_bwd(const void *d_plan, int ntensors, int nchunks, double sharpness, double strength,
+                     const float *d_upstream, void *stream);
+/* w_l = clamp(w_l, lo, hi) in place */
+int tmq_mt_clamp(const void *d_plan, int ntensors, int nchunks, float lo, float hi, void *stream);
+
+/* Device self-check of the constant-divisor fast path used inside the kernels above: counts, over every finite
+ * fp32 numerator with |a| in [2^-60, 2^60], results that differ from IEEE division by 2*sigma(digamma/2).
+ * *mismatches is a device uint64 the caller zeroes first. */
+int tmq_selftest_const_div(double digamma, unsigned long long *mismatches, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Hot path 2a: bit-exact 2-bit packing.  W is [N][K] row-major (Linear [out][in]; a conv kernel
+ * [O][I][ky][kx] is the same thing with K = I*ky*kx).  P is [K][ceil(N/16)] 32-bit words, element i of a
+ * word in bits [31-2i : 30-2i], codes 0 -> 00, +1 -> 01, -1 -> 10, tail elements zero.
+ * ------------------------------------------------------------------------------------------------ */
+
+/* replaces: compactify_ternary, tmq/tmq_native.cpp:418-425 (matrix :303-319/:152-171, conv kernel :279-294/:185-208) */
+int tmq_pack2b_f32(const float *W, uint32_t *P, int64_t N, int64_t K, void *stream);
+int tmq_pack2b_i32(const int32_t *W, uint32_t *P, int64_t N, int64_t K, void *stream);
+int tmq_pack2b_i8(const int8_t *W, uint32_t *P, int64_t N, int64_t K, void *stream);
+/* replaces: expand_ternary, tmq/tmq_native.cpp:516-544 (:249-266; the 2-D routine :220-234 drops the transpose,
+ * this is the true inverse for both ranks) */
+int tmq_unpack2b_f32(const uint32_t *P, float *W, int64_t N, int64_t K, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TMQ_B200_H */

@@ -1,0 +1,256 @@
+"""Operator layer: the functions TMQ's layers call, with the reference's names and argument meaning, backed by the
+C ABI of libtmq_b200.so.
+
+Mirrors the pybind surface of the reference (`tmq_cuda`, tmq/tmq_cuda.cu:800-809, and `tmq_native`,
+tmq/tmq_native.cpp:550-555): inputs are borrowed, outputs are freshly allocated on the input's device, wrong
+devices / dtypes raise RuntimeError, the unimplemented half-precision paths raise ValueError.  Unlike the reference
+the calls run on the current stream of the tensor's device and check contiguity.  This module only moves
+pointers; every computation happens in the CUDA library, and nothing here works without it.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+_scratch = {}
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _require_cuda_f32(t, name):
+    if not isinstance(t, torch.Tensor) or t.device.type != "cuda":
+        raise RuntimeError(f"{name}: expected a CUDA tensor")
+    if t.dtype == torch.float16:
+        raise ValueError("Not implemented yet")
+    if t.dtype != torch.float32:
+        raise ValueError("Expected either a float16 or a float32 tensor as input/output")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def reduce_scratch(device):
+    """Per-device scratch of the two-stage reductions (zeroed once; the kernels leave it zeroed)."""
+    device = torch.device(device)
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    buf = _scratch.get(key)
+    if buf is None:
+        buf = torch.zeros(lib().tmq_reduce_scratch_bytes(), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+# ------------------------------------------------------------------------------------------------ soft-step
+
+def fwd_softstep(weights, digamma):
+    w = _require_cuda_f32(weights, "fwd_softstep")
+    out = torch.empty_like(w)
+    with torch.cuda.device(w.device):
+        check(lib().tmq_softstep_fwd(_ptr(w), _ptr(out), w.numel(), float(digamma), _stream(w)), "fwd_softstep")
+    return out
+
+
+def bwd_softstep(weights, digamma, scale, grad):
+    w = _require_cuda_f32(weights, "bwd_softstep")
+    g = _require_cuda_f32(grad, "bwd_softstep")
+    if g.shape != w.shape:
+        g = g.expand_as(w).contiguous()
+    out = torch.empty_like(w)
+    with torch.cuda.device(w.device):
+        check(lib().tmq_softstep_bwd(_ptr(w), _ptr(g), _ptr(out), w.numel(), float(digamma), float(scale), _stream(w)),
+              "bwd_softstep")
+    return out
+
+
+def fwd_softstep_derivative(weights, digamma, strength):
+    w = _require_cuda_f32(weights, "fwd_softstep_derivative")
+    out = torch.empty_like(w)
+    with torch.cuda.device(w.device):
+        check(lib().tmq_softstep_deriv_fwd(_ptr(w), _ptr(out), w.numel(), float(digamma), float(strength), _stream(w)),
+              "fwd_softstep_derivative")
+    return out
+
+
+def bwd_softstep_derivative(weights, digamma, strength, grad):
+    w = _require_cuda_f32(weights, "bwd_softstep_derivative")
+    g = _require_cuda_f32(grad, "bwd_softstep_derivative")
+    if g.shape != w.shape or not g.is_contiguous():
+        g = g.expand_as(w).contiguous()
+    out = torch.empty_like(w)
+    with torch.cuda.device(w.device):
+        check(lib().tmq_softstep_deriv_bwd(_ptr(w), _ptr(g), _ptr(out), w.numel(), float(digamma), float(strength),
+                                           _stream(w)), "bwd_softstep_derivative")
+    return out
+
+
+def clamp(weights, lo, hi, out=None):
+    w = _require_cuda_f32(weights, "clamp")
+    out = torch.empty_like(w) if out is None else out
+    with torch.cuda.device(w.device):
+        check(lib().tmq_clamp(_ptr(w), _ptr(out), w.numel(), float(lo), float(hi), _stream(w)), "clamp")
+    return out
+
+
+def qloss_sum(weights, sharpness, strength):
+    """fp64 0-d tensor: sum of the loss integrand over the tensor, never materialised."""
+    w = _require_cuda_f32(weights, "qloss_sum")
+    out = torch.empty((), dtype=torch.float64, device=w.device)
+    scratch = reduce_scratch(w.device)
+    with torch.cuda.device(w.device):
+        check(lib().tmq_qloss_sum(_ptr(w), w.numel(), float(sharpness), float(strength), _ptr(out), _ptr(scratch),
+                                  scratch.numel(), _stream(w)), "qloss_sum")
+    return out
+
+
+def fused_step(weights, grad, digamma, sharpness, strength, lo, hi, scale=1.0, gq=None, out=None):
+    """One pass: (softstep(w), total gradient wrt w, clamp(w), fp64 loss sum).  `out` may carry preallocated
+    (y, gw, wc, loss) buffers."""
+    w = _require_cuda_f32(weights, "fused_step")
+    g = _require_cuda_f32(grad, "fused_step")
+    n = w.numel()
+    if out is None:
+        out = (torch.empty_like(w), torch.empty_like(w), torch.empty_like(w),
+               torch.empty((), dtype=torch.float64, device=w.device))
+    y, gw, wc, loss = out
+    if gq is None:
+        gq = float(torch.tensor(1.0, dtype=torch.float32) / torch.tensor(float(n), dtype=torch.float32))
+    scratch = reduce_scratch(w.device)
+    with torch.cuda.device(w.device):
+        check(lib().tmq_softstep_fused_step(_ptr(w), _ptr(g), _ptr(y), _ptr(gw), _ptr(wc), _ptr(loss), n, float(digamma),
+                                            float(scale), float(sharpness), float(strength), float(gq), float(lo),
+                                            float(hi), _ptr(scratch), scratch.numel(), _stream(w)), "fused_step")
+    return y, gw, wc, loss
+
+
+def selftest_const_div(digamma, device="cuda"):
+    cnt = torch.zeros((), dtype=torch.int64, device=device)
+    with torch.cuda.device(cnt.device):
+        check(lib().tmq_selftest_const_div(float(digamma), _ptr(cnt), _stream(cnt)), "selftest_const_div")
+    return int(cnt.item())
+
+
+# ------------------------------------------------------------------------------------------------ multi-tensor
+
+class MultiTensorPlan:
+    """Device-resident table over a fixed list of weight tensors (one per registered layer) so that loss, its
+    gradient and the clamp run as ONE launch each instead of one per layer."""
+
+    def __init__(self, weights, with_grad_out=False):
+        assert len(weights) > 0
+        self.device = weights[0].device
+        for w in weights:
+            if w.device != self.device or w.dtype != torch.float32 or not w.is_contiguous():
+                raise RuntimeError("MultiTensorPlan: weights must be contiguous fp32 tensors on one CUDA device")
+        self.weights = list(weights)
+        self.ptrs = [w.data_ptr() for w in weights]
+        self.grads = None
+        if with_grad_out:
+            # one flat buffer, each tensor's slice 16-byte aligned
+            offs, total = [], 0
+            for w in weights:
+                offs.append(total)
+                total += (w.numel() + 3) // 4 * 4
+            flat = torch.empty(total, dtype=torch.float32, device=self.device)
+            self.grads = [flat[o:o + w.numel()].view(w.shape) for o, w in zip(offs, weights)]
+        n = len(weights)
+        arr = (_lib.MtTensor * n)()
+        for i, w in enumerate(weights):
+            arr[i].w = w.data_ptr()
+            arr[i].out = self.grads[i].data_ptr() if self.grads is not None else None
+            arr[i].n = w.numel()
+        nbytes = lib().tmq_mt_plan_bytes(arr, n)
+        host = torch.empty(nbytes, dtype=torch.uint8)
+        nchunks = ctypes.c_int(0)
+        check(lib().tmq_mt_plan_build(arr, n, ctypes.c_void_p(host.data_ptr()), nbytes, ctypes.byref(nchunks)),
+              "mt_plan_build")
+        self.ntensors, self.nchunks = n, nchunks.value
+        self.table = host.to(self.device)
+
+    def matches(self, weights):
+        return len(weights) == len(self.ptrs) and all(w.data_ptr() == p for w, p in zip(weights, self.ptrs))
+
+    def qloss(self, sharpness, strength):
+        out = torch.empty((), dtype=torch.float64, device=self.device)
+        scratch = reduce_scratch(self.device)
+        with torch.cuda.device(self.device):
+            check(lib().tmq_mt_qloss(_ptr(self.table), self.ntensors, self.nchunks, float(sharpness), float(strength),
+                                     _ptr(out), _ptr(scratch), scratch.numel(), _stream(out)), "mt_qloss")
+        return out
+
+    def qloss_bwd(self, sharpness, strength, upstream=None):
+        assert self.grads is not None
+        up = None
+        if upstream is not None:
+            up = upstream.to(device=self.device, dtype=torch.float32).reshape(()).contiguous()
+        with torch.cuda.device(self.device):
+            check(lib().tmq_mt_qloss_bwd(_ptr(self.table), self.ntensors, self.nchunks, float(sharpness),
+                                         float(strength), _ptr(up) if up is not None else None,
+                                         _stream(self.table)), "mt_qloss_bwd")
+        return self.grads
+
+    def clamp_(self, lo, hi):
+        with torch.cuda.device(self.device):
+            check(lib().tmq_mt_clamp(_ptr(self.table), self.ntensors, self.nchunks, float(lo), float(hi),
+                                     _stream(self.table)), "mt_clamp")
+
+
+# ------------------------------------------------------------------------------------------------ packing
+
+def _work_device(t):
+    """Packing runs on the GPU; host tensors make a round trip through the current device."""
+    if t.device.type == "cuda":
+        return t.device
+    if not torch.cuda.is_available():
+        raise _lib.TmqError("tmq_b200 needs a CUDA device: packing runs in the CUDA library and there is no CPU path")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def compactify_ternary(tensor):
+    """[N,K] or [O,I,ky,kx] float32|int32|int8 -> int32 packed [K, ceil(N/16)] or [I,ky,kx,ceil(O/16)] on the
+    input's device (tmq/tmq_native.cpp:418-425)."""
+    if tensor.dim() not in (2, 4):
+        raise RuntimeError("compactify_ternary: expected a 2-D or 4-D tensor")
+    fn = {torch.float32: "tmq_pack2b_f32", torch.int32: "tmq_pack2b_i32", torch.int8: "tmq_pack2b_i8"}.get(tensor.dtype)
+    if fn is None:
+        raise ValueError("Cannot handle the supplied data-type")
+    dev = _work_device(tensor)
+    w = tensor.detach().to(dev).contiguous()
+    N = w.shape[0]
+    K = w.numel() // N if N else 0
+    Q = (N + 15) // 16
+    out_shape = (K, Q) if w.dim() == 2 else (w.shape[1], w.shape[2], w.shape[3], Q)
+    out = torch.empty(out_shape, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        check(getattr(lib(), fn)(_ptr(w), _ptr(out), N, K, _stream(w)), "compactify_ternary")
+    return out.to(tensor.device)
+
+
+def expand_ternary(packed, orig_shape, entropy_decode=False):
+    """Packed int32 -> float32 {-1,0,+1} tensor of `orig_shape` (tmq/tmq_native.cpp:516-544; 2-D uses the true
+    inverse of the packer, which the reference's 2-D routine is not)."""
+    if entropy_decode:
+        from .codec import decompress_ternary
+        packed = decompress_ternary(packed, orig_shape)
+    if packed.dtype != torch.int32:
+        raise RuntimeError("expand_ternary: expected an int32 tensor")
+    orig_shape = [int(s) for s in orig_shape]
+    if len(orig_shape) not in (2, 4):
+        raise ValueError("Shape needs to be of dim 2 or 4")
+    N = orig_shape[0]
+    K = 1
+    for s in orig_shape[1:]:
+        K *= s
+    if packed.numel() != K * ((N + 15) // 16):
+        raise RuntimeError("expand_ternary: packed tensor does not match the original shape")
+    dev = _work_device(packed)
+    p = packed.detach().to(dev).contiguous()
+    out = torch.empty(orig_shape, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib().tmq_unpack2b_f32(_ptr(p), _ptr(out), N, K, _stream(p)), "expand_ternary")
+    return out.to(packed.device)
