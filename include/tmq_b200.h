@@ -65,6 +65,17 @@ size_t tmq_reduce_scratch_bytes(void);
 int tmq_qloss_sum(const float *w, size_t n, double sharpness, double strength, double *sum_out, void *scratch,
                   size_t scratch_bytes, void *stream);
 
+/* Same result as tmq_qloss_sum for callers that cannot hand over a scratch buffer because they cannot allocate
+ * device memory at all (hosts whose device memory was partitioned once at start-up, plug-ins inside a framework
+ * that owns the whole pool, paths where cudaMalloc is off limits because it may stall the device).  The scratch is
+ * a fixed 33 KB array inside the library image, resident on every GPU that loads the library.  No counterpart in
+ * the reference.  Limits: n <= TMQ_QLOSS_NOALLOC_MAX_ELEMS, else TMQ_ERR_SCRATCH and nothing runs.  All calls on a
+ * GPU share that one array (each call re-zeroes what must start at zero), so calls whose kernels could overlap on
+ * the GPU race with each other: keep them ordered.  The first call on each device also resolves the array's device
+ * address; issue that first call before any stream capture begins. */
+#define TMQ_QLOSS_NOALLOC_MAX_ELEMS 33554432ull
+int tmq_qloss_sum_noalloc(const float *w, size_t n, double sharpness, double strength, double *sum_out, void *stream);
+
 /* One pass over a weight tensor doing everything the QAT step does to it elementwise:
  *   y   = softstep(w; digamma)                                         (forward,            tmq/tmq.py:417-419)
  *   gw  = scale*g*softstep'(w; digamma) + gq*strength*softstep''(w; sharpness)

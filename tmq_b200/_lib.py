@@ -30,6 +30,7 @@ _SIGNATURES = {
     "tmq_clamp": (c_int, [c_void_p, c_void_p, c_size_t, c_float, c_float, c_void_p]),
     "tmq_reduce_scratch_bytes": (c_size_t, []),
     "tmq_qloss_sum": (c_int, [c_void_p, c_size_t, c_double, c_double, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "tmq_qloss_sum_noalloc": (c_int, [c_void_p, c_size_t, c_double, c_double, c_void_p, c_void_p]),
     "tmq_softstep_fused_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_double,
                                         c_double, c_double, c_double, c_float, c_float, c_float, c_void_p, c_size_t,
                                         c_void_p]),
