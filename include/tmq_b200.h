@@ -126,6 +126,30 @@ int tmq_pack2b_i8(const int8_t *W, uint32_t *P, int64_t N, int64_t K, void *stre
  * this is the true inverse for both ranks) */
 int tmq_unpack2b_f32(const uint32_t *P, float *W, int64_t N, int64_t K, void *stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Hot path 2b: ternary GEMM / GEMV from packed weights, tensor-core path (tcgen05 + TMEM + TMA).
+ *   Y[m][n] = scale[n] * sum_k X[m][k] * T[n][k] + bias[n],   T[n][k] in {-1, 0, +1}
+ * replaces: ternary_mmm_cuda / ternary_mvm_cuda, tmq/tmq_cuda.cu:478-549 (kernel :289-427), :563-603 (kernel
+ * :242-286); callers tmq/tmq.py:662-688 (Linear.compact_forward), :822-871 (Conv2d.compact_forward, after im2col).
+ * The reference multiplies fp32 activations on CUDA cores and applies post_scale / bias in Python; here scale and
+ * bias are per output channel and fused (pass NULL for none).
+ *
+ * Weights are consumed in a PREPACKED layout derived once from the reference layout P[K][ceil(N/16)]:
+ * Wt[N][Kp/16] words, Kp = K rounded up to 64, 16 consecutive k of one output channel per word, bit order per
+ * activation type (fmt 0: bf16 activations, fmt 1: int8 activations).  tmq_prepack_words gives the word count.
+ * ------------------------------------------------------------------------------------------------ */
+size_t tmq_prepack_words(int64_t N, int64_t K);
+int tmq_prepack(const uint32_t *P, uint32_t *Wt, int64_t N, int64_t K, int fmt, void *stream);
+
+/* X: bf16 [M][K] row-major, K % 8 == 0, 16-byte aligned.  Y: bf16 (out_f32 = 0) or fp32 (out_f32 = 1) [M][ldy].
+ * fp32 accumulation.  *status (device int, zeroed by the caller) receives TMQ_ERR_TIMEOUT if a bounded device-side
+ * wait ran out; the kernel then skips its work instead of hanging. */
+int tmq_ternary_gemm_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int64_t M,
+                          int64_t N, int64_t K, int64_t ldy, int out_f32, int *status, void *stream);
+/* X: int8 [M][K], K % 16 == 0.  Y: int32 [M][ldy], exact. */
+int tmq_ternary_gemm_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
+                        int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,101 @@
+"""Tensor-core ternary GEMM (tcgen05) against the oracle: int8 activations bit-exact; bf16 activations within
+rel 1e-3 of the fp64 result before output rounding (fp32 output), and within one bf16 ulp after it (bf16 output)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ternary as T
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tmq_b200 import ops
+    return ops
+
+
+def make_weights(N, K, seed, p=(0.3, 0.4, 0.3)):
+    rng = np.random.default_rng(seed)
+    u = rng.random((N, K))
+    W = np.where(u < p[0], -1.0, np.where(u < p[0] + p[1], 0.0, 1.0)).astype(np.float32)
+    return W, T.pack(W)
+
+
+SHAPES = [(1, 128, 64), (8, 128, 64), (32, 256, 128), (33, 200, 192), (64, 128, 256), (100, 130, 72), (128, 384, 512),
+          (129, 128, 64), (256, 256, 1024), (300, 520, 576), (512, 1000, 2304)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_i8_exact(ops, M, N, K):
+    K = (K + 15) // 16 * 16
+    W, P = make_weights(N, K, M * 7 + N)
+    rng = np.random.default_rng(K)
+    X = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_I8)
+    Y = ops.ternary_gemm_i8(torch.from_numpy(X).cuda(), wt, N)
+    ops.check_gemm_status()
+    assert np.array_equal(Y.cpu().numpy(), T.gemm_i8_fast(X, P, N))
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_bf16_tolerance(ops, M, N, K):
+    K = (K + 7) // 8 * 8
+    W, P = make_weights(N, K, M * 11 + N)
+    gen = torch.Generator().manual_seed(K)
+    X = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    scale = (torch.rand(N, generator=gen) * 0.09 + 0.01)
+    bias = torch.randn(N, generator=gen)
+    wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16)
+    ref_acc = T.gemm_f64_fast(X.float().numpy(), P, N)                       # exact sum of exact products
+    ref = ref_acc * scale.double().numpy()[None, :] + bias.double().numpy()[None, :]
+    y32 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.float32)
+    ops.check_gemm_status()
+    got = y32.cpu().double().numpy()
+    rms = np.sqrt((ref ** 2).mean(axis=1, keepdims=True))
+    assert np.all(np.abs(got - ref) <= 1e-3 * np.maximum(np.abs(ref), rms)), np.abs(got - ref).max()
+    # in practice fp32 accumulation of exact products is far tighter than the 1e-3 bar
+    assert np.all(np.abs(got - ref) <= 1e-5 * np.maximum(np.abs(ref), rms))
+    y16 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.bfloat16)
+    ops.check_gemm_status()
+    want16 = torch.from_numpy(ref).to(torch.bfloat16).float().numpy()
+    ulp = np.abs(want16) * 2.0 ** -7                     # one bf16 ulp, plus the fp32 accumulation slack near zero
+    assert np.all(np.abs(y16.cpu().float().numpy() - want16) <= ulp + 1e-5 * rms)
+
+
+def test_gemm_no_scale_bias_matches_reference_semantics(ops):
+    """scale = 1, bias = 0 reproduces the reference kernel's plain X.T product (tmq/tmq_cuda.cu:289-427)."""
+    M, N, K = 64, 128, 128
+    W, P = make_weights(N, K, 5)
+    X = torch.randint(-4, 5, (M, K)).to(torch.bfloat16)            # small integers: every partial sum is exact
+    wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16)
+    y = ops.ternary_gemm(X.cuda(), wt, N, out_dtype=torch.float32)
+    ops.check_gemm_status()
+    assert np.array_equal(y.cpu().numpy(), T.gemm_f32_seq(X.float().numpy(), P, N))
+
+
+def test_prepack_is_layout_only(ops):
+    """Prepacking twice gives the same words, and both formats decode to the same matrix (checked through GEMMs with
+    one-hot activations, which read out single weight columns exactly)."""
+    N, K = 144, 128
+    W, P = make_weights(N, K, 9)
+    Pd = torch.from_numpy(P).cuda()
+    a, b = ops.prepack(Pd, N, ops.FMT_BF16), ops.prepack(Pd, N, ops.FMT_BF16)
+    assert torch.equal(a, b)
+    eye16 = torch.eye(K, dtype=torch.bfloat16, device="cuda")
+    eye8 = torch.eye(K, dtype=torch.int8, device="cuda")
+    t16 = ops.ternary_gemm(eye16, a, N, out_dtype=torch.float32)                   # [K, N] = T^T
+    t8 = ops.ternary_gemm_i8(eye8, ops.prepack(Pd, N, ops.FMT_I8), N)
+    ops.check_gemm_status()
+    assert np.array_equal(t16.cpu().numpy(), W.T)
+    assert np.array_equal(t8.cpu().numpy(), W.T.astype(np.int32))
+
+
+def test_gemm_argument_checks(ops):
+    wt = torch.zeros((128, 4), dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError):
+        ops.ternary_gemm(torch.zeros((4, 64), dtype=torch.float32, device="cuda"), wt, 128)
+    with pytest.raises(RuntimeError):
+        ops.ternary_gemm(torch.zeros((4, 128), dtype=torch.bfloat16, device="cuda"), wt, 128)   # K mismatch
+    with pytest.raises(RuntimeError):                                                             # K % 8 != 0
+        ops.ternary_gemm(torch.zeros((4, 60), dtype=torch.bfloat16, device="cuda"), wt, 128)

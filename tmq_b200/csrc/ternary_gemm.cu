@@ -1,0 +1,401 @@
+// Ternary GEMM from 2-bit packed weights on the 5th-generation tensor cores:  Y[m][n] = scale[n] * sum_k X[m][k] *
+// T[n][k] + bias[n],  T in {-1, 0, +1}.
+//
+// Replaces the reference's CUDA-core kernel (tmq/tmq_cuda.cu:289-427, launcher :478-549), which multiplies fp32
+// activations with a constant-memory LUT decode of the packed words.  Here the packed tile is decoded in shared
+// memory to EXACT bf16 / int8 values and fed to tcgen05.mma with the accumulator in tensor memory:
+//
+//   * roles per CTA (192 threads): warp 0 issues TMA loads (activation tile with 128-byte swizzle + the raw
+//     packed-weight tile), warps 2-5 decode the packed tile into the swizzled K-major operand layout, one thread of
+//     warp 1 issues the MMAs; warps 2-5 then drain the accumulator (tcgen05.ld), apply scale/bias and store.
+//   * the WEIGHT tile is the 128-row "A" operand and the ACTIVATION tile the N-side "B" operand (BN = 32..256
+//     rows), so one decoded weight tile is reused by up to 256 activation rows and skinny problems use a small BN.
+//     TMEM lane i therefore holds output column n0+i, TMEM column j holds output row m0+j.
+//   * 4-stage mbarrier pipeline: full_raw (TMA bytes landed) -> full_a (decode done) -> MMA -> empty (tcgen05.commit).
+//   * exactness: bf16 operands carry the code bits directly as {0, +2.0, -2.0} (sign and top exponent bit), the
+//     factor 2 is folded into the epilogue scale; products and int8 dot products are exact, accumulation is
+//     fp32 / int32 in TMEM.
+//   * every mbarrier wait is bounded and reports TMQ_ERR_TIMEOUT through a status word instead of hanging.
+//
+// Prepacked weight layout (built once from the reference layout by tmq_prepack): Wt[N][Kp/16] words, Kp = K rounded
+// up to 64, word = 16 consecutive k of one output channel, bit order chosen per activation type so that decode is
+// a shift+mask (bf16) or a byte-permute table lookup (int8).
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace tmq {
+
+constexpr int kGemmThreads = 192;
+constexpr int kTileN = 128;    // weight rows (output channels) per CTA = UMMA M
+constexpr int kStages = 4;
+constexpr int kRowBytes = 128; // bytes of one operand row per k-block (64 bf16 or 128 int8)
+
+enum { KIND_BF16 = 0, KIND_I8 = 1 };
+
+struct GemmArgs {
+    const float *scale;  // [N] or null (=1)
+    const float *bias;   // [N] or null (=0)
+    void *Y;
+    long long M, N, K, ldy;
+    int out_f32;         // bf16 kind: write fp32 instead of bf16
+    int *status;
+};
+
+template <int KIND>
+struct KindTraits;
+template <>
+struct KindTraits<KIND_BF16> {
+    static constexpr int BK = 64;          // k per block
+    static constexpr int RAW_ROW = 16;     // packed bytes per row per k-block
+    static constexpr uint32_t C_FMT = 1u;  // f32 accumulator
+};
+template <>
+struct KindTraits<KIND_I8> {
+    static constexpr int BK = 128;
+    static constexpr int RAW_ROW = 32;
+    static constexpr uint32_t C_FMT = 2u;  // s32 accumulator
+};
+
+template <int KIND, int BN>
+struct SmemLayout {
+    static constexpr int A_BYTES = kTileN * kRowBytes;                       // 16 KB
+    static constexpr int B_BYTES = BN * kRowBytes;
+    static constexpr int RAW_BYTES = kTileN * KindTraits<KIND>::RAW_ROW;     // 2 KB / 4 KB
+    static constexpr int A_OFF = 0;
+    static constexpr int B_OFF = A_OFF + kStages * A_BYTES;
+    static constexpr int RAW_OFF = B_OFF + kStages * B_BYTES;
+    static constexpr int BAR_OFF = RAW_OFF + kStages * RAW_BYTES;
+    static constexpr int TOTAL = BAR_OFF + 256 + 1024;                       // + barriers + alignment slack
+};
+
+// ---- decode of one packed word ------------------------------------------------------------------------------------
+
+// bf16 format: bits [31-2j:30-2j] = (sign, nonzero) of k = 2j+1, bits [15-2j:14-2j] of k = 2j, j = 0..7.
+// (w << 2j) & 0xC000C000 is then the bf16 pair {k=2j (low half), k=2j+1 (high half)} with values 0 / +2 / -2.
+__device__ __forceinline__ void decode_word_bf16(uint32_t w, uint32_t (&r)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; j++) r[j] = (w << (2 * j)) & 0xC000C000u;
+}
+
+// int8 format: nibble-spaced reference codes (0 -> 0, 1 -> +1, 2 -> -1); a byte permute with the 4-entry table
+// {0x00, 0x01, 0xFF, 0x00} turns four codes into four int8 values at once.
+__device__ __forceinline__ void decode_word_i8(uint32_t w, uint32_t (&r)[4]) {
+    const uint32_t table = 0x00FF0100u;
+    const uint32_t lo = w & 0x33333333u, hi = (w >> 2) & 0x33333333u;
+    r[0] = __byte_perm(table, 0u, lo);
+    r[1] = __byte_perm(table, 0u, hi);
+    r[2] = __byte_perm(table, 0u, lo >> 16);
+    r[3] = __byte_perm(table, 0u, hi >> 16);
+}
+
+// ---- the kernel -----------------------------------------------------------------------------------------------------
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, GemmArgs args) {
+    using KT = KindTraits<KIND>;
+    using L = SmemLayout<KIND, BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *full_raw = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
+    uint64_t *full_a = full_raw + kStages;
+    uint64_t *empty = full_a + kStages;
+    uint64_t *acc_full = empty + kStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long n0 = (long long)blockIdx.x * kTileN;
+    const long long m0 = (long long)blockIdx.y * BN;
+    const int nkb = (int)((args.K + KT::BK - 1) / KT::BK);
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            ptx::mbar_init(full_raw + s, 1);
+            ptx::mbar_init(full_a + s, 128);
+            ptx::mbar_init(empty + s, 1);
+        }
+        ptx::mbar_init(acc_full, 1);
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_x);
+        ptx::prefetch_tensormap(&tmap_w);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const bool healthy = (*reinterpret_cast<volatile int *>(args.status) == 0);
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0 && healthy) {
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % kStages;
+                const uint32_t ph = (uint32_t)(kb / kStages) & 1u;
+                if (!ptx::mbar_wait(empty + s, ph ^ 1u, args.status)) break;
+                ptx::mbar_arrive_expect_tx(full_raw + s, (uint32_t)(L::RAW_BYTES + L::B_BYTES));
+                ptx::tma_load_2d(smem + L::RAW_OFF + s * L::RAW_BYTES, &tmap_w, full_raw + s, kb * (KT::RAW_ROW / 4), (int)n0);
+                ptx::tma_load_2d(smem + L::B_OFF + s * L::B_BYTES, &tmap_x, full_raw + s, kb * KT::BK, (int)m0);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0 && healthy) {
+            constexpr uint32_t idesc = (KT::C_FMT << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; kb++) {
+                const int s = kb % kStages;
+                const uint32_t ph = (uint32_t)(kb / kStages) & 1u;
+                ok = ptx::mbar_wait(full_a + s, ph, args.status);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint64_t a_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::A_OFF + s * L::A_BYTES));
+                const uint64_t b_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES));
+#pragma unroll
+                for (int k4 = 0; k4 < kRowBytes / 32; k4++) {  // 32 bytes of K per instruction (16 bf16 / 32 int8)
+                    const uint32_t accum = (kb > 0 || k4 > 0) ? 1u : 0u;
+                    if (KIND == KIND_BF16) ptx::umma_f16(tmem_base, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                    else ptx::umma_i8(tmem_base, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                }
+                ptx::umma_commit(empty + s);  // stage reusable once these MMAs have read it
+            }
+            if (ok) ptx::umma_commit(acc_full);
+        }
+    } else {
+        // ---------------------------------------------------------------- decode warps (2..5), then epilogue
+        const int row = threadIdx.x - 64;  // weight row inside the tile, 0..127
+        bool ok = healthy;
+        for (int kb = 0; kb < nkb && ok; kb++) {
+            const int s = kb % kStages;
+            const uint32_t ph = (uint32_t)(kb / kStages) & 1u;
+            ok = ptx::mbar_wait(full_raw + s, ph, args.status);
+            if (!ok) break;
+            const uint8_t *raw = smem + L::RAW_OFF + s * L::RAW_BYTES + row * KT::RAW_ROW;
+            uint8_t *arow = smem + L::A_OFF + s * L::A_BYTES + row * kRowBytes;
+            const int sw = row & 7;
+            if (KIND == KIND_BF16) {
+                const uint4 p = *reinterpret_cast<const uint4 *>(raw);
+                const uint32_t words[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+                for (int wi = 0; wi < 4; wi++) {
+                    uint32_t r[8];
+                    decode_word_bf16(words[wi], r);
+                    *reinterpret_cast<uint4 *>(arow + (((2 * wi) ^ sw) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
+                    *reinterpret_cast<uint4 *>(arow + (((2 * wi + 1) ^ sw) << 4)) = make_uint4(r[4], r[5], r[6], r[7]);
+                }
+            } else {
+                const uint4 p0 = *reinterpret_cast<const uint4 *>(raw);
+                const uint4 p1 = *reinterpret_cast<const uint4 *>(raw + 16);
+                const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                for (int wi = 0; wi < 8; wi++) {
+                    uint32_t r[4];
+                    decode_word_i8(words[wi], r);
+                    *reinterpret_cast<uint4 *>(arow + ((wi ^ sw) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
+                }
+            }
+            ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+            ptx::mbar_arrive(full_a + s);
+        }
+        // ---------------------------------------------------------------- epilogue
+        if (ok) ok = ptx::mbar_wait(acc_full, 0u, args.status);
+        ptx::tc_fence_after_sync();
+        const int quarter = warp & 3;                    // TMEM lanes this warp may touch: 32*quarter .. +31
+        const long long n = n0 + quarter * 32 + lane;
+        const bool n_ok = ok && n < args.N;
+        float sc = 1.0f, bi = 0.0f;
+        if (n_ok) {
+            if (args.scale) sc = args.scale[n];
+            if (args.bias) bi = args.bias[n];
+        }
+        if (KIND == KIND_BF16) sc *= 0.5f;               // operands carried +-2.0
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld_x16(lane_addr + (uint32_t)c, v);
+                ptx::tmem_ld_wait();
+                if (n_ok) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const long long m = m0 + c + j;
+                        if (m < args.M) {
+                            if (KIND == KIND_I8) {
+                                reinterpret_cast<int *>(args.Y)[m * args.ldy + n] = (int)v[j];
+                            } else {
+                                const float f = fmaf(__uint_as_float(v[j]), sc, bi);
+                                if (args.out_f32) reinterpret_cast<float *>(args.Y)[m * args.ldy + n] = f;
+                                else reinterpret_cast<__nv_bfloat16 *>(args.Y)[m * args.ldy + n] = __float2bfloat16_rn(f);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- prepack: reference layout P[K][ceil(N/16)] -> Wt[N][Kp/16] ----------------------------------------------------------
+
+__device__ __forceinline__ uint32_t ref_code(const uint32_t *__restrict__ P, long long Q, long long K, long long n,
+                                             long long k) {
+    if (k >= K) return 0u;
+    return (P[k * Q + (n >> 4)] >> (2 * (15 - (int)(n & 15)))) & 3u;
+}
+
+__global__ void __launch_bounds__(256) prepack_kernel(const uint32_t *__restrict__ P, uint32_t *__restrict__ Wt,
+                                                       long long N, long long K, long long KW, int fmt) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= N * KW) return;
+    // consecutive threads take consecutive n for one kw: their reads of P share 32-bit words and rows
+    const long long n = idx % N, kw = idx / N;
+    const long long Q = (N + 15) / 16;
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const uint32_t c = ref_code(P, Q, K, n, kw * 16 + i);  // 0: zero, 1: +1, 2: -1 (3 never produced -> zero)
+        if (fmt == KIND_BF16) {
+            const uint32_t v = (c == 1u) ? 1u : ((c == 2u) ? 3u : 0u);  // (sign, nonzero)
+            const int j = i >> 1;
+            const int pos = (i & 1) ? (30 - 2 * j) : (14 - 2 * j);
+            word |= v << pos;
+        } else {
+            const uint32_t v = (c == 3u) ? 0u : c;
+            const int pos = ((i >> 3) << 4) + ((i & 3) << 2) + (((i >> 2) & 1) << 1);
+            word |= v << pos;
+        }
+    }
+    Wt[n * KW + kw] = word;
+}
+
+// ---- host side --------------------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        else
+            (void)cudaGetLastError();
+    });
+    return fn;
+}
+
+static bool make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t outer,
+                        uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int KIND, int BN>
+static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
+    using KT = KindTraits<KIND>;
+    using L = SmemLayout<KIND, BN>;
+    const long long KW = ((a.K + 63) / 64) * 4;  // words per prepacked row
+    CUtensorMap mx, mw;
+    const bool okx = (KIND == KIND_BF16)
+        ? make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, X, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.K * 2, KT::BK, BN,
+                      CU_TENSOR_MAP_SWIZZLE_128B)
+        : make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, X, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.K, KT::BK, BN,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    const bool okw = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KW * 4,
+                                 KT::RAW_ROW / 4, kTileN, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (!okx || !okw) return TMQ_ERR_LAUNCH;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(ternary_gemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    });
+    if (attr_err != cudaSuccess) return cuda_status(attr_err);
+    dim3 grid((unsigned)((a.N + kTileN - 1) / kTileN), (unsigned)((a.M + BN - 1) / BN));
+    ternary_gemm_kernel<KIND, BN><<<grid, kGemmThreads, L::TOTAL, st>>>(mx, mw, a);
+    return launch_status();
+}
+
+template <int KIND>
+static int dispatch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
+    if (a.M > 128) return launch_gemm<KIND, 256>(X, Wt, a, st);
+    if (a.M > 64) return launch_gemm<KIND, 128>(X, Wt, a, st);
+    if (a.M > 32) return launch_gemm<KIND, 64>(X, Wt, a, st);
+    return launch_gemm<KIND, 32>(X, Wt, a, st);
+}
+
+static int check_gemm_common(const void *X, const uint32_t *Wt, const void *Y, long long M, long long N, long long K,
+                             long long ldy, const int *status, int x_elem_bytes) {
+    if (!X || !Wt || !Y || !status) return TMQ_ERR_ARG;
+    if (M <= 0 || N <= 0 || K <= 0 || ldy < N) return TMQ_ERR_ARG;
+    if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
+    if ((K * x_elem_bytes) % 16 != 0) return TMQ_ERR_UNSUPPORTED;  // TMA row pitch must be a multiple of 16 bytes
+    if (!aligned(X, 16) || !aligned(Wt, 16) || !aligned(status, 4)) return TMQ_ERR_ALIGN;
+    if ((M + 255) / 256 > 65535) return TMQ_ERR_UNSUPPORTED;
+    return TMQ_OK;
+}
+
+}  // namespace tmq
+
+using namespace tmq;
+
+extern "C" size_t tmq_prepack_words(int64_t N, int64_t K) {
+    if (N <= 0 || K <= 0) return 0;
+    return (size_t)N * (size_t)(((K + 63) / 64) * 4);
+}
+
+extern "C" int tmq_prepack(const uint32_t *P, uint32_t *Wt, int64_t N, int64_t K, int fmt, void *stream) {
+    if (!P || !Wt || N <= 0 || K <= 0 || (fmt != KIND_BF16 && fmt != KIND_I8)) return TMQ_ERR_ARG;
+    if (!aligned(Wt, 16)) return TMQ_ERR_ALIGN;
+    const long long KW = ((K + 63) / 64) * 4;
+    const long long total = (long long)N * KW;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
+    prepack_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(P, Wt, N, K, KW, fmt);
+    return launch_status();
+}
+
+extern "C" int tmq_ternary_gemm_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y,
+                                     int64_t M, int64_t N, int64_t K, int64_t ldy, int out_f32, int *status,
+                                     void *stream) {
+    int rc = check_gemm_common(X, Wt, Y, M, N, K, ldy, status, 2);
+    if (rc != TMQ_OK) return rc;
+    if (!aligned(Y, out_f32 ? 4 : 2)) return TMQ_ERR_ALIGN;
+    GemmArgs a = {scale, bias, Y, M, N, K, ldy, out_f32, status};
+    return dispatch_gemm<KIND_BF16>(X, Wt, a, (cudaStream_t)stream);
+}
+
+extern "C" int tmq_ternary_gemm_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K,
+                                   int64_t ldy, int *status, void *stream) {
+    int rc = check_gemm_common(X, Wt, Y, M, N, K, ldy, status, 1);
+    if (rc != TMQ_OK) return rc;
+    if (!aligned(Y, 4)) return TMQ_ERR_ALIGN;
+    GemmArgs a = {nullptr, nullptr, Y, M, N, K, ldy, 0, status};
+    return dispatch_gemm<KIND_I8>(X, Wt, a, (cudaStream_t)stream);
+}

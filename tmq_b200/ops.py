@@ -254,3 +254,88 @@ def expand_ternary(packed, orig_shape, entropy_decode=False):
     with torch.cuda.device(dev):
         check(lib().tmq_unpack2b_f32(_ptr(p), _ptr(out), N, K, _stream(p)), "expand_ternary")
     return out.to(packed.device)
+
+
+# ------------------------------------------------------------------------------------------------ ternary GEMM
+
+FMT_BF16, FMT_I8 = 0, 1
+_status = {}
+
+
+def gemm_status_word(device):
+    """Per-device int32 the GEMM kernels report bounded-wait failures into (0 = healthy)."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _status.get(key)
+    if buf is None:
+        buf = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = buf
+    return buf
+
+
+def check_gemm_status(device="cuda"):
+    """Synchronising check: raises if any GEMM launch on this device gave up on a device-side wait."""
+    code = int(gemm_status_word(device).item())
+    if code != 0:
+        gemm_status_word(device).zero_()
+        raise _lib.TmqError(f"ternary GEMM kernel reported status {code}: "
+                            f"{lib().tmq_status_string(code).decode()}")
+
+
+def prepack(packed, columns, fmt=FMT_BF16):
+    """Reference-layout packed weights int32 [K, ceil(N/16)] (or the 4-D conv form) -> prepacked int32 [N, Kp/16]
+    in the bit order the GEMM kernels decode (fmt: FMT_BF16 or FMT_I8).  Done once per weight tensor."""
+    if packed.dtype != torch.int32 or packed.device.type != "cuda":
+        raise RuntimeError("prepack: expected a CUDA int32 tensor")
+    N = int(columns)
+    Q = (N + 15) // 16
+    p = packed.contiguous().view(-1, Q)
+    K = p.shape[0]
+    words = lib().tmq_prepack_words(N, K)
+    out = torch.empty((N, words // N), dtype=torch.int32, device=p.device)
+    with torch.cuda.device(p.device):
+        check(lib().tmq_prepack(_ptr(p), _ptr(out), N, K, int(fmt), _stream(p)), "prepack")
+    return out
+
+
+def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16):
+    """Y = scale * (x @ T^T) + bias with x bf16 [M, K] and prepacked weights wt (FMT_BF16); fp32 accumulation on the
+    tensor cores; Y is bf16 or fp32 [M, N]."""
+    if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 2:
+        raise RuntimeError("ternary_gemm: expected a 2-D CUDA bf16 activation tensor")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("ternary_gemm: output dtype must be bfloat16 or float32")
+    x = x.contiguous()
+    M, K = x.shape
+    N = int(columns)
+    if wt.dtype != torch.int32 or wt.shape[0] != N or wt.shape[1] != (K + 63) // 64 * 4:
+        raise RuntimeError("ternary_gemm: prepacked weights do not match the problem shape")
+    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if M == 0:
+        return y
+    sc = None if scale is None else scale.to(device=x.device, dtype=torch.float32).contiguous()
+    bi = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
+    st = gemm_status_word(x.device)
+    with torch.cuda.device(x.device):
+        check(lib().tmq_ternary_gemm_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
+                                          _ptr(bi) if bi is not None else None, _ptr(y), M, N, K, N,
+                                          1 if out_dtype == torch.float32 else 0, _ptr(st), _stream(x)), "ternary_gemm")
+    return y
+
+
+def ternary_gemm_i8(x, wt, columns):
+    """Exact int32 Y = x @ T^T with x int8 [M, K] and prepacked weights wt (FMT_I8)."""
+    if x.dtype != torch.int8 or x.device.type != "cuda" or x.dim() != 2:
+        raise RuntimeError("ternary_gemm_i8: expected a 2-D CUDA int8 activation tensor")
+    x = x.contiguous()
+    M, K = x.shape
+    N = int(columns)
+    if wt.dtype != torch.int32 or wt.shape[0] != N or wt.shape[1] != (K + 63) // 64 * 4:
+        raise RuntimeError("ternary_gemm_i8: prepacked weights do not match the problem shape")
+    y = torch.empty((M, N), dtype=torch.int32, device=x.device)
+    if M == 0:
+        return y
+    st = gemm_status_word(x.device)
+    with torch.cuda.device(x.device):
+        check(lib().tmq_ternary_gemm_i8(_ptr(x), _ptr(wt), _ptr(y), M, N, K, N, _ptr(st), _stream(x)), "ternary_gemm_i8")
+    return y
