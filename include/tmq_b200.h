@@ -150,6 +150,14 @@ int tmq_ternary_gemm_bf16(const void *X, const uint32_t *Wt, const float *scale,
 int tmq_ternary_gemm_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
                         int *status, void *stream);
 
+/* Skinny form for M <= 8 activation rows (decode-like GEMV): streams the packed weights once at HBM speed, warp-level
+ * MMA on exactly decoded operands, deterministic.  Same operand conventions as the GEMM entry points above.
+ * replaces: ternary_mvm_cuda, tmq/tmq_cuda.cu:563-603 (kernel :242-286). */
+int tmq_ternary_gemv_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int64_t M,
+                          int64_t N, int64_t K, int64_t ldy, int out_f32, void *stream);
+int tmq_ternary_gemv_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
+                        void *stream);
+
 #ifdef __cplusplus
 }
 #endif

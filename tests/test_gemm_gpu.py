@@ -26,20 +26,29 @@ SHAPES = [(1, 128, 64), (8, 128, 64), (32, 256, 128), (33, 200, 192), (64, 128, 
           (129, 128, 64), (256, 256, 1024), (300, 520, 576), (512, 1000, 2304)]
 
 
+PATHS = ["tiles", "gemv"]
+
+
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("M,N,K", SHAPES)
-def test_gemm_i8_exact(ops, M, N, K):
+def test_gemm_i8_exact(ops, M, N, K, path):
+    if path == "gemv" and M > 40:
+        pytest.skip("the streaming kernel is meant for skinny problems")
     K = (K + 15) // 16 * 16
     W, P = make_weights(N, K, M * 7 + N)
     rng = np.random.default_rng(K)
     X = rng.integers(-127, 128, (M, K)).astype(np.int8)
     wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_I8)
-    Y = ops.ternary_gemm_i8(torch.from_numpy(X).cuda(), wt, N)
+    Y = ops.ternary_gemm_i8(torch.from_numpy(X).cuda(), wt, N, path=path)
     ops.check_gemm_status()
     assert np.array_equal(Y.cpu().numpy(), T.gemm_i8_fast(X, P, N))
 
 
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("M,N,K", SHAPES)
-def test_gemm_bf16_tolerance(ops, M, N, K):
+def test_gemm_bf16_tolerance(ops, M, N, K, path):
+    if path == "gemv" and M > 40:
+        pytest.skip("the streaming kernel is meant for skinny problems")
     K = (K + 7) // 8 * 8
     W, P = make_weights(N, K, M * 11 + N)
     gen = torch.Generator().manual_seed(K)
@@ -49,14 +58,14 @@ def test_gemm_bf16_tolerance(ops, M, N, K):
     wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16)
     ref_acc = T.gemm_f64_fast(X.float().numpy(), P, N)                       # exact sum of exact products
     ref = ref_acc * scale.double().numpy()[None, :] + bias.double().numpy()[None, :]
-    y32 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.float32)
+    y32 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.float32, path=path)
     ops.check_gemm_status()
     got = y32.cpu().double().numpy()
     rms = np.sqrt((ref ** 2).mean(axis=1, keepdims=True))
     assert np.all(np.abs(got - ref) <= 1e-3 * np.maximum(np.abs(ref), rms)), np.abs(got - ref).max()
     # in practice fp32 accumulation of exact products is far tighter than the 1e-3 bar
     assert np.all(np.abs(got - ref) <= 1e-5 * np.maximum(np.abs(ref), rms))
-    y16 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.bfloat16)
+    y16 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.bfloat16, path=path)
     ops.check_gemm_status()
     want16 = torch.from_numpy(ref).to(torch.bfloat16).float().numpy()
     ulp = np.abs(want16) * 2.0 ** -7                     # one bf16 ulp, plus the fp32 accumulation slack near zero
@@ -99,3 +108,26 @@ def test_gemm_argument_checks(ops):
         ops.ternary_gemm(torch.zeros((4, 128), dtype=torch.bfloat16, device="cuda"), wt, 128)   # K mismatch
     with pytest.raises(RuntimeError):                                                             # K % 8 != 0
         ops.ternary_gemm(torch.zeros((4, 60), dtype=torch.bfloat16, device="cuda"), wt, 128)
+
+
+@pytest.mark.parametrize("M", [1, 8, 32])
+def test_gemv_baseline_shape(ops, M):
+    """BASELINE decode-like config: N = 11008, K = 4096, weights at P = 0.3/0.4/0.3, per-channel scale in [0.01, 0.1],
+    bf16 activations N(0,1) (rel 1e-3 before output rounding) and int8 activations in [-127, 127] (bit-exact)."""
+    N, K = 11008, 4096
+    W, P = make_weights(N, K, 0)
+    Pd = torch.from_numpy(P).cuda()
+    gen = torch.Generator().manual_seed(M)
+    X = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    scale = torch.rand(N, generator=gen) * 0.09 + 0.01
+    ref = T.gemm_f64_fast(X.float().numpy(), P, N) * scale.double().numpy()[None, :]
+    y = ops.ternary_gemm(X.cuda(), ops.prepack(Pd, N, ops.FMT_BF16), N, scale.cuda(), out_dtype=torch.float32)
+    rms = np.sqrt((ref ** 2).mean(axis=1, keepdims=True))
+    assert np.all(np.abs(y.cpu().double().numpy() - ref) <= 1e-3 * np.maximum(np.abs(ref), rms))
+    assert np.all(np.abs(y.cpu().double().numpy() - ref) <= 1e-5 * np.maximum(np.abs(ref), rms))
+    X8 = torch.randint(-127, 128, (M, K), generator=gen, dtype=torch.int8)
+    y8 = ops.ternary_gemm_i8(X8.cuda(), ops.prepack(Pd, N, ops.FMT_I8), N)
+    assert np.array_equal(y8.cpu().numpy(), T.gemm_i8_fast(X8.numpy(), P, N))
+    # deterministic: same bits on a second run
+    y2 = ops.ternary_gemm(X.cuda(), ops.prepack(Pd, N, ops.FMT_BF16), N, scale.cuda(), out_dtype=torch.float32)
+    assert torch.equal(y, y2)

@@ -48,6 +48,9 @@ _SIGNATURES = {
     "tmq_prepack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "tmq_ternary_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                       c_int64, c_int, c_void_p, c_void_p]),
+    "tmq_ternary_gemv_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                      c_int64, c_int, c_void_p]),
+    "tmq_ternary_gemv_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "tmq_ternary_gemm_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p]),
 }

@@ -259,6 +259,7 @@ def expand_ternary(packed, orig_shape, entropy_decode=False):
 # ------------------------------------------------------------------------------------------------ ternary GEMM
 
 FMT_BF16, FMT_I8 = 0, 1
+GEMV_MAX_ROWS = 32        # up to here the streaming GEMV kernel (8 rows per pass) beats the tiled tensor-core kernel
 _status = {}
 
 
@@ -298,9 +299,10 @@ def prepack(packed, columns, fmt=FMT_BF16):
     return out
 
 
-def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16):
+def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16, path="auto"):
     """Y = scale * (x @ T^T) + bias with x bf16 [M, K] and prepacked weights wt (FMT_BF16); fp32 accumulation on the
-    tensor cores; Y is bf16 or fp32 [M, N]."""
+    tensor cores; Y is bf16 or fp32 [M, N].  path: "auto" (GEMV kernel up to GEMV_MAX_ROWS rows, tiled tcgen05 kernel
+    above), or "gemv" / "tiles" to pin one."""
     if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 2:
         raise RuntimeError("ternary_gemm: expected a 2-D CUDA bf16 activation tensor")
     if out_dtype not in (torch.bfloat16, torch.float32):
@@ -315,6 +317,18 @@ def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16
         return y
     sc = None if scale is None else scale.to(device=x.device, dtype=torch.float32).contiguous()
     bi = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
+    if path == "gemv" or (path == "auto" and M <= GEMV_MAX_ROWS):
+        # decode-like shapes: the streaming kernel, 8 activation rows per pass
+        esz = y.element_size()
+        with torch.cuda.device(x.device):
+            for m0 in range(0, M, 8):
+                rows = min(8, M - m0)
+                check(lib().tmq_ternary_gemv_bf16(ctypes.c_void_p(x.data_ptr() + m0 * K * 2), _ptr(wt),
+                                                  _ptr(sc) if sc is not None else None,
+                                                  _ptr(bi) if bi is not None else None,
+                                                  ctypes.c_void_p(y.data_ptr() + m0 * N * esz), rows, N, K, N,
+                                                  1 if out_dtype == torch.float32 else 0, _stream(x)), "ternary_gemv")
+        return y
     st = gemm_status_word(x.device)
     with torch.cuda.device(x.device):
         check(lib().tmq_ternary_gemm_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
@@ -323,7 +337,7 @@ def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16
     return y
 
 
-def ternary_gemm_i8(x, wt, columns):
+def ternary_gemm_i8(x, wt, columns, path="auto"):
     """Exact int32 Y = x @ T^T with x int8 [M, K] and prepacked weights wt (FMT_I8)."""
     if x.dtype != torch.int8 or x.device.type != "cuda" or x.dim() != 2:
         raise RuntimeError("ternary_gemm_i8: expected a 2-D CUDA int8 activation tensor")
@@ -334,6 +348,14 @@ def ternary_gemm_i8(x, wt, columns):
         raise RuntimeError("ternary_gemm_i8: prepacked weights do not match the problem shape")
     y = torch.empty((M, N), dtype=torch.int32, device=x.device)
     if M == 0:
+        return y
+    if path == "gemv" or (path == "auto" and M <= GEMV_MAX_ROWS):
+        with torch.cuda.device(x.device):
+            for m0 in range(0, M, 8):
+                rows = min(8, M - m0)
+                check(lib().tmq_ternary_gemv_i8(ctypes.c_void_p(x.data_ptr() + m0 * K), _ptr(wt),
+                                                ctypes.c_void_p(y.data_ptr() + m0 * N * 4), rows, N, K, N, _stream(x)),
+                      "ternary_gemv_i8")
         return y
     st = gemm_status_word(x.device)
     with torch.cuda.device(x.device):
