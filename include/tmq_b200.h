@@ -158,6 +158,16 @@ int tmq_ternary_gemv_bf16(const void *X, const uint32_t *Wt, const float *scale,
 int tmq_ternary_gemv_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
                         void *stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Entropy-coded storage of packed weights (HOST pointers; sequential range coder, no GPU work).  Streams are
+ * byte-identical to the reference's: 26-byte big-endian header + range-coder payload.  P is the packed matrix
+ * [rows][ceil(cols/16)] with rows = K and cols = N of the weight (the coder walks the packed, transposed matrix).
+ * replaces: compress_ternary / decompress_ternary, tmq/tmq_native.cpp:439-503 (:50-140), tmq/rangecoder.h:41-193.
+ * ------------------------------------------------------------------------------------------------ */
+size_t tmq_rc_encode_bound(int64_t rows, int64_t cols);
+int tmq_rc_encode(const uint32_t *P, int64_t rows, int64_t cols, uint8_t *out, size_t out_cap, size_t *out_len);
+int tmq_rc_decode(const uint8_t *in, size_t in_len, uint32_t *P, int64_t rows, int64_t cols);
+
 #ifdef __cplusplus
 }
 #endif

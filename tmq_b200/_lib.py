@@ -44,6 +44,9 @@ _SIGNATURES = {
     "tmq_pack2b_i32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "tmq_pack2b_i8": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "tmq_unpack2b_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "tmq_rc_encode_bound": (c_size_t, [c_int64, c_int64]),
+    "tmq_rc_encode": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_size_t, ctypes.POINTER(c_size_t)]),
+    "tmq_rc_decode": (c_int, [c_void_p, c_size_t, c_void_p, c_int64, c_int64]),
     "tmq_prepack_words": (c_size_t, [c_int64, c_int64]),
     "tmq_prepack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "tmq_ternary_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
