@@ -90,9 +90,10 @@ int tmq_softstep_fused_step(const float *w, const float *g, float *y, float *gw,
 /* Multi-tensor forms: one launch over every registered layer (tmq/tmq.py:263-272, :298-310 loop over layers).
  * A plan is a host-built table the caller uploads once to device memory (8-byte aligned) and reuses. */
 typedef struct {
-    const float *w; /* weights (device)                                         */
-    float *out;     /* per-tensor output (gradient for qloss_bwd, unused else)  */
-    uint64_t n;     /* elements                                                 */
+    const float *w;      /* weights (device)                                                        */
+    float *out;          /* per-tensor output (gradient for qloss_bwd), used when out_base is NULL   */
+    uint64_t n;          /* elements                                                                */
+    uint64_t out_offset; /* element offset of this tensor's output inside out_base (multiple of 4)  */
 } tmq_mt_tensor;
 
 size_t tmq_mt_plan_bytes(const tmq_mt_tensor *tensors, int ntensors);
@@ -101,9 +102,11 @@ int tmq_mt_plan_build(const tmq_mt_tensor *tensors, int ntensors, void *host_pla
 /* *loss_out (device fp64) = sum_l mean_i(strength*softstep'(w_li; sharpness)) */
 int tmq_mt_qloss(const void *d_plan, int ntensors, int nchunks, double sharpness, double strength, double *loss_out,
                  void *scratch, size_t scratch_bytes, void *stream);
-/* out_l = (upstream / n_l) * strength * softstep''(w_l; sharpness); d_upstream: device fp32 scalar or NULL (= 1) */
+/* out_l = (upstream / n_l) * strength * softstep''(w_l; sharpness); d_upstream: device fp32 scalar or NULL (= 1).
+ * Outputs go to out_base + out_offset_l when out_base is given (a fresh flat buffer per call, 16-byte aligned),
+ * else to the per-tensor pointers stored in the plan. */
 int tmq_mt_qloss_bwd(const void *d_plan, int ntensors, int nchunks, double sharpness, double strength,
-                     const float *d_upstream, void *stream);
+                     const float *d_upstream, float *out_base, void *stream);
 /* w_l = clamp(w_l, lo, hi) in place */
 int tmq_mt_clamp(const void *d_plan, int ntensors, int nchunks, float lo, float hi, void *stream);
 

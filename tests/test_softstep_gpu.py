@@ -145,7 +145,7 @@ def test_multi_tensor_forms(ops):
     gen = torch.Generator().manual_seed(3)
     shapes = [(64, 3, 7, 7), (64, 64, 3, 3), (101, 512), (5,), (4097,)]
     ws = [(torch.rand(s, generator=gen) * 3 - 1.5).cuda() for s in shapes]
-    plan = ops.MultiTensorPlan(ws, with_grad_out=True)
+    plan = ops.MultiTensorPlan(ws)
     loss = plan.qloss(5.0, 1e-3).item()
     ref = sum(O.qloss_sum_f64(w.cpu().numpy(), 5.0, 1e-3) / w.numel() for w in ws)
     assert abs(loss - ref) <= 2.5e-7 * abs(ref)

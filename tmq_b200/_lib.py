@@ -16,7 +16,7 @@ c_int, c_size_t, c_double, c_float, c_void_p, c_int64 = (ctypes.c_int, ctypes.c_
 
 
 class MtTensor(ctypes.Structure):
-    _fields_ = [("w", c_void_p), ("out", c_void_p), ("n", ctypes.c_uint64)]
+    _fields_ = [("w", c_void_p), ("out", c_void_p), ("n", ctypes.c_uint64), ("out_offset", ctypes.c_uint64)]
 
 
 _SIGNATURES = {
@@ -37,7 +37,7 @@ _SIGNATURES = {
     "tmq_mt_plan_bytes": (c_size_t, [ctypes.POINTER(MtTensor), c_int]),
     "tmq_mt_plan_build": (c_int, [ctypes.POINTER(MtTensor), c_int, c_void_p, c_size_t, ctypes.POINTER(c_int)]),
     "tmq_mt_qloss": (c_int, [c_void_p, c_int, c_int, c_double, c_double, c_void_p, c_void_p, c_size_t, c_void_p]),
-    "tmq_mt_qloss_bwd": (c_int, [c_void_p, c_int, c_int, c_double, c_double, c_void_p, c_void_p]),
+    "tmq_mt_qloss_bwd": (c_int, [c_void_p, c_int, c_int, c_double, c_double, c_void_p, c_void_p, c_void_p]),
     "tmq_mt_clamp": (c_int, [c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
     "tmq_selftest_const_div": (c_int, [c_double, c_void_p, c_void_p]),
     "tmq_pack2b_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),

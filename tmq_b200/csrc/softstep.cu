@@ -424,6 +424,7 @@ struct MtTensor {
     const float *w;
     float *out;
     unsigned long long n;
+    unsigned long long out_offset;
 };
 struct MtChunk {
     unsigned tensor;
@@ -433,7 +434,8 @@ struct MtChunk {
 template <unsigned F, bool FAST>
 __global__ void __launch_bounds__(kThreads) softstep_mt_kernel(const MtTensor *__restrict__ tensors,
                                                                 const MtChunk *__restrict__ chunks, int nchunks,
-                                                                Args a, const float *__restrict__ upstream) {
+                                                                Args a, const float *__restrict__ upstream,
+                                                                float *__restrict__ out_base) {
     constexpr bool SUM = (F & F_QSUM) != 0;
     double acc = 0.0;
     const float up = (F & F_QGRAD) ? (upstream ? *upstream : 1.0f) : 0.0f;
@@ -443,7 +445,8 @@ __global__ void __launch_bounds__(kThreads) softstep_mt_kernel(const MtTensor *_
         const size_t begin = (size_t)ch.index * kChunk;
         const size_t count = (t.n - begin) < (size_t)kChunk ? (size_t)(t.n - begin) : (size_t)kChunk;
         const float *w = t.w + begin;
-        float *out = (F & F_CLAMP) ? const_cast<float *>(t.w) + begin : t.out + begin;
+        float *out = (F & F_CLAMP) ? const_cast<float *>(t.w) + begin
+                                   : (out_base ? out_base + t.out_offset : t.out) + begin;
         if (F & F_QGRAD) a.gq = __fdiv_rn(up, (float)t.n);  // what autograd's mean backward hands down
         double csum = 0.0;
         const size_t nv = count / 4;
@@ -634,7 +637,8 @@ extern "C" int tmq_mt_plan_build(const tmq_mt_tensor *tensors, int ntensors, voi
     for (int i = 0; i < ntensors; i++) {
         if (!tensors[i].w || tensors[i].n == 0) return TMQ_ERR_ARG;
         if (!aligned(tensors[i].w, 16) || (tensors[i].out && !aligned(tensors[i].out, 16))) return TMQ_ERR_ALIGN;
-        T[i].w = tensors[i].w; T[i].out = tensors[i].out; T[i].n = tensors[i].n;
+        if (tensors[i].out_offset % 4 != 0) return TMQ_ERR_ALIGN;
+        T[i].w = tensors[i].w; T[i].out = tensors[i].out; T[i].n = tensors[i].n; T[i].out_offset = tensors[i].out_offset;
         const unsigned cnt = (unsigned)((tensors[i].n + kChunk - 1) / kChunk);
         for (unsigned c = 0; c < cnt; c++) { C[k].tensor = (unsigned)i; C[k].index = c; k++; }
     }
@@ -643,15 +647,15 @@ extern "C" int tmq_mt_plan_build(const tmq_mt_tensor *tensors, int ntensors, voi
 }
 
 template <unsigned F>
-static int launch_mt(const void *d_plan, int ntensors, int nchunks, Args a, const float *up, bool fast,
+static int launch_mt(const void *d_plan, int ntensors, int nchunks, Args a, const float *up, float *out_base, bool fast,
                      cudaStream_t st) {
     if (!d_plan || ntensors <= 0 || nchunks <= 0) return TMQ_ERR_ARG;
     if (!aligned(d_plan, 8)) return TMQ_ERR_ALIGN;
     const MtTensor *T = reinterpret_cast<const MtTensor *>(d_plan);
     const MtChunk *C = reinterpret_cast<const MtChunk *>(T + ntensors);
     const unsigned grid = (unsigned)(nchunks < kMaxPartials ? nchunks : kMaxPartials);
-    if (fast) softstep_mt_kernel<F, true><<<grid, kThreads, 0, st>>>(T, C, nchunks, a, up);
-    else softstep_mt_kernel<F, false><<<grid, kThreads, 0, st>>>(T, C, nchunks, a, up);
+    if (fast) softstep_mt_kernel<F, true><<<grid, kThreads, 0, st>>>(T, C, nchunks, a, up, out_base);
+    else softstep_mt_kernel<F, false><<<grid, kThreads, 0, st>>>(T, C, nchunks, a, up, out_base);
     return launch_status();
 }
 
@@ -663,16 +667,17 @@ extern "C" int tmq_mt_qloss(const void *d_plan, int ntensors, int nchunks, doubl
     Args a = {};
     a.one = 1.0f; a.nzero = -0.0f;
     a.q = make_hardness(sharpness); a.sd = (float)(strength * sharpness); a.scratch = scratch; a.loss_out = loss_out;
-    return launch_mt<F_QSUM>(d_plan, ntensors, nchunks, a, nullptr, factor_ok(a.sd), (cudaStream_t)stream);
+    return launch_mt<F_QSUM>(d_plan, ntensors, nchunks, a, nullptr, nullptr, factor_ok(a.sd), (cudaStream_t)stream);
 }
 
 extern "C" int tmq_mt_qloss_bwd(const void *d_plan, int ntensors, int nchunks, double sharpness, double strength,
-                                const float *d_upstream, void *stream) {
+                                const float *d_upstream, float *out_base, void *stream) {
     if (!hardness_ok(sharpness) || !isfinite(strength)) return TMQ_ERR_ARG;
+    if (out_base && !aligned(out_base, 16)) return TMQ_ERR_ALIGN;
     Args a = {};
     a.one = 1.0f; a.nzero = -0.0f;
     a.q = make_hardness(sharpness); a.sdd = (float)(strength * sharpness * sharpness);
-    return launch_mt<F_QGRAD>(d_plan, ntensors, nchunks, a, d_upstream, factor_ok(a.sdd), (cudaStream_t)stream);
+    return launch_mt<F_QGRAD>(d_plan, ntensors, nchunks, a, d_upstream, out_base, factor_ok(a.sdd), (cudaStream_t)stream);
 }
 
 extern "C" int tmq_mt_clamp(const void *d_plan, int ntensors, int nchunks, float lo, float hi, void *stream) {
@@ -680,7 +685,7 @@ extern "C" int tmq_mt_clamp(const void *d_plan, int ntensors, int nchunks, float
     Args a = {};
     a.one = 1.0f; a.nzero = -0.0f;
     a.lo = lo; a.hi = hi;
-    return launch_mt<F_CLAMP>(d_plan, ntensors, nchunks, a, nullptr, true, (cudaStream_t)stream);
+    return launch_mt<F_CLAMP>(d_plan, ntensors, nchunks, a, nullptr, nullptr, true, (cudaStream_t)stream);
 }
 
 extern "C" int tmq_selftest_const_div(double digamma, unsigned long long *mismatches, void *stream) {

@@ -141,29 +141,27 @@ class MultiTensorPlan:
     """Device-resident table over a fixed list of weight tensors (one per registered layer) so that loss, its
     gradient and the clamp run as ONE launch each instead of one per layer."""
 
-    def __init__(self, weights, with_grad_out=False):
+    def __init__(self, weights):
         assert len(weights) > 0
         self.device = weights[0].device
         for w in weights:
-            if w.device != self.device or w.dtype != torch.float32 or not w.is_contiguous():
+            if w.device != self.device or w.device.type != "cuda" or w.dtype != torch.float32 or not w.is_contiguous():
                 raise RuntimeError("MultiTensorPlan: weights must be contiguous fp32 tensors on one CUDA device")
-        self.weights = list(weights)
         self.ptrs = [w.data_ptr() for w in weights]
-        self.grads = None
-        if with_grad_out:
-            # one flat buffer, each tensor's slice 16-byte aligned
-            offs, total = [], 0
-            for w in weights:
-                offs.append(total)
-                total += (w.numel() + 3) // 4 * 4
-            flat = torch.empty(total, dtype=torch.float32, device=self.device)
-            self.grads = [flat[o:o + w.numel()].view(w.shape) for o, w in zip(offs, weights)]
+        self.shapes = [tuple(w.shape) for w in weights]
+        # outputs of the gradient kernel live in one flat buffer, each tensor's slice 16-byte aligned
+        self.offsets, total = [], 0
+        for w in weights:
+            self.offsets.append(total)
+            total += (w.numel() + 3) // 4 * 4
+        self.flat_elems = total
         n = len(weights)
         arr = (_lib.MtTensor * n)()
         for i, w in enumerate(weights):
             arr[i].w = w.data_ptr()
-            arr[i].out = self.grads[i].data_ptr() if self.grads is not None else None
+            arr[i].out = None
             arr[i].n = w.numel()
+            arr[i].out_offset = self.offsets[i]
         nbytes = lib().tmq_mt_plan_bytes(arr, n)
         host = torch.empty(nbytes, dtype=torch.uint8)
         nchunks = ctypes.c_int(0)
@@ -173,9 +171,11 @@ class MultiTensorPlan:
         self.table = host.to(self.device)
 
     def matches(self, weights):
-        return len(weights) == len(self.ptrs) and all(w.data_ptr() == p for w, p in zip(weights, self.ptrs))
+        return (len(weights) == len(self.ptrs) and all(w.data_ptr() == p for w, p in zip(weights, self.ptrs))
+                and all(tuple(w.shape) == s for w, s in zip(weights, self.shapes)))
 
     def qloss(self, sharpness, strength):
+        """fp64 0-d tensor: sum over tensors of mean(strength * S'(w; sharpness))."""
         out = torch.empty((), dtype=torch.float64, device=self.device)
         scratch = reduce_scratch(self.device)
         with torch.cuda.device(self.device):
@@ -184,15 +184,22 @@ class MultiTensorPlan:
         return out
 
     def qloss_bwd(self, sharpness, strength, upstream=None):
-        assert self.grads is not None
+        """Gradients of qloss() wrt every tensor (fresh storage per call), scaled by the fp32 0-d `upstream`."""
         up = None
         if upstream is not None:
             up = upstream.to(device=self.device, dtype=torch.float32).reshape(()).contiguous()
+        flat = torch.empty(self.flat_elems, dtype=torch.float32, device=self.device)
         with torch.cuda.device(self.device):
             check(lib().tmq_mt_qloss_bwd(_ptr(self.table), self.ntensors, self.nchunks, float(sharpness),
-                                         float(strength), _ptr(up) if up is not None else None,
+                                         float(strength), _ptr(up) if up is not None else None, _ptr(flat),
                                          _stream(self.table)), "mt_qloss_bwd")
-        return self.grads
+        grads = []
+        for off, shape in zip(self.offsets, self.shapes):
+            n = 1
+            for d in shape:
+                n *= d
+            grads.append(flat[off:off + n].view(shape))
+        return grads
 
     def clamp_(self, lo, hi):
         with torch.cuda.device(self.device):
