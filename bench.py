@@ -260,6 +260,10 @@ def run_ours(args):
                      "kernel": "softstep_kernel<FWD|BWD|QSUM|QGRAD|CLAMP>", "kernel_ms": kernel_ms,
                      "algorithmic_bytes": n * BYTES_PER_ELEM},
     }
+    if world == 1 and not args.no_extra:
+        del w, g, out, dw, dg
+        torch.cuda.empty_cache()
+        line["extra"] = ternary_sections(peaks)
     if world == 1 and not args.no_cpu:
         gbs, dt = cpu_softstep_baseline(1 << 24, 3)
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
@@ -268,6 +272,119 @@ def run_ours(args):
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------ ternary kernels
+
+def _time_cuda(fn, reps, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def _ternary_packed(ops, N, K, seed, p=(0.3, 0.4, 0.3)):
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    u = torch.rand(N, K, generator=gen, device="cuda")
+    W = torch.where(u < p[0], -1.0, torch.where(u < p[0] + p[1], 0.0, 1.0))
+    return ops.compactify_ternary(W)
+
+
+def measure_tensor_peaks():
+    """Dense 8192^3 library GEMMs on this GPU, best of 10: bf16 (torch.matmul) and int8 (torch._int_mm)."""
+    out = {}
+    a = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
+    b = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
+    best = min(_time_cuda(lambda: a @ b, 1, warm=1) for _ in range(10))
+    out["bf16_tflops"] = 2 * 8192 ** 3 / best / 1e9
+    try:
+        ai = torch.randint(-127, 128, (8192, 8192), device="cuda", dtype=torch.int8)
+        bi = torch.randint(-127, 128, (8192, 8192), device="cuda", dtype=torch.int8).t()
+        best = min(_time_cuda(lambda: torch._int_mm(ai, bi), 1, warm=1) for _ in range(10))
+        out["int8_tops"] = 2 * 8192 ** 3 / best / 1e9
+    except Exception as exc:  # library path unavailable: leave the peak out rather than guess
+        out["int8_tops"] = None
+        out["int8_error"] = str(exc)[:120]
+    return out
+
+
+def ternary_sections(peaks):
+    """Baseline configs 5 (prefill GEMM M=8192, K=8192, N=28672) and 3 (decode GEMV N=11008, K=4096, M in 1/8/32)."""
+    import ctypes
+    from tmq_b200 import _lib, ops
+    L = _lib.lib()
+    res = {}
+    lib_peaks = measure_tensor_peaks()
+    res["library_peaks_this_run"] = lib_peaks
+    # ---- config 5
+    M, K, N = 8192, 8192, 28672
+    P = _ternary_packed(ops, N, K, 0)
+    scale = torch.rand(N, device="cuda") * 0.09 + 0.01
+    X = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    wt = ops.prepack(P, N, ops.FMT_BF16)
+    ms = _time_cuda(lambda: ops.ternary_gemm(X, wt, N, scale), 10)
+    ops.check_gemm_status()
+    tf = 2 * M * N * K / ms / 1e9
+    res["gemm_bf16_M8192_K8192_N28672"] = {"ms": ms, "tops_equiv": tf, "peak": peaks["bf16_tflops"],
+                                           "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
+                                           "frac_of_library_bf16_this_run": tf / lib_peaks["bf16_tflops"]}
+    del wt, X
+    X8 = torch.randint(-127, 128, (M, K), device="cuda", dtype=torch.int8)
+    wt8 = ops.prepack(P, N, ops.FMT_I8)
+    ms = _time_cuda(lambda: ops.ternary_gemm_i8(X8, wt8, N), 10)
+    ops.check_gemm_status()
+    tf = 2 * M * N * K / ms / 1e9
+    res["gemm_i8_M8192_K8192_N28672"] = {"ms": ms, "tops_equiv": tf, "library_int8_peak_this_run": lib_peaks["int8_tops"],
+                                         "frac_of_library_int8_this_run": (tf / lib_peaks["int8_tops"])
+                                         if lib_peaks["int8_tops"] else None,
+                                         "frac_of_nominal_4500": tf / 4500.0}
+    del wt8, X8, P
+    # ---- config 3: 32 distinct matrices (352 MB > L2) back to back in one CUDA graph
+    N, K, NM = 11008, 4096, 32
+    wts = []
+    for i in range(NM):
+        wts.append(ops.prepack(_ternary_packed(ops, N, K, 100 + i), N, ops.FMT_BF16))
+    scale = torch.rand(N, device="cuda") * 0.09 + 0.01
+    for Mg in (1, 8, 32):
+        X = torch.randn(Mg, K, device="cuda").to(torch.bfloat16)
+        Y = torch.empty(Mg, N, device="cuda", dtype=torch.bfloat16)
+        stream = torch.cuda.Stream()
+
+        def run(i, st):
+            for m0 in range(0, Mg, 8):
+                rc = L.tmq_ternary_gemv_bf16(X.data_ptr() + m0 * K * 2, wts[i].data_ptr(), scale.data_ptr(), None,
+                                             Y.data_ptr() + m0 * N * 2, min(8, Mg - m0), N, K, N, 0, st)
+                assert rc == 0
+        with torch.cuda.stream(stream):
+            for i in range(NM):
+                run(i, stream.cuda_stream)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(NM):
+                    run(i, stream.cuda_stream)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(10):
+                graph.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / 10 / NM * 1e3
+        nbytes = N * K // 4 + 2 * Mg * K + 2 * Mg * N + 4 * N
+        res[f"gemv_bf16_M{Mg}_N11008_K4096"] = {"us_per_matrix": us, "gbs": nbytes / us / 1e3,
+                                               "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"],
+                                               "tops_equiv": 2 * Mg * N * K / us / 1e6, "algorithmic_bytes": nbytes,
+                                               "protocol": "32 distinct matrices in one CUDA graph, time/32"}
+    return res
 
 
 def main():
@@ -279,6 +396,7 @@ def main():
     ap.add_argument("--n", type=int, default=1 << 26, help="elements per GPU (default: the baseline's 2^26)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the ternary GEMM / GEMV sections")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
