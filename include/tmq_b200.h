@@ -142,6 +142,9 @@ int tmq_unpack2b_f32(const uint32_t *P, float *W, int64_t N, int64_t K, void *st
  * activation type (fmt 0: bf16 activations, fmt 1: int8 activations).  tmq_prepack_words gives the word count.
  * ------------------------------------------------------------------------------------------------ */
 size_t tmq_prepack_words(int64_t N, int64_t K);
+/* fmt 2 / 3: the same words as fmt 0 / 1 stored tile-contiguously, Wt[tile][k-block][128 rows][words], rows padded
+ * to whole 128-channel tiles; this is what the skinny tensor-core kernel (tmq_ternary_gemv_tc_*) streams. */
+size_t tmq_prepack_tiled_words(int64_t N, int64_t K, int fmt);
 int tmq_prepack(const uint32_t *P, uint32_t *Wt, int64_t N, int64_t K, int fmt, void *stream);
 
 /* X: bf16 [M][K] row-major, K % 8 == 0, 16-byte aligned.  Y: bf16 (out_f32 = 0) or fp32 (out_f32 = 1) [M][ldy].
@@ -160,6 +163,19 @@ int tmq_ternary_gemv_bf16(const void *X, const uint32_t *Wt, const float *scale,
                           int64_t N, int64_t K, int64_t ldy, int out_f32, void *stream);
 int tmq_ternary_gemv_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
                         void *stream);
+
+/* Skinny form on the tensor cores for 1..32 activation rows: split-K over ~4 CTAs per SM, all of a CTA's packed
+ * weight bytes in flight at once (TMA ring), decode in shared memory, tcgen05.mma with N = 16 / 32, deterministic
+ * in-kernel reduction of the split partials.  `workspace`: tmq_gemv_workspace_bytes(M, N, K) bytes of device memory,
+ * 256-byte aligned, zero-filled once before first use (the kernel re-arms it); calls sharing it must be ordered.
+ * `status` as for tmq_ternary_gemm_bf16.  Wt is the TILED prepack (fmt 2 for bf16, fmt 3 for int8 activations).
+ * replaces: ternary_mvm_cuda, tmq/tmq_cuda.cu:563-603 (kernel :242-286). */
+size_t tmq_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int tmq_ternary_gemv_tc_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int64_t M,
+                             int64_t N, int64_t K, int64_t ldy, int out_f32, void *workspace, size_t workspace_bytes,
+                             int *status, void *stream);
+int tmq_ternary_gemv_tc_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
+                           void *workspace, size_t workspace_bytes, int *status, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Entropy-coded storage of packed weights (HOST pointers; sequential range coder, no GPU work).  Streams are

@@ -26,20 +26,21 @@ SHAPES = [(1, 128, 64), (8, 128, 64), (32, 256, 128), (33, 200, 192), (64, 128, 
           (129, 128, 64), (256, 256, 1024), (300, 520, 576), (512, 1000, 2304)]
 
 
-PATHS = ["tiles", "gemv"]
+PATHS = ["tiles", "gemv", "tc"]
 
 
 @pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_gemm_i8_exact(ops, M, N, K, path):
-    if path == "gemv" and M > 40:
-        pytest.skip("the streaming kernel is meant for skinny problems")
+    if (path == "gemv" and M > 40) or (path == "tc" and M > 32):
+        pytest.skip("the streaming kernels are meant for skinny problems")
     K = (K + 15) // 16 * 16
     W, P = make_weights(N, K, M * 7 + N)
     rng = np.random.default_rng(K)
     X = rng.integers(-127, 128, (M, K)).astype(np.int8)
     wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_I8)
-    Y = ops.ternary_gemm_i8(torch.from_numpy(X).cuda(), wt, N, path=path)
+    wtt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_I8_TILED)
+    Y = ops.ternary_gemm_i8(torch.from_numpy(X).cuda(), wt, N, path=path, wt_tiled=wtt)
     ops.check_gemm_status()
     assert np.array_equal(Y.cpu().numpy(), T.gemm_i8_fast(X, P, N))
 
@@ -47,8 +48,8 @@ def test_gemm_i8_exact(ops, M, N, K, path):
 @pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_gemm_bf16_tolerance(ops, M, N, K, path):
-    if path == "gemv" and M > 40:
-        pytest.skip("the streaming kernel is meant for skinny problems")
+    if (path == "gemv" and M > 40) or (path == "tc" and M > 32):
+        pytest.skip("the streaming kernels are meant for skinny problems")
     K = (K + 7) // 8 * 8
     W, P = make_weights(N, K, M * 11 + N)
     gen = torch.Generator().manual_seed(K)
@@ -56,16 +57,17 @@ def test_gemm_bf16_tolerance(ops, M, N, K, path):
     scale = (torch.rand(N, generator=gen) * 0.09 + 0.01)
     bias = torch.randn(N, generator=gen)
     wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16)
+    wtt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16_TILED)
     ref_acc = T.gemm_f64_fast(X.float().numpy(), P, N)                       # exact sum of exact products
     ref = ref_acc * scale.double().numpy()[None, :] + bias.double().numpy()[None, :]
-    y32 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.float32, path=path)
+    y32 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.float32, path=path, wt_tiled=wtt)
     ops.check_gemm_status()
     got = y32.cpu().double().numpy()
     rms = np.sqrt((ref ** 2).mean(axis=1, keepdims=True))
     assert np.all(np.abs(got - ref) <= 1e-3 * np.maximum(np.abs(ref), rms)), np.abs(got - ref).max()
     # in practice fp32 accumulation of exact products is far tighter than the 1e-3 bar
     assert np.all(np.abs(got - ref) <= 1e-5 * np.maximum(np.abs(ref), rms))
-    y16 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.bfloat16, path=path)
+    y16 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.bfloat16, path=path, wt_tiled=wtt)
     ops.check_gemm_status()
     want16 = torch.from_numpy(ref).to(torch.bfloat16).float().numpy()
     ulp = np.abs(want16) * 2.0 ** -7                     # one bf16 ulp, plus the fp32 accumulation slack near zero
@@ -121,13 +123,17 @@ def test_gemv_baseline_shape(ops, M):
     X = torch.randn(M, K, generator=gen).to(torch.bfloat16)
     scale = torch.rand(N, generator=gen) * 0.09 + 0.01
     ref = T.gemm_f64_fast(X.float().numpy(), P, N) * scale.double().numpy()[None, :]
-    y = ops.ternary_gemm(X.cuda(), ops.prepack(Pd, N, ops.FMT_BF16), N, scale.cuda(), out_dtype=torch.float32)
+    wt, wtt = ops.prepack(Pd, N, ops.FMT_BF16), ops.prepack(Pd, N, ops.FMT_BF16_TILED)
+    y = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), out_dtype=torch.float32, wt_tiled=wtt)
     rms = np.sqrt((ref ** 2).mean(axis=1, keepdims=True))
     assert np.all(np.abs(y.cpu().double().numpy() - ref) <= 1e-3 * np.maximum(np.abs(ref), rms))
     assert np.all(np.abs(y.cpu().double().numpy() - ref) <= 1e-5 * np.maximum(np.abs(ref), rms))
     X8 = torch.randint(-127, 128, (M, K), generator=gen, dtype=torch.int8)
-    y8 = ops.ternary_gemm_i8(X8.cuda(), ops.prepack(Pd, N, ops.FMT_I8), N)
+    y8 = ops.ternary_gemm_i8(X8.cuda(), ops.prepack(Pd, N, ops.FMT_I8), N, wt_tiled=ops.prepack(Pd, N, ops.FMT_I8_TILED))
     assert np.array_equal(y8.cpu().numpy(), T.gemm_i8_fast(X8.numpy(), P, N))
     # deterministic: same bits on a second run
-    y2 = ops.ternary_gemm(X.cuda(), ops.prepack(Pd, N, ops.FMT_BF16), N, scale.cuda(), out_dtype=torch.float32)
+    y2 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), out_dtype=torch.float32, wt_tiled=wtt)
+    for pth in ("gemv", "tiles"):
+        yo = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), out_dtype=torch.float32, path=pth)
+        assert np.all(np.abs(yo.cpu().double().numpy() - ref) <= 1e-5 * np.maximum(np.abs(ref), rms)), pth
     assert torch.equal(y, y2)

@@ -48,12 +48,18 @@ _SIGNATURES = {
     "tmq_rc_encode": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_size_t, ctypes.POINTER(c_size_t)]),
     "tmq_rc_decode": (c_int, [c_void_p, c_size_t, c_void_p, c_int64, c_int64]),
     "tmq_prepack_words": (c_size_t, [c_int64, c_int64]),
+    "tmq_prepack_tiled_words": (c_size_t, [c_int64, c_int64, c_int]),
     "tmq_prepack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "tmq_ternary_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                       c_int64, c_int, c_void_p, c_void_p]),
     "tmq_ternary_gemv_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                       c_int64, c_int, c_void_p]),
     "tmq_ternary_gemv_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "tmq_gemv_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "tmq_ternary_gemv_tc_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                         c_int64, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "tmq_ternary_gemv_tc_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
+                                       c_size_t, c_void_p, c_void_p]),
     "tmq_ternary_gemm_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p]),
 }

@@ -69,6 +69,13 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *m
         : "memory");
 }
 
+// Untiled bulk copy global -> shared of this CTA (both addresses 16-byte aligned, size a multiple of 16 bytes).
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------------- tcgen05 / TMEM
 
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_slot, uint32_t ncols) {  // whole warp

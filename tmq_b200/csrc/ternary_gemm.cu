@@ -26,6 +26,8 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "decode.cuh"
+#include "tma_host.cuh"
 #include "ptx.cuh"
 
 namespace tmq {
@@ -72,26 +74,6 @@ struct SmemLayout {
     static constexpr int BAR_OFF = RAW_OFF + kStages * RAW_BYTES;
     static constexpr int TOTAL = BAR_OFF + 256 + 1024;                       // + barriers + alignment slack
 };
-
-// ---- decode of one packed word ------------------------------------------------------------------------------------
-
-// bf16 format: bits [31-2j:30-2j] = (sign, nonzero) of k = 2j+1, bits [15-2j:14-2j] of k = 2j, j = 0..7.
-// (w << 2j) & 0xC000C000 is then the bf16 pair {k=2j (low half), k=2j+1 (high half)} with values 0 / +2 / -2.
-__device__ __forceinline__ void decode_word_bf16(uint32_t w, uint32_t (&r)[8]) {
-#pragma unroll
-    for (int j = 0; j < 8; j++) r[j] = (w << (2 * j)) & 0xC000C000u;
-}
-
-// int8 format: nibble-spaced reference codes (0 -> 0, 1 -> +1, 2 -> -1); a byte permute with the 4-entry table
-// {0x00, 0x01, 0xFF, 0x00} turns four codes into four int8 values at once.
-__device__ __forceinline__ void decode_word_i8(uint32_t w, uint32_t (&r)[4]) {
-    const uint32_t table = 0x00FF0100u;
-    const uint32_t lo = w & 0x33333333u, hi = (w >> 2) & 0x33333333u;
-    r[0] = __byte_perm(table, 0u, lo);
-    r[1] = __byte_perm(table, 0u, hi);
-    r[2] = __byte_perm(table, 0u, lo >> 16);
-    r[3] = __byte_perm(table, 0u, hi >> 16);
-}
 
 // ---- the kernel -----------------------------------------------------------------------------------------------------
 
@@ -259,63 +241,45 @@ __device__ __forceinline__ uint32_t ref_code(const uint32_t *__restrict__ P, lon
     return (P[k * Q + (n >> 4)] >> (2 * (15 - (int)(n & 15)))) & 3u;
 }
 
+// fmt bit 0: 0 = bf16-ready word, 1 = int8-ready word.  fmt bit 1: 0 = row-major Wt[N][KW], 1 = tile-contiguous
+// Wt[tile][k-block][128 rows][words per row and k-block] (rows beyond N are zero), so that the raw tile of one
+// (128-channel tile, k-block) unit is a single contiguous 2 KB / 4 KB run.
 __global__ void __launch_bounds__(256) prepack_kernel(const uint32_t *__restrict__ P, uint32_t *__restrict__ Wt,
-                                                       long long N, long long K, long long KW, int fmt) {
+                                                       long long N, long long K, long long KW, long long rows_out,
+                                                       int fmt) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= N * KW) return;
+    if (idx >= rows_out * KW) return;
     // consecutive threads take consecutive n for one kw: their reads of P share 32-bit words and rows
-    const long long n = idx % N, kw = idx / N;
+    const long long n = idx % rows_out, kw = idx / rows_out;
     const long long Q = (N + 15) / 16;
+    const int kind = fmt & 1;
     uint32_t word = 0;
+    if (n < N) {
 #pragma unroll
-    for (int i = 0; i < 16; i++) {
-        const uint32_t c = ref_code(P, Q, K, n, kw * 16 + i);  // 0: zero, 1: +1, 2: -1 (3 never produced -> zero)
-        if (fmt == KIND_BF16) {
-            const uint32_t v = (c == 1u) ? 1u : ((c == 2u) ? 3u : 0u);  // (sign, nonzero)
-            const int j = i >> 1;
-            const int pos = (i & 1) ? (30 - 2 * j) : (14 - 2 * j);
-            word |= v << pos;
-        } else {
-            const uint32_t v = (c == 3u) ? 0u : c;
-            const int pos = ((i >> 3) << 4) + ((i & 3) << 2) + (((i >> 2) & 1) << 1);
-            word |= v << pos;
+        for (int i = 0; i < 16; i++) {
+            const uint32_t c = ref_code(P, Q, K, n, kw * 16 + i);  // 0: zero, 1: +1, 2: -1 (3 never produced -> zero)
+            if (kind == KIND_BF16) {
+                const uint32_t v = (c == 1u) ? 1u : ((c == 2u) ? 3u : 0u);  // (sign, nonzero)
+                const int j = i >> 1;
+                const int pos = (i & 1) ? (30 - 2 * j) : (14 - 2 * j);
+                word |= v << pos;
+            } else {
+                const uint32_t v = (c == 3u) ? 0u : c;
+                const int pos = ((i >> 3) << 4) + ((i & 3) << 2) + (((i >> 2) & 1) << 1);
+                word |= v << pos;
+            }
         }
     }
-    Wt[n * KW + kw] = word;
+    if (fmt & 2) {
+        const int wpr = kind == KIND_BF16 ? 4 : 8;  // words per row and k-block
+        const long long tile = n >> 7, row = n & 127, kb = kw / wpr, wi = kw % wpr, nkb = KW / wpr;
+        Wt[((tile * nkb + kb) * 128 + row) * wpr + wi] = word;
+    } else {
+        Wt[n * KW + kw] = word;
+    }
 }
 
 // ---- host side --------------------------------------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-        else
-            (void)cudaGetLastError();
-    });
-    return fn;
-}
-
-static bool make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t outer,
-                        uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
-    EncodeTiledFn fn = encode_tiled();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {pitch_bytes};
-    cuuint32_t box[2] = {box_inner, box_outer};
-    cuuint32_t estr[2] = {1, 1};
-    return fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 template <int KIND, int BN>
 static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
@@ -370,14 +334,23 @@ extern "C" size_t tmq_prepack_words(int64_t N, int64_t K) {
     return (size_t)N * (size_t)(((K + 63) / 64) * 4);
 }
 
+extern "C" size_t tmq_prepack_tiled_words(int64_t N, int64_t K, int fmt) {
+    if (N <= 0 || K <= 0) return 0;
+    const long long tiles = (N + 127) / 128;
+    const long long kw = (fmt & 1) ? ((K + 127) / 128) * 8 : ((K + 63) / 64) * 4;
+    return (size_t)tiles * 128 * (size_t)kw;
+}
+
 extern "C" int tmq_prepack(const uint32_t *P, uint32_t *Wt, int64_t N, int64_t K, int fmt, void *stream) {
-    if (!P || !Wt || N <= 0 || K <= 0 || (fmt != KIND_BF16 && fmt != KIND_I8)) return TMQ_ERR_ARG;
+    if (!P || !Wt || N <= 0 || K <= 0 || fmt < 0 || fmt > 3) return TMQ_ERR_ARG;
     if (!aligned(Wt, 16)) return TMQ_ERR_ALIGN;
-    const long long KW = ((K + 63) / 64) * 4;
-    const long long total = (long long)N * KW;
+    const bool tiled = (fmt & 2) != 0;
+    const long long KW = (tiled && (fmt & 1)) ? ((K + 127) / 128) * 8 : ((K + 63) / 64) * 4;
+    const long long rows_out = tiled ? ((N + 127) / 128) * 128 : N;
+    const long long total = rows_out * KW;
     const long long blocks = (total + 255) / 256;
     if (blocks > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
-    prepack_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(P, Wt, N, K, KW, fmt);
+    prepack_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(P, Wt, N, K, KW, rows_out, fmt);
     return launch_status();
 }
 

@@ -3,21 +3,21 @@
 //
 // Replaces the reference's batch-1 kernel (tmq/tmq_cuda.cu:242-286, launcher :563-603), which reads the packed words
 // with a stride of N/16 words between threads, multiplies by a constant-memory LUT and finishes with shared atomics.
-// Here the 11 MB of packed weights are streamed exactly once with 128-bit coalesced loads, all of a CTA's loads in
-// flight together, and HBM is the only resource that should matter:
+// Here the packed weights are streamed exactly once with 128-bit loads and HBM is the resource that should matter:
 //
-//   * work split: a CTA owns up to 5 groups of 16 output channels and ALL of K; its 16 warps take 256-wide slices
-//     of K (one each for K = 4096, several in turn for larger K).  Lane (g, t) of a warp streams 64 consecutive k of channels g
-//     and g+8 of every group: one 16-byte load per channel and group, every load independent of every other.
-//   * arithmetic: a 2-bit code costs about one integer instruction to decode, which already saturates the issue
+//   * work split: one small CTA (4 warps) per group of 16 output channels, all of K.  Warp w takes the 256-wide
+//     K slices w, w+4, ...; lane (g, t) streams 64 consecutive k of channels g and g+8 per slice, one 16-byte load
+//     each, and issues the loads of four slices (8 loads, all independent) before it consumes any.
+//   * many CTAs are resident per SM and consecutive launches are chained with programmatic dependent launch: a CTA
+//     of launch i+1 starts as soon as an SM slot frees up and issues its weight loads (which depend on nothing)
+//     while launch i is still computing; activations and outputs are only touched after griddepcontrol.wait, i.e.
+//     after the previous kernel in the stream has completed.  A single launch cannot hide its own ramp-up latency
+//     (about as long as streaming an 11 MB matrix takes), a chain of them - which is what decoding is - can.
+//   * arithmetic: a 2-bit code costs about one integer instruction to decode, which already fills half the issue
 //     slots at HBM speed; an fp32 add/sub per weight on top (the CUDA-core formulation) cannot keep up.  The decoded
-//     codes are therefore fed, exact, to warp-level mma (m16n8k16 bf16 / m16n8k32 s8) with the <= 8 activation rows as
-//     the 8 MMA columns and fp32 / int32 accumulation: products with {-1,0,+1} are exact either way.
-//   * the activation slice a lane needs (64 k of row g) lives in registers for the whole CTA lifetime.
+//     codes are fed, exact, to warp-level mma (m16n8k16 bf16 / m16n8k32 s8) with the <= 8 activation rows as the 8
+//     MMA columns and fp32 / int32 accumulation: products with {-1,0,+1} are exact either way.
 //   * the per-warp partial sums are combined through shared memory in a fixed order: deterministic.
-//   * launches are chained with programmatic dependent launch: the CTAs of launch i+1 may start, and issue their
-//     weight loads (which depend on nothing), as soon as SMs free up while launch i drains; activations and outputs
-//     are only touched after griddepcontrol.wait, i.e. after the previous kernel in the stream has completed.
 //
 // Weights use the same prepacked layout as the tensor-core GEMM (tmq_prepack, fmt 0 / 1).
 #include <cuda_bf16.h>
@@ -28,8 +28,8 @@
 
 namespace tmq {
 
-constexpr int kGemvMaxGroups = 5;    // 16-channel groups per CTA
-constexpr int kGemvMaxWarps = 16;    // K slices handled concurrently
+constexpr int kGemvWarps = 4;        // warps per CTA
+constexpr int kGemvBatch = 4;        // K slices a warp has in flight at once
 
 struct GemvArgs {
     const void *X;          // [M][K] bf16 or int8
@@ -37,7 +37,7 @@ struct GemvArgs {
     const float *scale, *bias;
     void *Y;
     long long M, N, K, KW, ldy;
-    int groups_per_cta, nwarps, out_f32;
+    int out_f32;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -65,9 +65,141 @@ __device__ __forceinline__ uint4 ldg_stream(const uint32_t *p) {
 
 // KIND 0: bf16 activations (fmt-0 words), KIND 1: int8 activations (fmt-1 words)
 template <int KIND>
-__global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) ternary_gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(kGemvWarps * 32) ternary_gemv_kernel(const GemvArgs a) {
     using Acc = typename std::conditional<KIND == 0, float, int>::type;
-    __shared__ Acc red[kGemvMaxWarps][kGemvMaxGroups][16][8];  // 40 KB
+    __shared__ Acc red[kGemvWarps][16][8];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next launch may start its own prologue
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const long long r0 = (long long)blockIdx.x * 16 + g, r1 = r0 + 8;  // the two output channels of this lane
+    const uint32_t *w0 = a.Wt + r0 * a.KW, *w1 = a.Wt + r1 * a.KW;
+    const bool ok0 = r0 < a.N, ok1 = r1 < a.N;
+    const int nslices = (int)((a.K + 255) / 256);
+    bool waited = false;
+
+    Acc acc[4] = {0, 0, 0, 0};
+    for (int s0 = warp; s0 < nslices; s0 += kGemvWarps * kGemvBatch) {
+        // ---- weights of up to kGemvBatch slices: every load issued before anything consumes them
+        uint4 wlo[kGemvBatch], whi[kGemvBatch];
+#pragma unroll
+        for (int b = 0; b < kGemvBatch; b++) {
+            const int slice = s0 + b * kGemvWarps;
+            const long long word = ((long long)slice * 256 + 64 * t) >> 4;  // KW is a multiple of 4 words
+            wlo[b] = make_uint4(0, 0, 0, 0);
+            whi[b] = make_uint4(0, 0, 0, 0);
+            if (slice < nslices && word < a.KW) {
+                if (ok0) wlo[b] = ldg_stream(w0 + word);
+                if (ok1) whi[b] = ldg_stream(w1 + word);
+            }
+        }
+        if (!waited) {  // everything above read only the weights, which no kernel of the chain writes
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+        }
+#pragma unroll
+        for (int b = 0; b < kGemvBatch; b++) {
+            const int slice = s0 + b * kGemvWarps;
+            if (slice >= nslices) break;
+            const long long k_lane = (long long)slice * 256 + 64 * t;
+            // ---- activations of row g for these 64 k (zero beyond M or K); K % 8 == 0 (bf16) / K % 16 == 0 (int8)
+            constexpr int XR = (KIND == 0) ? 32 : 16;
+            uint32_t xr[XR];
+#pragma unroll
+            for (int q = 0; q < XR / 4; q++) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                const long long k = k_lane + (long long)q * (KIND == 0 ? 8 : 16);
+                if (g < a.M && k < a.K) {
+                    const char *p = reinterpret_cast<const char *>(a.X) + ((long long)g * a.K + k) * (KIND == 0 ? 2 : 1);
+                    v = __ldg(reinterpret_cast<const uint4 *>(p));
+                }
+                xr[4 * q + 0] = v.x; xr[4 * q + 1] = v.y; xr[4 * q + 2] = v.z; xr[4 * q + 3] = v.w;
+            }
+            const uint32_t lo[4] = {wlo[b].x, wlo[b].y, wlo[b].z, wlo[b].w};
+            const uint32_t hi[4] = {whi[b].x, whi[b].y, whi[b].z, whi[b].w};
+#pragma unroll
+            for (int w = 0; w < 4; w++) {  // word w = k offsets 16w .. 16w+15 of the lane's 64
+                if (KIND == 0) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {  // k offsets 16w+4j .. +3: pairs 2j and 2j+1 of the word
+                        const uint32_t a0 = (lo[w] << (4 * j)) & 0xC000C000u, a2 = (lo[w] << (4 * j + 2)) & 0xC000C000u;
+                        const uint32_t a1 = (hi[w] << (4 * j)) & 0xC000C000u, a3 = (hi[w] << (4 * j + 2)) & 0xC000C000u;
+                        mma_bf16(reinterpret_cast<float(&)[4]>(acc), a0, a1, a2, a3, xr[8 * w + 2 * j], xr[8 * w + 2 * j + 1]);
+                    }
+                } else {
+                    const uint32_t table = 0x00FF0100u;
+                    const uint32_t l0 = lo[w] & 0x33333333u, l1 = (lo[w] >> 2) & 0x33333333u;
+                    const uint32_t h0 = hi[w] & 0x33333333u, h1 = (hi[w] >> 2) & 0x33333333u;
+                    // k 0-3 / 4-7 of the word, then k 8-11 / 12-15
+                    mma_s8(reinterpret_cast<int(&)[4]>(acc), __byte_perm(table, 0u, l0), __byte_perm(table, 0u, h0),
+                           __byte_perm(table, 0u, l1), __byte_perm(table, 0u, h1), xr[4 * w + 0], xr[4 * w + 1]);
+                    mma_s8(reinterpret_cast<int(&)[4]>(acc), __byte_perm(table, 0u, l0 >> 16), __byte_perm(table, 0u, h0 >> 16),
+                           __byte_perm(table, 0u, l1 >> 16), __byte_perm(table, 0u, h1 >> 16), xr[4 * w + 2], xr[4 * w + 3]);
+                }
+            }
+        }
+    }
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // ---- combine the warps' K slices in a fixed order
+    red[warp][g][2 * t] = acc[0];
+    red[warp][g][2 * t + 1] = acc[1];
+    red[warp][g + 8][2 * t] = acc[2];
+    red[warp][g + 8][2 * t + 1] = acc[3];
+    __syncthreads();
+    {
+        const int row = threadIdx.x & 15, col = threadIdx.x >> 4;  // 128 threads = 16 channels x 8 activation rows
+        const long long n = (long long)blockIdx.x * 16 + row;
+        if (n < a.N && col < a.M) {
+            Acc sum = 0;
+#pragma unroll
+            for (int w = 0; w < kGemvWarps; w++) sum += red[w][row][col];
+            if (KIND == 1) {
+                reinterpret_cast<int *>(a.Y)[(long long)col * a.ldy + n] = (int)sum;
+            } else {
+                const float sc = (a.scale ? a.scale[n] : 1.0f) * 0.5f;  // operands carried +-2.0
+                const float f = fmaf((float)sum, sc, a.bias ? a.bias[n] : 0.0f);
+                if (a.out_f32) reinterpret_cast<float *>(a.Y)[(long long)col * a.ldy + n] = f;
+                else reinterpret_cast<__nv_bfloat16 *>(a.Y)[(long long)col * a.ldy + n] = __float2bfloat16_rn(f);
+            }
+        }
+    }
+}
+
+template <int KIND>
+static int launch_gemv(GemvArgs a, cudaStream_t st) {
+    const long long grid = (a.N + 15) / 16;
+    if (grid > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kGemvWarps * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_kernel<KIND>, a));
+}
+
+constexpr int kWideGroups = 5;   // 16-channel groups per CTA of the wide variant
+constexpr int kWideWarps = 16;   // K slices handled concurrently
+
+struct WideArgs {
+    const void *X;
+    const uint32_t *Wt;
+    const float *scale, *bias;
+    void *Y;
+    long long M, N, K, KW, ldy;
+    int groups_per_cta, nwarps, out_f32;
+};
+
+// Wide variant: a CTA of 16 warps owns up to 5 channel groups and all of K; each warp keeps the activations of its
+// 256-wide K slice in registers and reuses them for every group, which cuts the activation reads five-fold.  Measured
+// faster than the small-CTA kernel for bf16 activations (whose 64 activations per lane take 32 registers to fetch).
+template <int KIND>
+__global__ void __launch_bounds__(kWideWarps * 32, 1) ternary_gemv_wide_kernel(const WideArgs a) {
+    using Acc = typename std::conditional<KIND == 0, float, int>::type;
+    __shared__ Acc red[kWideWarps][kWideGroups][16][8];  // 40 KB
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next launch may start its own prologue
     bool waited = false;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -76,9 +208,9 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) ternary_gemv_kernel(con
     const long long group0 = (long long)blockIdx.x * G;
     const long long ngroups = (a.N + 15) / 16;
 
-    Acc acc[kGemvMaxGroups][4];
+    Acc acc[kWideGroups][4];
 #pragma unroll
-    for (int i = 0; i < kGemvMaxGroups; i++)
+    for (int i = 0; i < kWideGroups; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0;
 
@@ -86,10 +218,10 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) ternary_gemv_kernel(con
     for (long long slice = warp; slice < nslices; slice += a.nwarps) {
         const long long k_lane = slice * 256 + 64 * t;  // first k of this lane
         // ---- weights: issue every load of this slice before anything consumes them
-        uint4 wlo[kGemvMaxGroups], whi[kGemvMaxGroups];
+        uint4 wlo[kWideGroups], whi[kWideGroups];
         const bool k_ok = (k_lane >> 4) < a.KW;  // KW is a multiple of 4 words: a lane's 4 words are all in or all out
 #pragma unroll
-        for (int i = 0; i < kGemvMaxGroups; i++) {
+        for (int i = 0; i < kWideGroups; i++) {
             wlo[i] = make_uint4(0, 0, 0, 0);
             whi[i] = make_uint4(0, 0, 0, 0);
             if (i < G && group0 + i < ngroups && k_ok) {
@@ -117,7 +249,7 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) ternary_gemv_kernel(con
         }
         // ---- decode + MMA
 #pragma unroll
-        for (int i = 0; i < kGemvMaxGroups; i++) {
+        for (int i = 0; i < kWideGroups; i++) {
             if (i < G) {
                 const uint32_t lo[4] = {wlo[i].x, wlo[i].y, wlo[i].z, wlo[i].w};
                 const uint32_t hi[4] = {whi[i].x, whi[i].y, whi[i].z, whi[i].w};
@@ -149,7 +281,7 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) ternary_gemv_kernel(con
     if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
     // ---- combine the K slices: fixed order over warps
 #pragma unroll
-    for (int i = 0; i < kGemvMaxGroups; i++) {
+    for (int i = 0; i < kWideGroups; i++) {
         if (i < G) {
             red[warp][i][g][2 * t] = acc[i][0];
             red[warp][i][g][2 * t + 1] = acc[i][1];
@@ -177,16 +309,16 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32, 1) ternary_gemv_kernel(con
 }
 
 template <int KIND>
-static int launch_gemv(GemvArgs a, cudaStream_t st) {
+static int launch_gemv_wide(WideArgs a, cudaStream_t st) {
     const long long ngroups = (a.N + 15) / 16;
     long long G = (ngroups + kNumSMs - 1) / kNumSMs;
-    if (G > kGemvMaxGroups) G = kGemvMaxGroups;
+    if (G > kWideGroups) G = kWideGroups;
     if (G < 1) G = 1;
     const long long grid = (ngroups + G - 1) / G;
     if (grid > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
     long long nslices = (a.K + 255) / 256;
     a.groups_per_cta = (int)G;
-    a.nwarps = (int)(nslices < kGemvMaxWarps ? nslices : kGemvMaxWarps);
+    a.nwarps = (int)(nslices < kWideWarps ? nslices : kWideWarps);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3((unsigned)(a.nwarps * 32));
@@ -197,7 +329,7 @@ static int launch_gemv(GemvArgs a, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_kernel<KIND>, a));
+    return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_wide_kernel<KIND>, a));
 }
 
 static int check_gemv(const void *X, const uint32_t *Wt, const void *Y, long long M, long long N, long long K,
@@ -217,14 +349,14 @@ extern "C" int tmq_ternary_gemv_bf16(const void *X, const uint32_t *Wt, const fl
                                      int64_t M, int64_t N, int64_t K, int64_t ldy, int out_f32, void *stream) {
     int rc = check_gemv(X, Wt, Y, M, N, K, ldy, 2);
     if (rc != TMQ_OK) return rc;
-    GemvArgs a = {X, Wt, scale, bias, Y, M, N, K, ((K + 63) / 64) * 4, ldy, 0, 0, out_f32};
-    return launch_gemv<0>(a, (cudaStream_t)stream);
+    WideArgs a = {X, Wt, scale, bias, Y, M, N, K, ((K + 63) / 64) * 4, ldy, 0, 0, out_f32};
+    return launch_gemv_wide<0>(a, (cudaStream_t)stream);
 }
 
 extern "C" int tmq_ternary_gemv_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K,
                                    int64_t ldy, void *stream) {
     int rc = check_gemv(X, Wt, Y, M, N, K, ldy, 1);
     if (rc != TMQ_OK) return rc;
-    GemvArgs a = {X, Wt, nullptr, nullptr, Y, M, N, K, ((K + 63) / 64) * 4, ldy, 0, 0, 0};
+    GemvArgs a = {X, Wt, nullptr, nullptr, Y, M, N, K, ((K + 63) / 64) * 4, ldy, 0};
     return launch_gemv<1>(a, (cudaStream_t)stream);
 }

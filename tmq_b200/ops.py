@@ -266,7 +266,8 @@ def expand_ternary(packed, orig_shape, entropy_decode=False):
 # ------------------------------------------------------------------------------------------------ ternary GEMM
 
 FMT_BF16, FMT_I8 = 0, 1
-GEMV_MAX_ROWS = 32        # up to here the streaming GEMV kernel (8 rows per pass) beats the tiled tensor-core kernel
+FMT_BF16_TILED, FMT_I8_TILED = 2, 3     # tile-contiguous storage for the skinny tensor-core kernel
+GEMV_MAX_ROWS = 32        # up to here the split-K streaming kernel is used instead of the tiled one
 _status = {}
 
 
@@ -290,6 +291,20 @@ def check_gemm_status(device="cuda"):
                             f"{lib().tmq_status_string(code).decode()}")
 
 
+_gemv_ws = {}
+
+
+def gemv_workspace(device, nbytes):
+    """Per-device workspace of the split-K GEMV kernel (zeroed when created; the kernel re-arms it)."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _gemv_ws.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(int(nbytes), dtype=torch.uint8, device=device)
+        _gemv_ws[key] = buf
+    return buf
+
+
 def prepack(packed, columns, fmt=FMT_BF16):
     """Reference-layout packed weights int32 [K, ceil(N/16)] (or the 4-D conv form) -> prepacked int32 [N, Kp/16]
     in the bit order the GEMM kernels decode (fmt: FMT_BF16 or FMT_I8).  Done once per weight tensor."""
@@ -299,17 +314,40 @@ def prepack(packed, columns, fmt=FMT_BF16):
     Q = (N + 15) // 16
     p = packed.contiguous().view(-1, Q)
     K = p.shape[0]
-    words = lib().tmq_prepack_words(N, K)
-    out = torch.empty((N, words // N), dtype=torch.int32, device=p.device)
+    if fmt in (FMT_BF16_TILED, FMT_I8_TILED):
+        out = torch.empty(lib().tmq_prepack_tiled_words(N, K, int(fmt)), dtype=torch.int32, device=p.device)
+    else:
+        words = lib().tmq_prepack_words(N, K)
+        out = torch.empty((N, words // N), dtype=torch.int32, device=p.device)
     with torch.cuda.device(p.device):
         check(lib().tmq_prepack(_ptr(p), _ptr(out), N, K, int(fmt), _stream(p)), "prepack")
     return out
 
 
-def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16, path="auto"):
-    """Y = scale * (x @ T^T) + bias with x bf16 [M, K] and prepacked weights wt (FMT_BF16); fp32 accumulation on the
-    tensor cores; Y is bf16 or fp32 [M, N].  path: "auto" (GEMV kernel up to GEMV_MAX_ROWS rows, tiled tcgen05 kernel
-    above), or "gemv" / "tiles" to pin one."""
+def _pick_path(path, M, have_tiled):
+    if path != "auto":
+        return path
+    if M <= GEMV_MAX_ROWS and have_tiled:
+        return "tc"
+    if M <= 8:
+        return "gemv"
+    return "tiles"
+
+
+def _check_weights(name, wt, N, K, wt_tiled, fmt_tiled):
+    if wt is not None and (wt.dtype != torch.int32 or wt.dim() != 2 or wt.shape[0] != N
+                           or wt.shape[1] != (K + 63) // 64 * 4):
+        raise RuntimeError(f"{name}: prepacked weights do not match the problem shape")
+    if wt_tiled is not None and (wt_tiled.dtype != torch.int32
+                                 or wt_tiled.numel() != lib().tmq_prepack_tiled_words(N, K, fmt_tiled)):
+        raise RuntimeError(f"{name}: tiled prepacked weights do not match the problem shape")
+
+
+def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16, path="auto", wt_tiled=None):
+    """Y = scale * (x @ T^T) + bias with x bf16 [M, K]; fp32 accumulation; Y is bf16 or fp32 [M, N].
+    wt: prepack(..., FMT_BF16); wt_tiled: prepack(..., FMT_BF16_TILED), needed by the skinny tensor-core kernel.
+    path: "auto", or pin "tiles" (tiled tcgen05 GEMM), "tc" (persistent split-K tcgen05 kernel, M <= 32, tiled
+    weights) or "gemv" (warp-level MMA streaming kernel, 8 rows per pass)."""
     if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 2:
         raise RuntimeError("ternary_gemm: expected a 2-D CUDA bf16 activation tensor")
     if out_dtype not in (torch.bfloat16, torch.float32):
@@ -317,54 +355,71 @@ def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16
     x = x.contiguous()
     M, K = x.shape
     N = int(columns)
-    if wt.dtype != torch.int32 or wt.shape[0] != N or wt.shape[1] != (K + 63) // 64 * 4:
-        raise RuntimeError("ternary_gemm: prepacked weights do not match the problem shape")
+    _check_weights("ternary_gemm", wt, N, K, wt_tiled, FMT_BF16_TILED)
     y = torch.empty((M, N), dtype=out_dtype, device=x.device)
     if M == 0:
         return y
     sc = None if scale is None else scale.to(device=x.device, dtype=torch.float32).contiguous()
     bi = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
-    if path == "gemv" or (path == "auto" and M <= GEMV_MAX_ROWS):
-        # decode-like shapes: the streaming kernel, 8 activation rows per pass
-        esz = y.element_size()
-        with torch.cuda.device(x.device):
-            for m0 in range(0, M, 8):
-                rows = min(8, M - m0)
-                check(lib().tmq_ternary_gemv_bf16(ctypes.c_void_p(x.data_ptr() + m0 * K * 2), _ptr(wt),
-                                                  _ptr(sc) if sc is not None else None,
-                                                  _ptr(bi) if bi is not None else None,
-                                                  ctypes.c_void_p(y.data_ptr() + m0 * N * esz), rows, N, K, N,
-                                                  1 if out_dtype == torch.float32 else 0, _stream(x)), "ternary_gemv")
-        return y
-    st = gemm_status_word(x.device)
+    psc, pbi = (_ptr(sc) if sc is not None else None), (_ptr(bi) if bi is not None else None)
+    f32 = 1 if out_dtype == torch.float32 else 0
+    path = _pick_path(path, M, wt_tiled is not None)
+    if path != "tc" and wt is None:
+        raise RuntimeError("ternary_gemm: this path needs the row-major prepacked weights")
     with torch.cuda.device(x.device):
-        check(lib().tmq_ternary_gemm_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
-                                          _ptr(bi) if bi is not None else None, _ptr(y), M, N, K, N,
-                                          1 if out_dtype == torch.float32 else 0, _ptr(st), _stream(x)), "ternary_gemm")
+        if path == "tc":
+            if wt_tiled is None or M > GEMV_MAX_ROWS:
+                raise RuntimeError("ternary_gemm: the skinny tensor-core path needs tiled weights and M <= 32")
+            ws = gemv_workspace(x.device, lib().tmq_gemv_workspace_bytes(M, N, K))
+            st = gemm_status_word(x.device)
+            check(lib().tmq_ternary_gemv_tc_bf16(_ptr(x), _ptr(wt_tiled), psc, pbi, _ptr(y), M, N, K, N, f32, _ptr(ws),
+                                                 ws.numel(), _ptr(st), _stream(x)), "ternary_gemv_tc")
+        elif path == "gemv":
+            esz = y.element_size()
+            for m0 in range(0, M, 8):
+                check(lib().tmq_ternary_gemv_bf16(ctypes.c_void_p(x.data_ptr() + m0 * K * 2), _ptr(wt), psc, pbi,
+                                                  ctypes.c_void_p(y.data_ptr() + m0 * N * esz), min(8, M - m0), N, K, N,
+                                                  f32, _stream(x)), "ternary_gemv")
+        elif path == "tiles":
+            st = gemm_status_word(x.device)
+            check(lib().tmq_ternary_gemm_bf16(_ptr(x), _ptr(wt), psc, pbi, _ptr(y), M, N, K, N, f32, _ptr(st),
+                                              _stream(x)), "ternary_gemm")
+        else:
+            raise ValueError(f"ternary_gemm: unknown path {path!r}")
     return y
 
 
-def ternary_gemm_i8(x, wt, columns, path="auto"):
-    """Exact int32 Y = x @ T^T with x int8 [M, K] and prepacked weights wt (FMT_I8)."""
+def ternary_gemm_i8(x, wt, columns, path="auto", wt_tiled=None):
+    """Exact int32 Y = x @ T^T with x int8 [M, K]; wt: prepack(..., FMT_I8), wt_tiled: prepack(..., FMT_I8_TILED)."""
     if x.dtype != torch.int8 or x.device.type != "cuda" or x.dim() != 2:
         raise RuntimeError("ternary_gemm_i8: expected a 2-D CUDA int8 activation tensor")
     x = x.contiguous()
     M, K = x.shape
     N = int(columns)
-    if wt.dtype != torch.int32 or wt.shape[0] != N or wt.shape[1] != (K + 63) // 64 * 4:
-        raise RuntimeError("ternary_gemm_i8: prepacked weights do not match the problem shape")
+    _check_weights("ternary_gemm_i8", wt, N, K, wt_tiled, FMT_I8_TILED)
     y = torch.empty((M, N), dtype=torch.int32, device=x.device)
     if M == 0:
         return y
-    if path == "gemv" or (path == "auto" and M <= GEMV_MAX_ROWS):
-        with torch.cuda.device(x.device):
-            for m0 in range(0, M, 8):
-                rows = min(8, M - m0)
-                check(lib().tmq_ternary_gemv_i8(ctypes.c_void_p(x.data_ptr() + m0 * K), _ptr(wt),
-                                                ctypes.c_void_p(y.data_ptr() + m0 * N * 4), rows, N, K, N, _stream(x)),
-                      "ternary_gemv_i8")
-        return y
-    st = gemm_status_word(x.device)
+    path = _pick_path(path, M, wt_tiled is not None)
+    if path != "tc" and wt is None:
+        raise RuntimeError("ternary_gemm_i8: this path needs the row-major prepacked weights")
     with torch.cuda.device(x.device):
-        check(lib().tmq_ternary_gemm_i8(_ptr(x), _ptr(wt), _ptr(y), M, N, K, N, _ptr(st), _stream(x)), "ternary_gemm_i8")
+        if path == "tc":
+            if wt_tiled is None or M > GEMV_MAX_ROWS:
+                raise RuntimeError("ternary_gemm_i8: the skinny tensor-core path needs tiled weights and M <= 32")
+            ws = gemv_workspace(x.device, lib().tmq_gemv_workspace_bytes(M, N, K))
+            st = gemm_status_word(x.device)
+            check(lib().tmq_ternary_gemv_tc_i8(_ptr(x), _ptr(wt_tiled), _ptr(y), M, N, K, N, _ptr(ws), ws.numel(),
+                                               _ptr(st), _stream(x)), "ternary_gemv_tc_i8")
+        elif path == "gemv":
+            for m0 in range(0, M, 8):
+                check(lib().tmq_ternary_gemv_i8(ctypes.c_void_p(x.data_ptr() + m0 * K), _ptr(wt),
+                                                ctypes.c_void_p(y.data_ptr() + m0 * N * 4), min(8, M - m0), N, K, N,
+                                                _stream(x)), "ternary_gemv_i8")
+        elif path == "tiles":
+            st = gemm_status_word(x.device)
+            check(lib().tmq_ternary_gemm_i8(_ptr(x), _ptr(wt), _ptr(y), M, N, K, N, _ptr(st), _stream(x)),
+                  "ternary_gemm_i8")
+        else:
+            raise ValueError(f"ternary_gemm_i8: unknown path {path!r}")
     return y
