@@ -177,6 +177,14 @@ int tmq_ternary_gemv_tc_bf16(const void *X, const uint32_t *Wt, const float *sca
 int tmq_ternary_gemv_tc_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
                            void *workspace, size_t workspace_bytes, int *status, void *stream);
 
+/* Ternary Conv2d as an implicit GEMM (no im2col buffer): X bf16 NHWC [B][H][W][C], C % 64 == 0; Wt = fmt-0 prepack of
+ * the packed weight with its K rows reordered to (ky, kx, c); Y bf16 NHWC [B][OH][OW][N] with the output geometry of
+ * F.conv2d; scale / bias per output channel (folded BatchNorm, NULL for none), optional ReLU.
+ * replaces: Conv2d.compact_forward, tmq/tmq.py:822-871 (F.unfold + ternary_mmm_cuda + F.fold). */
+int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int B, int H,
+                            int W, int C, int N, int ky, int kx, int sy, int sx, int py, int px, int dy, int dx, int relu,
+                            int *status, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Entropy-coded storage of packed weights (HOST pointers; sequential range coder, no GPU work).  Streams are
  * byte-identical to the reference's: 26-byte big-endian header + range-coder payload.  P is the packed matrix

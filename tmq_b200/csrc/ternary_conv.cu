@@ -1,0 +1,315 @@
+// Ternary Conv2d from 2-bit packed weights as an IMPLICIT GEMM on tcgen05: no im2col buffer is ever written.
+//   Y[b][oy][ox][n] = act( scale[n] * sum_{ky,kx,c} X[b][oy*s+ky*d-p][ox*s+kx*d-p][c] * T[n][(ky,kx,c)] + bias[n] )
+//
+// Replaces the reference's convolution path (tmq/tmq.py:822-871): F.unfold materialises every patch in fp32
+// (K/C times the input), a CUDA-core GEMM multiplies it (tmq/tmq_cuda.cu:289-427) and F.fold reshapes the result.
+// Here activations are bf16 NHWC, K runs as (ky, kx, c) so that 64 consecutive k of one filter tap are 128
+// contiguous bytes of the input, and the patch rows of a tile are gathered straight into the swizzled operand layout:
+//   * same CTA organisation as the tiled GEMM (ternary_gemm.cu): weights are the 128-row A operand decoded in shared
+//     memory from a TMA-loaded raw tile, output pixels are the N side (BN = 128 or 256), accumulator in TMEM;
+//   * 4 gather warps replace the activation TMA: per k-block each thread issues 16-byte cp.async copies (zero-filled
+//     outside the image = padding) for its rows, then publishes a stage two k-blocks later, once the copies have landed
+//     and a proxy fence has made them visible to the tensor core;
+//   * the epilogue applies the folded-BatchNorm scale / bias and ReLU and writes NHWC, which is exactly the row-major
+//     [pixels][channels] GEMM output.
+// Needs C % 64 == 0 (every ResNet layer but the 3-channel stem).  All mbarrier waits are bounded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "decode.cuh"
+#include "ptx.cuh"
+#include "tma_host.cuh"
+
+namespace tmq {
+
+constexpr int kConvThreads = 320;  // warp 0: weight TMA, warp 1: MMA, warps 2-5: decode + epilogue, warps 6-9: gather
+constexpr int kConvStages = 4;
+constexpr int kConvLag = 2;        // a gathered stage is published this many k-blocks after it was issued
+
+struct ConvArgs {
+    const __nv_bfloat16 *X;
+    const float *scale, *bias;
+    __nv_bfloat16 *Y;
+    int B, H, W, C, OH, OW, N;
+    int ky, kx, sy, sx, py, px, dy, dx;
+    long long M;  // B * OH * OW
+    int relu;
+    int *status;
+};
+
+template <int BN>
+struct ConvSmem {
+    static constexpr int A_BYTES = 128 * 128;
+    static constexpr int B_BYTES = BN * 128;
+    static constexpr int RAW_BYTES = 128 * 16;
+    static constexpr int A_OFF = 0;
+    static constexpr int B_OFF = A_OFF + kConvStages * A_BYTES;
+    static constexpr int RAW_OFF = B_OFF + kConvStages * B_BYTES;
+    static constexpr int BAR_OFF = RAW_OFF + kConvStages * RAW_BYTES;
+    static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void *gsrc, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kConvThreads, 1)
+ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs args) {
+    using L = ConvSmem<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *full_raw = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
+    uint64_t *full_a = full_raw + kConvStages;
+    uint64_t *full_b = full_a + kConvStages;
+    uint64_t *empty = full_b + kConvStages;
+    uint64_t *acc_full = empty + kConvStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long n0 = (long long)blockIdx.x * 128;
+    const long long m0 = (long long)blockIdx.y * BN;
+    const int cpb = args.C / 64;                       // k-blocks per filter tap
+    const int nkb = args.ky * args.kx * cpb;
+    constexpr uint32_t TMEM_COLS = BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kConvStages; s++) {
+            ptx::mbar_init(full_raw + s, 1);
+            ptx::mbar_init(full_a + s, 4);   // one arrival per decode warp
+            ptx::mbar_init(full_b + s, 4);   // one arrival per gather warp
+            ptx::mbar_init(empty + s, 1);
+        }
+        ptx::mbar_init(acc_full, 1);
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_w);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const bool healthy = (*reinterpret_cast<volatile int *>(args.status) == 0);
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- raw packed weights by TMA
+        if (lane == 0 && healthy) {
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % kConvStages;
+                const uint32_t ph = (uint32_t)(kb / kConvStages) & 1u;
+                if (!ptx::mbar_wait(empty + s, ph ^ 1u, args.status)) break;
+                ptx::mbar_arrive_expect_tx(full_raw + s, (uint32_t)L::RAW_BYTES);
+                ptx::tma_load_2d(smem + L::RAW_OFF + s * L::RAW_BYTES, &tmap_w, full_raw + s, kb * 4, (int)n0);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0 && healthy) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; kb++) {
+                const int s = kb % kConvStages;
+                const uint32_t ph = (uint32_t)(kb / kConvStages) & 1u;
+                ok = ptx::mbar_wait(full_a + s, ph, args.status);
+                if (ok) ok = ptx::mbar_wait(full_b + s, ph, args.status);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint64_t a_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::A_OFF + s * L::A_BYTES));
+                const uint64_t b_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES));
+#pragma unroll
+                for (int k4 = 0; k4 < 4; k4++)
+                    ptx::umma_f16(tmem_base, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                ptx::umma_commit(empty + s);
+            }
+            if (ok) ptx::umma_commit(acc_full);
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- decode warps, then epilogue
+        const int row = threadIdx.x - 64;
+        const int sw = row & 7;
+        bool ok = healthy;
+        for (int kb = 0; kb < nkb && ok; kb++) {
+            const int s = kb % kConvStages;
+            const uint32_t ph = (uint32_t)(kb / kConvStages) & 1u;
+            ok = ptx::mbar_wait(full_raw + s, ph, args.status);
+            if (!ok) break;
+            const uint4 p = *reinterpret_cast<const uint4 *>(smem + L::RAW_OFF + s * L::RAW_BYTES + row * 16);
+            uint8_t *arow = smem + L::A_OFF + s * L::A_BYTES + row * 128;
+            const uint32_t words[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+            for (int wi = 0; wi < 4; wi++) {
+                uint32_t r[8];
+                decode_word_bf16(words[wi], r);
+                *reinterpret_cast<uint4 *>(arow + (((2 * wi) ^ sw) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
+                *reinterpret_cast<uint4 *>(arow + (((2 * wi + 1) ^ sw) << 4)) = make_uint4(r[4], r[5], r[6], r[7]);
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(full_a + s);
+        }
+        if (ok) ok = ptx::mbar_wait(acc_full, 0u, args.status);
+        ptx::tc_fence_after_sync();
+        const int quarter = warp & 3;
+        const long long n = n0 + quarter * 32 + lane;
+        const bool n_ok = ok && n < args.N;
+        float sc = 0.5f, bi = 0.0f;                   // operands carried +-2.0
+        if (n_ok) {
+            if (args.scale) sc *= args.scale[n];
+            if (args.bias) bi = args.bias[n];
+        }
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld_x16(lane_addr + (uint32_t)c, v);
+                ptx::tmem_ld_wait();
+                if (n_ok) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const long long m = m0 + c + j;
+                        if (m < args.M) {
+                            float f = fmaf(__uint_as_float(v[j]), sc, bi);
+                            if (args.relu) f = fmaxf(f, 0.0f);
+                            args.Y[m * args.N + n] = __float2bfloat16_rn(f);
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- gather warps: patches -> swizzled B tile
+        const int g = threadIdx.x - 192;              // 0..127
+        constexpr int RPT = BN / 128;                 // rows per thread
+        int rb[RPT], roy[RPT], rox[RPT];
+        bool rvalid[RPT];
+#pragma unroll
+        for (int j = 0; j < RPT; j++) {
+            const long long m = m0 + g + 128 * j;
+            rvalid[j] = m < args.M;
+            const long long mm = rvalid[j] ? m : 0;
+            rb[j] = (int)(mm / ((long long)args.OH * args.OW));
+            const int rem = (int)(mm % ((long long)args.OH * args.OW));
+            roy[j] = (rem / args.OW) * args.sy - args.py;
+            rox[j] = (rem % args.OW) * args.sx - args.px;
+        }
+        bool ok = healthy;
+        int published = 0;
+        for (int kb = 0; kb < nkb && ok; kb++) {
+            const int s = kb % kConvStages;
+            const uint32_t ph = (uint32_t)(kb / kConvStages) & 1u;
+            ok = ptx::mbar_wait(empty + s, ph ^ 1u, args.status);
+            if (!ok) break;
+            const int tap = kb / cpb, c0 = (kb % cpb) * 64;
+            const int fy = (tap / args.kx) * args.dy, fx = (tap % args.kx) * args.dx;
+            const uint32_t bbase = ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES);
+#pragma unroll
+            for (int j = 0; j < RPT; j++) {
+                const int r = g + 128 * j;
+                const int iy = roy[j] + fy, ix = rox[j] + fx;
+                const bool inb = rvalid[j] && iy >= 0 && iy < args.H && ix >= 0 && ix < args.W;
+                const __nv_bfloat16 *src = inb ? args.X + (((long long)rb[j] * args.H + iy) * args.W + ix) * args.C + c0 : args.X;
+                const uint32_t dst = bbase + r * 128;
+                const uint32_t nbytes = inb ? 16u : 0u;  // 0 source bytes = zero fill (padding, rows past the end)
+#pragma unroll
+                for (int c = 0; c < 8; c++) cp_async_16(dst + ((c ^ (r & 7)) << 4), src + c * 8, nbytes);
+            }
+            cp_async_commit();
+            if (kb >= kConvLag) {
+                cp_async_wait<kConvLag>();            // the stage issued kConvLag k-blocks ago has landed
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(full_b + (published % kConvStages));
+                published++;
+            }
+        }
+        if (ok) {
+            // drain: publish what is still in flight, oldest first
+            if (published < nkb - 1) {
+                cp_async_wait<1>();
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(full_b + (published % kConvStages));
+                published++;
+            }
+            cp_async_wait<0>();
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            while (published < nkb) {
+                if (lane == 0) ptx::mbar_arrive(full_b + (published % kConvStages));
+                published++;
+            }
+        } else {
+            cp_async_wait<0>();
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int BN>
+static int launch_conv(const uint32_t *Wt, const ConvArgs &a, long long K, cudaStream_t st) {
+    using L = ConvSmem<BN>;
+    const long long KW = ((K + 63) / 64) * 4;
+    CUtensorMap mw;
+    if (!make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KW * 4, 4, 128,
+                     CU_TENSOR_MAP_SWIZZLE_NONE))
+        return TMQ_ERR_LAUNCH;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(ternary_conv_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    });
+    if (attr_err != cudaSuccess) return cuda_status(attr_err);
+    const long long gy = (a.M + BN - 1) / BN;
+    if (gy > 65535) return TMQ_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)((a.N + 127) / 128), (unsigned)gy);
+    ternary_conv_kernel<BN><<<grid, kConvThreads, L::TOTAL, st>>>(mw, a);
+    return launch_status();
+}
+
+}  // namespace tmq
+
+using namespace tmq;
+
+extern "C" int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y,
+                                       int B, int H, int W, int C, int N, int ky, int kx, int sy, int sx, int py, int px,
+                                       int dy, int dx, int relu, int *status, void *stream) {
+    if (!X || !Wt || !Y || !status) return TMQ_ERR_ARG;
+    if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || N <= 0 || ky <= 0 || kx <= 0 || sy <= 0 || sx <= 0 || py < 0 || px < 0 ||
+        dy <= 0 || dx <= 0)
+        return TMQ_ERR_ARG;
+    if (C % 64 != 0) return TMQ_ERR_UNSUPPORTED;
+    const int OH = (H + 2 * py - dy * (ky - 1) - 1) / sy + 1, OW = (W + 2 * px - dx * (kx - 1) - 1) / sx + 1;
+    if (OH <= 0 || OW <= 0) return TMQ_ERR_ARG;
+    if (!aligned(X, 16) || !aligned(Wt, 16) || !aligned(Y, 2) || !aligned(status, 4)) return TMQ_ERR_ALIGN;
+    ConvArgs a;
+    a.X = reinterpret_cast<const __nv_bfloat16 *>(X);
+    a.scale = scale; a.bias = bias;
+    a.Y = reinterpret_cast<__nv_bfloat16 *>(Y);
+    a.B = B; a.H = H; a.W = W; a.C = C; a.OH = OH; a.OW = OW; a.N = N;
+    a.ky = ky; a.kx = kx; a.sy = sy; a.sx = sx; a.py = py; a.px = px; a.dy = dy; a.dx = dx;
+    a.M = (long long)B * OH * OW;
+    a.relu = relu;
+    a.status = status;
+    const long long K = (long long)ky * kx * C;
+    // 256-pixel tiles when that still fills the GPU, else 128
+    const long long ctas256 = ((a.N + 127) / 128) * ((a.M + 255) / 256);
+    if (ctas256 >= 2 * kNumSMs) return launch_conv<256>(Wt, a, K, (cudaStream_t)stream);
+    return launch_conv<128>(Wt, a, K, (cudaStream_t)stream);
+}

@@ -423,3 +423,31 @@ def ternary_gemm_i8(x, wt, columns, path="auto", wt_tiled=None):
         else:
             raise ValueError(f"ternary_gemm_i8: unknown path {path!r}")
     return y
+HAVE_IMPLICIT_CONV = True
+
+
+def ternary_conv2d_nhwc(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None, bias=None,
+                        relu=False):
+    """Implicit-GEMM convolution: x bf16 NHWC [B, H, W, C] (C % 64 == 0), wt = prepack(FMT_BF16) of the packed weight
+    with rows in (ky, kx, c) order -> bf16 NHWC [B, OH, OW, N]."""
+    if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 4 or not x.is_contiguous():
+        raise RuntimeError("ternary_conv2d_nhwc: expected a contiguous 4-D CUDA bf16 NHWC tensor")
+    b, h, w, c = x.shape
+    (ky, kx), (sy, sx), (py, px), (dy, dx) = kernel, stride, padding, dilation
+    n = int(columns)
+    if c % 64 != 0:
+        raise RuntimeError("ternary_conv2d_nhwc: the channel count must be a multiple of 64")
+    if wt.dtype != torch.int32 or wt.shape[0] != n or wt.shape[1] != (ky * kx * c + 63) // 64 * 4:
+        raise RuntimeError("ternary_conv2d_nhwc: prepacked weights do not match the problem shape")
+    oh = (h + 2 * py - dy * (ky - 1) - 1) // sy + 1
+    ow = (w + 2 * px - dx * (kx - 1) - 1) // sx + 1
+    y = torch.empty((b, oh, ow, n), dtype=torch.bfloat16, device=x.device)
+    sc = None if scale is None else scale.to(device=x.device, dtype=torch.float32).contiguous()
+    bi = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
+    st = gemm_status_word(x.device)
+    with torch.cuda.device(x.device):
+        check(lib().tmq_ternary_conv2d_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
+                                            _ptr(bi) if bi is not None else None, _ptr(y), b, h, w, c, n, ky, kx, sy, sx,
+                                            py, px, dy, dx, 1 if relu else 0, _ptr(st), _stream(x)),
+              "ternary_conv2d_nhwc")
+    return y

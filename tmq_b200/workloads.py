@@ -1,0 +1,156 @@
+"""The ResNet-18 workloads of the baseline configuration, built from the public API only.
+
+  * `build_resnet18(num_classes)`         torchvision ResNet-18 with every conv / fc layer swapped for its TMQ layer,
+                                          fc without bias but with its own BatchNorm (the reference's sample set-up,
+                                          samples/resnet_train.py:344-358)
+  * `qat_step(...)`                       one QAT step: forward, cross-entropy + quantization loss, backward,
+                                          (all-reduce), optimizer, clamp (samples/resnet_train.py:102-160)
+  * `PackedResNet18`                      inference from packed weights: BatchNorm folded into per-channel scale/bias of
+                                          the conv epilogue, bf16 NHWC activations, convolutions as implicit GEMMs
+"""
+import torch
+from torch import nn
+
+from . import dist as tdist
+from . import ops
+from . import tmq as api
+
+
+def build_resnet18(num_classes=101, ctrl=None, max_epochs=50, qpenalty_range=(0.0, 1e-3)):
+    import torchvision
+    model = torchvision.models.resnet18(num_classes=num_classes)
+    if ctrl is None:
+        ctrl = api.QuantizationControl(epoch_knots=api.QuantizationScheduleBuilder.default_schedule(max_epochs),
+                                       qpenalty_range=qpenalty_range)
+    api.quantize_model(model, ctrl)
+    model.fc.disable_bias()
+    model.fc.implicit_bn()
+    return model, ctrl
+
+
+def qat_step(model, ctrl, optimizer, x, y, bucket=None):
+    """One training step on this rank's slice of the batch.  With a FlatGradBucket the gradients are averaged over
+    the ranks with a single all-reduce before the optimizer runs.  Returns (loss, cross-entropy, quantization loss)."""
+    if bucket is not None:
+        bucket.zero()
+    else:
+        optimizer.zero_grad(set_to_none=True)
+    logits = model(x)
+    ce = nn.functional.cross_entropy(logits, y)
+    ql = ctrl.quantization_loss()
+    loss = ce + ql if ql is not None else ce
+    loss.backward()
+    if bucket is not None:
+        bucket.allreduce_mean()
+    optimizer.step()
+    ctrl.clamp()
+    return loss.detach(), ce.detach(), (ql.detach() if ql is not None else None)
+
+
+# ---- packed inference ----------------------------------------------------------------------------------------------------
+
+def _fold_bn(bn, conv_bias=None, post_scale=1.0):
+    """BatchNorm (eval) after a bias-free linear map -> per-channel (scale, bias) of that map's epilogue."""
+    inv = torch.rsqrt(bn.running_var.float() + bn.eps)
+    gamma = bn.weight.float() if bn.weight is not None else torch.ones_like(inv)
+    beta = bn.bias.float() if bn.bias is not None else torch.zeros_like(inv)
+    scale = gamma * inv * post_scale
+    bias = beta - bn.running_mean.float() * gamma * inv
+    if conv_bias is not None:
+        bias = bias + conv_bias.float() * gamma * inv
+    return scale.contiguous(), bias.contiguous()
+
+
+class PackedConv:
+    """A ternary convolution with folded BatchNorm, run from packed weights on bf16 NHWC activations."""
+
+    def __init__(self, layer, bn, relu):
+        assert layer.weight.dtype == torch.int32, "layer must be in compact form (compressed_state_dict)"
+        self.cout, self.cin, self.ky, self.kx = [int(v) for v in layer.original_shape]
+        self.stride, self.padding = api._pair(layer.stride), api._pair(layer.padding)
+        self.dilation = api._pair(layer.dilation)
+        self.relu = relu
+        self.scale, self.bias = _fold_bn(bn, getattr(layer, "bias", None), float(layer.post_scale_imm))
+        packed = layer.weight.data.view(-1, layer.weight.shape[-1])            # rows in (c, ky, kx) order
+        # the implicit GEMM walks K as (ky, kx, c): channel runs are contiguous in NHWC
+        k = torch.arange(self.cin * self.ky * self.kx, device=packed.device)
+        c, rem = k // (self.ky * self.kx), k % (self.ky * self.kx)
+        self.perm_from_ckk = torch.argsort(rem * self.cin + c)                 # new row j <- old row perm[j]
+        self.packed_kkc = packed.index_select(0, self.perm_from_ckk).contiguous()
+        self.K = self.packed_kkc.shape[0]
+        self.implicit = (self.cin % 64 == 0)
+        kpad = (-self.K) % 8
+        p = torch.nn.functional.pad(self.packed_kkc, (0, 0, 0, kpad)) if kpad else self.packed_kkc
+        self.wt = ops.prepack(p, self.cout, ops.FMT_BF16)
+        self.kpad = kpad
+
+    def __call__(self, x_nhwc, residual=None):
+        """x_nhwc: bf16 [B, H, W, C] contiguous -> bf16 [B, OH, OW, Cout]; optional residual added before the ReLU."""
+        b, h, w, c = x_nhwc.shape
+        (sy, sx), (py, px), (dy, dx) = self.stride, self.padding, self.dilation
+        oh = (h + 2 * py - dy * (self.ky - 1) - 1) // sy + 1
+        ow = (w + 2 * px - dx * (self.kx - 1) - 1) // sx + 1
+        if self.implicit and ops.HAVE_IMPLICIT_CONV:
+            y = ops.ternary_conv2d_nhwc(x_nhwc, self.wt, self.cout, (self.ky, self.kx), self.stride, self.padding,
+                                        self.dilation, self.scale, self.bias, relu=self.relu and residual is None)
+            y = y.view(b, oh, ow, self.cout)
+        else:
+            # explicit patches (only the 3-channel stem takes this route): (ky, kx, c) order to match the weights
+            xp = torch.nn.functional.pad(x_nhwc, (0, 0, px, px, py, py))
+            cols = []
+            for iy in range(self.ky):
+                for ix in range(self.kx):
+                    cols.append(xp[:, iy * dy: iy * dy + (oh - 1) * sy + 1: sy, ix * dx: ix * dx + (ow - 1) * sx + 1: sx, :])
+            a = torch.cat(cols, dim=3).reshape(b * oh * ow, self.K)
+            if self.kpad:
+                a = torch.nn.functional.pad(a, (0, self.kpad))
+            y = ops.ternary_gemm(a.contiguous(), self.wt, self.cout, self.scale, self.bias).view(b, oh, ow, self.cout)
+            if self.relu and residual is None:
+                y = torch.relu_(y)
+        if residual is not None:
+            y = y + residual
+            if self.relu:
+                y = torch.relu_(y)
+        return y
+
+
+class PackedResNet18:
+    """ResNet-18 inference from packed ternary weights; input NCHW fp32/bf16 images, output fp32 logits."""
+
+    def __init__(self, model):
+        model.eval()
+        self.conv1 = PackedConv(model.conv1, model.bn1, relu=True)
+        self.blocks = []
+        for stage in (model.layer1, model.layer2, model.layer3, model.layer4):
+            for blk in stage:
+                down = None
+                if blk.downsample is not None:
+                    down = PackedConv(blk.downsample[0], blk.downsample[1], relu=False)
+                self.blocks.append((PackedConv(blk.conv1, blk.bn1, relu=True), PackedConv(blk.conv2, blk.bn2, relu=True),
+                                    down))
+        fc = model.fc
+        assert fc.weight.dtype == torch.int32
+        self.fc_n, self.fc_k = [int(v) for v in fc.original_shape]
+        self.fc_scale, self.fc_bias = _fold_bn(fc.bn, getattr(fc, "bias", None), float(fc.post_scale_imm))
+        packed = fc.weight.data
+        self.fc_wt = ops.prepack(packed, self.fc_n, ops.FMT_BF16)
+
+    @torch.no_grad()
+    def __call__(self, images):
+        x = images.to(torch.bfloat16).permute(0, 2, 3, 1).contiguous()                # NHWC
+        x = self.conv1(x)
+        x = torch.nn.functional.max_pool2d(x.permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1).contiguous()
+        for c1, c2, down in self.blocks:
+            identity = x if down is None else down(x)
+            x = c2(c1(x), residual=identity)
+        pooled = x.float().mean(dim=(1, 2)).to(torch.bfloat16).contiguous()          # [B, 512]
+        return ops.ternary_gemm(pooled, self.fc_wt, self.fc_n, self.fc_scale, self.fc_bias, out_dtype=torch.float32)
+
+
+def shard_batch(x, rank=None, world_size=None):
+    """This rank's contiguous slice of a batch (batch-sharded inference needs no collective)."""
+    r, w = tdist.world()
+    r = r if rank is None else rank
+    w = w if world_size is None else world_size
+    b, e = tdist.shard_range(x.shape[0], r, w)
+    return x[b:e]
