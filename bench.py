@@ -387,6 +387,107 @@ def ternary_sections(peaks):
     return res
 
 
+# ------------------------------------------------------------------------------------------------ other workloads
+
+def _finish(dist, line):
+    print(json.dumps(line), flush=True)
+
+
+def run_workload(args):
+    """Secondary workloads, same launch contract: --workload gemm | resnet_qat | resnet_infer (strong scaling)."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the tmq_b200 kernels have no CPU fallback")
+    dist, rank, local, world = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    from tmq_b200 import dist as tdist
+    from tmq_b200 import ops, workloads
+    import tmq_b200 as tmq
+    peaks, peak_kind = measured_peaks()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step, steps, warmup):
+        for i in range(max(warmup, 3)):
+            step(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            step(i)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
+    if args.workload == "gemm":
+        M, K, N = 8192, 8192, 28672
+        P = _ternary_packed(ops, N, K, 0)                         # same seed on every rank: the same matrix
+        scale = torch.rand(N, generator=torch.Generator(device=dev).manual_seed(1), device=dev) * 0.09 + 0.01
+        X = torch.randn(M, K, generator=torch.Generator(device=dev).manual_seed(2), device=dev).to(torch.bfloat16)
+        lin = tdist.ColumnShardedLinear(P, N, scale, None, rank=rank, world_size=world)
+        del P
+        ms = timed(lambda i: lin(X), args.steps, args.warmup)
+        ops.check_gemm_status(dev)
+        ms_local = _time_cuda(lambda: lin.local(X), max(3, args.steps // 2))
+        value = 2 * M * N * K / ms / 1e9
+        line = {"metric": "ternary_gemm_bf16_TOPS_equiv", "value": value, "unit": "TOPS-equiv", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": "ternary_linear_M8192_K8192_N28672", "sharding": "output columns, 128-aligned, "
+                           "NCCL all-gather of the column blocks", "local_gemm_ms": ms_local,
+                           "l2": "activations + output (604 MB) exceed L2"},
+                "gpu_launches": args.steps,
+                "roofline": {"bound": "tensor", "achieved": 2 * M * (N / world) * K / ms_local / 1e9,
+                             "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                             "frac": 2 * M * (N / world) * K / ms_local / 1e9 / peaks["bf16_tflops"], "traffic": None,
+                             "peak_kind": peak_kind, "kernel": "ternary_gemm_kernel<bf16,256>"}}
+    elif args.workload in ("resnet_qat", "resnet_infer"):
+        batch = 256
+        b0, b1 = tdist.shard_range(batch, rank, world)
+        gen = torch.Generator(device=dev).manual_seed(10 + rank)
+        x = torch.randn(b1 - b0, 3, 224, 224, generator=gen, device=dev)
+        y = torch.randint(0, 101, (b1 - b0,), generator=gen, device=dev)
+        torch.manual_seed(0)
+        if args.workload == "resnet_qat":
+            model, ctrl = workloads.build_resnet18(101)
+            model.to(dev).train()
+            for e in range(1, 45):
+                ctrl.step(e)
+            opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+            bucket = tdist.FlatGradBucket(model.parameters()) if world > 1 else None
+            ms = timed(lambda i: workloads.qat_step(model, ctrl, opt, x, y, bucket), args.steps, args.warmup)
+            metric, sharding = "resnet18_qat_images_per_s", "data parallel, one flat fp32 gradient all-reduce per step"
+        else:
+            model, ctrl = workloads.build_resnet18(101, ctrl=tmq.QuantizationControl())
+            with torch.no_grad():
+                for node in ctrl._registry.values():
+                    u = torch.rand(node.weight.shape)
+                    node.weight.copy_(torch.where(u < 0.35, -1.0, torch.where(u < 0.65, 0.0, 1.0)))
+            model.to(dev).eval()
+            tmq.compressed_state_dict(model)
+            net = workloads.PackedResNet18(model)
+            ms = timed(lambda i: net(x), args.steps, args.warmup)
+            ops.check_gemm_status(dev)
+            metric, sharding = "resnet18_packed_inference_images_per_s", "batch sharded, no collective"
+        line = {"metric": metric, "value": batch / (ms * 1e-3), "unit": "images/s", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f32" if args.workload == "resnet_qat" else "bf16", "data": "synthetic",
+                "config": {"workload": "resnet18_101cls_batch256_224x224", "sharding": sharding,
+                           "macs_per_batch": 4.643e11}}
+    else:
+        raise SystemExit(f"unknown workload {args.workload}")
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -397,9 +498,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-extra", action="store_true", help="skip the ternary GEMM / GEMV sections")
+    ap.add_argument("--workload", default="softstep", choices=["softstep", "gemm", "resnet_qat", "resnet_infer"])
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "softstep":
+        run_workload(args)
     else:
         run_ours(args)
 
