@@ -425,22 +425,47 @@ def run_workload(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()) / steps
 
-    if args.workload == "gemm":
-        M, K, N = 8192, 8192, 28672
+    if args.workload == "gemv":
+        # decode-like config through the C ABI, distinct matrices so that L2 cannot hold them (profiling helper)
+        from tmq_b200 import _lib
+        Lb = _lib.lib()
+        N, K, NM, Mg = 11008, 4096, args.gemv_matrices, args.gemv_rows
+        wts = [ops.prepack(_ternary_packed(ops, N, K, 100 + i), N, ops.FMT_BF16) for i in range(NM)]
+        scale = torch.rand(N, device=dev) * 0.09 + 0.01
+        X = torch.randn(Mg, K, device=dev).to(torch.bfloat16)
+        Y = torch.empty(Mg, N, device=dev, dtype=torch.bfloat16)
+        st = torch.cuda.current_stream().cuda_stream
+
+        def sweep(i):
+            for wt in wts:
+                for m0 in range(0, Mg, 8):
+                    rc = Lb.tmq_ternary_gemv_bf16(X.data_ptr() + m0 * K * 2, wt.data_ptr(), scale.data_ptr(), None,
+                                                  Y.data_ptr() + m0 * N * 2, min(8, Mg - m0), N, K, N, 0, st)
+                    assert rc == 0
+        ms = timed(sweep, args.steps, args.warmup) / NM
+        nbytes = N * K // 4 + 2 * Mg * K + 2 * Mg * N + 4 * N
+        line = {"metric": "ternary_gemv_bf16_GBps", "value": nbytes / ms / 1e6, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"ternary_gemv_M{Mg}_N11008_K4096", "matrices": NM,
+                           "note": "stream launches (no CUDA graph): includes launch gaps; the headline GEMV number is "
+                                   "the graph protocol of the default run"}}
+    elif args.workload == "gemm":
+        M, K, N = args.gemm_m, args.gemm_k, args.gemm_n
         P = _ternary_packed(ops, N, K, 0)                         # same seed on every rank: the same matrix
         scale = torch.rand(N, generator=torch.Generator(device=dev).manual_seed(1), device=dev) * 0.09 + 0.01
         X = torch.randn(M, K, generator=torch.Generator(device=dev).manual_seed(2), device=dev).to(torch.bfloat16)
         lin = tdist.ColumnShardedLinear(P, N, scale, None, rank=rank, world_size=world)
         del P
-        ms = timed(lambda i: lin(X), args.steps, args.warmup)
+        ms = timed(lambda i: lin(X, blocked=True), args.steps, args.warmup)
         ops.check_gemm_status(dev)
         ms_local = _time_cuda(lambda: lin.local(X), max(3, args.steps // 2))
         value = 2 * M * N * K / ms / 1e9
         line = {"metric": "ternary_gemm_bf16_TOPS_equiv", "value": value, "unit": "TOPS-equiv", "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": "ternary_linear_M8192_K8192_N28672", "sharding": "output columns, 128-aligned, "
-                           "NCCL all-gather of the column blocks", "local_gemm_ms": ms_local,
+                "config": {"workload": f"ternary_linear_M{M}_K{K}_N{N}", "sharding": "output columns, 128-aligned, "
+                           "one NCCL all-gather of the column blocks (left blocked: [world, M, N/world])", "local_gemm_ms": ms_local,
                            "l2": "activations + output (604 MB) exceed L2"},
                 "gpu_launches": args.steps,
                 "roofline": {"bound": "tensor", "achieved": 2 * M * (N / world) * K / ms_local / 1e9,
@@ -498,7 +523,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-extra", action="store_true", help="skip the ternary GEMM / GEMV sections")
-    ap.add_argument("--workload", default="softstep", choices=["softstep", "gemm", "resnet_qat", "resnet_infer"])
+    ap.add_argument("--workload", default="softstep", choices=["softstep", "gemm", "gemv", "resnet_qat", "resnet_infer"])
+    ap.add_argument("--gemm-m", type=int, default=8192)
+    ap.add_argument("--gemm-k", type=int, default=8192)
+    ap.add_argument("--gemm-n", type=int, default=28672)
+    ap.add_argument("--gemv-rows", type=int, default=1)
+    ap.add_argument("--gemv-matrices", type=int, default=32)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

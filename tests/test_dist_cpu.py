@@ -81,7 +81,12 @@ def _worker(rank, world, port, out_dir):
         N2 = 512
         W2 = rng.integers(-1, 2, (N2, K)).astype(np.float32)
         lin2 = tdist.ColumnShardedLinear(torch.from_numpy(T.pack(W2)), N2, matmul=_cpu_matmul)
-        ok_cols = ok_cols and torch.allclose(lin2(xs), xs @ torch.from_numpy(W2).T, rtol=1e-6, atol=1e-6)
+        full2 = xs @ torch.from_numpy(W2).T
+        ok_cols = ok_cols and torch.allclose(lin2(xs), full2, rtol=1e-6, atol=1e-6)
+        ok_cols = ok_cols and torch.allclose(lin2(xs, chunks=2), full2, rtol=1e-6, atol=1e-6)      # overlapped variant
+        blocks = lin2(xs, blocked=True)
+        ok_cols = ok_cols and blocks.shape == (world, M, N2 // world) and torch.allclose(
+            blocks.permute(1, 0, 2).reshape(M, N2), full2, rtol=1e-6, atol=1e-6)
         # ---- scalar all-reduce
         s = tdist.allreduce_scalar(torch.tensor(float(rank + 1), dtype=torch.float64))
         ok_scalar = s.item() == sum(range(1, world + 1))

@@ -100,19 +100,40 @@ class ColumnShardedLinear:
         return ops.ternary_gemm(x, self._wt, n, self.scale, self.bias, out_dtype=x.dtype
                                 if x.dtype in (torch.bfloat16, torch.float32) else torch.bfloat16)
 
-    def __call__(self, x, group=None):
-        y_local = self.local(x)
+    def __call__(self, x, group=None, chunks=1, blocked=False):
+        """Full output on every rank.  chunks > 1 splits the rows so that the all-gather of one chunk overlaps the
+        GEMM of the next (equal shards only).  blocked=True returns the column blocks as [world, M, n_shard] without
+        the final interleaving copy (a consumer that walks K in blocks can use them as they are)."""
         if self.world == 1:
-            return y_local
+            y = self.local(x)
+            return y.unsqueeze(0) if blocked else y
         widths = [b[1] - b[0] for b in self.bounds]
         widest = max(widths)
-        send = y_local.contiguous()
+        equal = all(wd == widest for wd in widths)
+        m = x.shape[0]
+        if chunks > 1 and equal and m >= chunks:
+            first = self.local(x[:1])
+            gathered = torch.empty((self.world, m, widest), dtype=first.dtype, device=first.device)
+            edges = [m * i // chunks for i in range(chunks + 1)]
+            works = []
+            for i in range(chunks):
+                r0, r1 = edges[i], edges[i + 1]
+                y_c = self.local(x[r0:r1]).contiguous()
+                stage = torch.empty((self.world * (r1 - r0), widest), dtype=y_c.dtype, device=y_c.device)
+                works.append((dist.all_gather_into_tensor(stage, y_c, group=group, async_op=True), stage, r0, r1))
+            for work, stage, r0, r1 in works:
+                work.wait()
+                gathered[:, r0:r1, :].copy_(stage.view(self.world, r1 - r0, widest))
+            return gathered if blocked else gathered.permute(1, 0, 2).reshape(m, self.n_total)
+        send = self.local(x).contiguous()
         if send.shape[1] != widest:      # collectives want equal shapes: the ragged last shard is padded for the trip
             send = torch.nn.functional.pad(send, (0, widest - send.shape[1]))
         stacked = torch.empty((self.world * send.shape[0], widest), dtype=send.dtype, device=send.device)
         dist.all_gather_into_tensor(stacked, send, group=group)      # rank blocks concatenated along dim 0
         gathered = stacked.view(self.world, send.shape[0], widest)
-        if all(wd == widest for wd in widths):
+        if blocked and equal:
+            return gathered
+        if equal:
             return gathered.permute(1, 0, 2).reshape(send.shape[0], self.n_total)
         return torch.cat([gathered[r, :, :wd] for r, wd in enumerate(widths)], dim=1)
 
