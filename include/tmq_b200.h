@@ -115,6 +115,13 @@ int tmq_mt_clamp(const void *d_plan, int ntensors, int nchunks, float lo, float 
  * *mismatches is a device uint64 the caller zeroes first. */
 int tmq_selftest_const_div(double digamma, unsigned long long *mismatches, void *stream);
 
+/* Device self-check of the range-specialised division used for the data-dependent quotients (denominators in
+ * [16, 8192)): compares it with IEEE division for the denominators number b_begin .. b_begin + b_count - 1 of those nine
+ * binades (9 * 2^23 in all), each against per_b numerators (per_b = 2^23: every mantissa).  *mismatches: device
+ * uint64, zeroed by the caller. */
+int tmq_selftest_div(unsigned per_b, unsigned long long b_begin, unsigned long long b_count,
+                     unsigned long long *mismatches, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Hot path 2a: bit-exact 2-bit packing.  W is [N][K] row-major (Linear [out][in]; a conv kernel
  * [O][I][ky][kx] is the same thing with K = I*ky*kx).  P is [K][ceil(N/16)] 32-bit words, element i of a

@@ -49,6 +49,14 @@ def test_const_div_fast_path_is_exact(ops):
         assert ops.selftest_const_div(d) == 0, d
 
 
+def test_ranged_division_is_exact(ops):
+    # every denominator of the nine binades against 4096 pseudo-random numerators each (3e11 quotients) ...
+    assert ops.selftest_div(4096) == 0
+    # ... and a slab of 2048 denominators per binade against EVERY numerator mantissa (1.5e11 quotients)
+    for binade in range(9):
+        assert ops.selftest_div(1 << 23, (binade << 23) + 12345 * (binade + 1), 2048) == 0, binade
+
+
 @pytest.mark.parametrize("n", [0, 1, 3, 4, 5, 255, 1023, 4096, 4097, 1 << 20, (1 << 20) + 7])
 def test_sizes_and_tails(ops, n):
     rng = np.random.default_rng(n)

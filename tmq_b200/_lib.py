@@ -39,6 +39,7 @@ _SIGNATURES = {
     "tmq_mt_qloss": (c_int, [c_void_p, c_int, c_int, c_double, c_double, c_void_p, c_void_p, c_size_t, c_void_p]),
     "tmq_mt_qloss_bwd": (c_int, [c_void_p, c_int, c_int, c_double, c_double, c_void_p, c_void_p, c_void_p]),
     "tmq_mt_clamp": (c_int, [c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
+    "tmq_selftest_div": (c_int, [ctypes.c_uint, ctypes.c_uint64, ctypes.c_uint64, c_void_p, c_void_p]),
     "tmq_selftest_const_div": (c_int, [c_double, c_void_p, c_void_p]),
     "tmq_pack2b_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "tmq_pack2b_i32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),

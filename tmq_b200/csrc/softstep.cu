@@ -14,6 +14,10 @@
 
 #include "common.cuh"
 
+#ifndef TMQ_SS_FASTDIV
+#define TMQ_SS_FASTDIV 1  // range-specialised division for the data-dependent quotients of the packed path
+#endif
+
 namespace tmq {
 
 thread_local int g_last_cuda_error = 0;
@@ -186,6 +190,38 @@ __device__ __forceinline__ float2 div2(float2 a, float2 b) { return make_float2(
 __device__ __forceinline__ float2 clamp2(float2 v, float lo, float hi) {
     return make_float2(clamp_nan(v.x, lo, hi), clamp_nan(v.y, lo, hi));
 }
+// a / b for data-dependent b in [16, 8192) and |a| in [2^-60, 2^60] or zero (the ranges of the three quotients below):
+// reciprocal seed, one Newton step, then two residual corrections, all FMAs.  This is the textbook correctly-rounded
+// sequence; what it leaves out against div.rn is the range check and slow path that these operand ranges never need.
+// Checked against IEEE division by tmq_selftest_div (every b of the nine binades, pseudo-random and exhaustive a).
+__device__ __forceinline__ float rcp_seed(float b) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(b));
+    return y;
+}
+__device__ __forceinline__ float div_ranged(float a, float b) {
+    const float y0 = rcp_seed(b);
+    const float nb = -b;
+    const float e = __fmaf_rn(nb, y0, 1.0f);
+    const float y = __fmaf_rn(y0, e, y0);
+    const float q0 = __fmul_rn(a, y);
+    const float r0 = __fmaf_rn(nb, q0, a);
+    const float q1 = __fmaf_rn(r0, y, q0);
+    const float r1 = __fmaf_rn(nb, q1, a);
+    return __fmaf_rn(r1, y, q1);
+}
+__device__ __forceinline__ float2 div_ranged2(float2 a, float2 b, float2 ONE, float2 NZ) {
+    const float2 y0 = make_float2(rcp_seed(b.x), rcp_seed(b.y));
+    const float2 nb = __ffma2_rn(b, make_float2(-ONE.x, -ONE.y), NZ);
+    const float2 e = __ffma2_rn(nb, y0, ONE);
+    const float2 y = __ffma2_rn(y0, e, y0);
+    const float2 q0 = __ffma2_rn(a, y, NZ);
+    const float2 r0 = __ffma2_rn(nb, q0, a);
+    const float2 q1 = __ffma2_rn(r0, y, q0);
+    const float2 r1 = __ffma2_rn(nb, q1, a);
+    return __ffma2_rn(r1, y, q1);
+}
+
 template <bool FAST>
 __device__ __forceinline__ float2 div_const2(float2 a, float D, float rD, float2 ONE, float2 NZ) {
     if (FAST) {
@@ -210,7 +246,7 @@ __device__ __forceinline__ Out2 element2(float2 w, float2 g, const Args &a) {
             const float2 p = add2(x2, f2(27.0f));
             const float2 q = mul2(x, p);
             const float2 s = add2(f2(27.0f), mul2(x2, f2(9.0f)));
-            const float2 z = div2(q, s);
+            const float2 z = TMQ_SS_FASTDIV ? div_ranged2(q, s, ONE, NZ) : div2(q, s);
             const float2 u = div_const2<FAST>(z, a.s.D, a.s.rD, ONE, NZ);
             r.y = add2(add2(u, f2(0.5f)), fw);
         }
@@ -219,7 +255,7 @@ __device__ __forceinline__ Out2 element2(float2 w, float2 g, const Args &a) {
             const float2 n = mul2(e, e);
             const float2 b = add2(f2(3.0f), x2);
             const float2 m = mul2(mul2(f2(9.0f), b), b);
-            const float2 ds = div2(n, m);
+            const float2 ds = TMQ_SS_FASTDIV ? div_ranged2(n, m, ONE, NZ) : div2(n, m);
             const float2 G = div_const2<FAST>(mul2(f2(a.s.d), ds), a.s.D, a.s.rD, ONE, NZ);
             r.gw = mul2(mul2(f2(a.scale), g), G);
         }
@@ -233,7 +269,7 @@ __device__ __forceinline__ Out2 element2(float2 w, float2 g, const Args &a) {
         if (F & (F_DFWD | F_QSUM)) {
             const float2 n = mul2(e, e);
             const float2 m = mul2(mul2(f2(9.0f), b), b);
-            const float2 ds = div2(n, m);
+            const float2 ds = TMQ_SS_FASTDIV ? div_ranged2(n, m, ONE, NZ) : div2(n, m);
             r.o = div_const2<FAST>(mul2(f2(a.sd), ds), a.q.D, a.q.rD, ONE, NZ);
             r.term = r.o;
         }
@@ -241,7 +277,13 @@ __device__ __forceinline__ Out2 element2(float2 w, float2 g, const Args &a) {
             const float2 i = mul2(f2(16.0f), x);
             const float2 N2 = mul2(i, e);
             const float2 Dd = mul2(mul2(mul2(f2(3.0f), b), b), b);
-            const float2 d2 = div2(N2, Dd);
+            float2 d2;
+            if (TMQ_SS_FASTDIV) {
+                d2 = div_ranged2(N2, Dd, ONE, NZ);
+                d2 = make_float2(copysignf(d2.x, N2.x), copysignf(d2.y, N2.y));  // -0 numerators (argument on the lower clamp)
+            } else {
+                d2 = div2(N2, Dd);
+            }
             const float2 num = mul2(f2(a.sdd), d2);
             float2 gr;
             if (FAST) {
@@ -297,6 +339,9 @@ constexpr int kThreads = 256;
 #endif
 #ifndef TMQ_SS_PACKED
 #define TMQ_SS_PACKED 1     // arithmetic on the packed f32x2 pipe, two elements per instruction
+#endif
+#ifndef TMQ_SS_FASTDIV
+#define TMQ_SS_FASTDIV 1    // range-specialised division for the data-dependent quotients of the packed path
 #endif
 #ifndef TMQ_SS_MINB
 #define TMQ_SS_MINB 4       // min resident blocks per SM handed to __launch_bounds__
@@ -503,6 +548,35 @@ __global__ void const_div_selftest_kernel(float D, float rD, unsigned long long 
     if ((threadIdx.x & 31) == 0 && bad) atomicAdd(mismatches, bad);
 }
 
+// Compares div_ranged with IEEE division: every denominator bit pattern of the binades [2^lo_exp, 2^hi_exp), each with
+// `per_b` numerators (mantissas from a counter-based hash, or - when per_b == 2^23 - every mantissa), numerator exponent
+// fixed at 2^0 and both signs alternating (the sequence is scale-invariant in the numerator barring under/overflow).
+__global__ void div_selftest_kernel(int lo_exp, int hi_exp, unsigned per_b, unsigned long long b_begin,
+                                    unsigned long long b_count, unsigned long long *mismatches) {
+    unsigned long long bad = 0;
+    const unsigned long long total = b_count * per_b;
+    for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i < total;
+         i += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned long long bi = b_begin + i / per_b;
+        const unsigned ai = (unsigned)(i % per_b);
+        const unsigned bexp = (unsigned)(127 + lo_exp) + (unsigned)(bi >> 23);
+        const float b = __uint_as_float((bexp << 23) | (unsigned)(bi & 0x7FFFFFu));
+        unsigned mant;
+        if (per_b == (1u << 23)) {
+            mant = ai;
+        } else {
+            unsigned h = ai * 0x9E3779B1u ^ (unsigned)(bi * 0x85EBCA77ull);
+            h ^= h >> 15; h *= 0x2C1B3C6Du; h ^= h >> 12;
+            mant = h & 0x7FFFFFu;
+        }
+        const float a = __uint_as_float(((ai & 1u) << 31) | (127u << 23) | mant);
+        bad += (__float_as_uint(div_ranged(a, b)) != __float_as_uint(__fdiv_rn(a, b)));
+    }
+    (void)hi_exp;
+    bad = (unsigned long long)__reduce_add_sync(0xffffffffu, (unsigned)bad);
+    if ((threadIdx.x & 31) == 0 && bad) atomicAdd(mismatches, bad);
+}
+
 }  // namespace tmq
 
 // ---------------------------------------------------------------------------------------------------- C ABI
@@ -686,6 +760,16 @@ extern "C" int tmq_mt_clamp(const void *d_plan, int ntensors, int nchunks, float
     a.one = 1.0f; a.nzero = -0.0f;
     a.lo = lo; a.hi = hi;
     return launch_mt<F_CLAMP>(d_plan, ntensors, nchunks, a, nullptr, nullptr, true, (cudaStream_t)stream);
+}
+
+extern "C" int tmq_selftest_div(unsigned per_b, unsigned long long b_begin, unsigned long long b_count,
+                                unsigned long long *mismatches, void *stream) {
+    // denominators of the soft-step quotients live in [27, 5184]: binades 2^4 .. 2^13
+    const unsigned long long all_b = 9ull << 23;
+    if (!mismatches || per_b == 0 || per_b > (1u << 23) || b_begin >= all_b || b_count == 0 || b_begin + b_count > all_b)
+        return TMQ_ERR_ARG;
+    div_selftest_kernel<<<kNumSMs * 16, 256, 0, (cudaStream_t)stream>>>(4, 13, per_b, b_begin, b_count, mismatches);
+    return launch_status();
 }
 
 extern "C" int tmq_selftest_const_div(double digamma, unsigned long long *mismatches, void *stream) {

@@ -28,6 +28,10 @@
 
 namespace tmq {
 
+#ifndef TMQ_GEMV_MINB
+#define TMQ_GEMV_MINB 1      // min resident CTAs per SM handed to __launch_bounds__ (capping registers at 64 to fit 8 measured slower)
+#endif
+
 constexpr int kGemvWarps = 4;        // warps per CTA
 constexpr int kGemvBatch = 4;        // K slices a warp has in flight at once
 
@@ -65,7 +69,7 @@ __device__ __forceinline__ uint4 ldg_stream(const uint32_t *p) {
 
 // KIND 0: bf16 activations (fmt-0 words), KIND 1: int8 activations (fmt-1 words)
 template <int KIND>
-__global__ void __launch_bounds__(kGemvWarps * 32) ternary_gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(kGemvWarps * 32, TMQ_GEMV_MINB) ternary_gemv_kernel(const GemvArgs a) {
     using Acc = typename std::conditional<KIND == 0, float, int>::type;
     __shared__ Acc red[kGemvWarps][16][8];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next launch may start its own prologue

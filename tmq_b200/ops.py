@@ -135,6 +135,14 @@ def selftest_const_div(digamma, device="cuda"):
     return int(cnt.item())
 
 
+def selftest_div(per_b, b_begin=0, b_count=9 << 23, device="cuda"):
+    """Mismatches of the range-specialised division against IEEE division (see tmq_selftest_div)."""
+    cnt = torch.zeros((), dtype=torch.int64, device=device)
+    with torch.cuda.device(cnt.device):
+        check(lib().tmq_selftest_div(int(per_b), int(b_begin), int(b_count), _ptr(cnt), _stream(cnt)), "selftest_div")
+    return int(cnt.item())
+
+
 # ------------------------------------------------------------------------------------------------ multi-tensor
 
 class MultiTensorPlan:
