@@ -137,3 +137,39 @@ def test_gemv_baseline_shape(ops, M):
         yo = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), out_dtype=torch.float32, path=pth)
         assert np.all(np.abs(yo.cpu().double().numpy() - ref) <= 1e-5 * np.maximum(np.abs(ref), rms)), pth
     assert torch.equal(y, y2)
+
+
+def test_full_size_prefill_shape_sampled(ops):
+    """BASELINE prefill config (M = 8192, K = 8192, N = 28672) at full size: a random 96 x 96 sample of the outputs
+    against fp64 dot products of the same operands (bf16 path: rel 1e-3 bar, 1e-5 expected; int8 path: bit-exact), plus
+    one size-independent property: activations with a single one per row read out weight columns exactly."""
+    M, K, N = 8192, 8192, 28672
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    u = torch.rand(N, K, generator=gen, device="cuda")
+    W = torch.where(u < 0.3, -1.0, torch.where(u < 0.7, 0.0, 1.0))
+    del u
+    P = ops.compactify_ternary(W)
+    scale = torch.rand(N, generator=gen, device="cuda") * 0.09 + 0.01
+    X = torch.randn(M, K, generator=gen, device="cuda").to(torch.bfloat16)
+    Y = ops.ternary_gemm(X, ops.prepack(P, N, ops.FMT_BF16), N, scale, out_dtype=torch.float32)
+    ops.check_gemm_status()
+    rows = torch.randint(0, M, (96,), generator=gen, device="cuda")
+    cols = torch.randint(0, N, (96,), generator=gen, device="cuda")
+    ref = (X[rows].double() @ W[cols].double().T) * scale[cols].double()
+    got = Y[rows][:, cols].double()
+    rms = ref.pow(2).mean().sqrt()
+    assert bool(((got - ref).abs() <= 1e-5 * torch.maximum(ref.abs(), rms)).all())
+    del Y
+    X8 = torch.randint(-127, 128, (M, K), generator=gen, device="cuda", dtype=torch.int8)
+    wt8 = ops.prepack(P, N, ops.FMT_I8)
+    Y8 = ops.ternary_gemm_i8(X8, wt8, N)
+    ops.check_gemm_status()
+    ref8 = (X8[rows].double() @ W[cols].double().T).to(torch.int32)
+    assert torch.equal(Y8[rows][:, cols], ref8)
+    del Y8, X8
+    # one-hot rows: Y[i] = column k_i of T, exactly
+    ks = torch.randint(0, K, (256,), generator=gen, device="cuda")
+    E = torch.zeros(256, K, dtype=torch.int8, device="cuda")
+    E[torch.arange(256, device="cuda"), ks] = 1
+    out = ops.ternary_gemm_i8(E, wt8, N, path="tiles")
+    assert torch.equal(out, W[:, ks].T.to(torch.int32))
