@@ -186,11 +186,17 @@ int tmq_ternary_gemv_tc_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int6
 
 /* Ternary Conv2d as an implicit GEMM (no im2col buffer): X bf16 NHWC [B][H][W][C], C % 64 == 0; Wt = fmt-0 prepack of
  * the packed weight with its K rows reordered to (ky, kx, c); Y bf16 NHWC [B][OH][OW][N] with the output geometry of
- * F.conv2d; scale / bias per output channel (folded BatchNorm, NULL for none), optional ReLU.
+ * F.conv2d; scale / bias per output channel (folded BatchNorm, NULL for none), optional residual (bf16, shape of Y,
+ * added before the activation), optional ReLU.
  * replaces: Conv2d.compact_forward, tmq/tmq.py:822-871 (F.unfold + ternary_mmm_cuda + F.fold). */
-int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int B, int H,
-                            int W, int C, int N, int ky, int kx, int sy, int sx, int py, int px, int dy, int dx, int relu,
-                            int *status, void *stream);
+int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, const void *residual,
+                            void *Y, int B, int H, int W, int C, int N, int ky, int kx, int sy, int sx, int py, int px,
+                            int dy, int dx, int relu, int *status, void *stream);
+/* Patch matrix for layers the implicit path cannot take (channel count not a multiple of 64, e.g. a 3-channel stem):
+ * X fp32 NCHW -> A bf16 [B*OH*OW][Kp], K = ky*kx*C in (ky, kx, c) order zero-padded to Kp (% 8 == 0); feed A to
+ * tmq_ternary_gemm_bf16.  replaces: F.unfold in Conv2d.compact_forward, tmq/tmq.py:857-858. */
+int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int H, int W, int ky, int kx, int sy, int sx, int py, int px,
+                          int dy, int dx, int Kp, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Entropy-coded storage of packed weights (HOST pointers; sequential range coder, no GPU work).  Streams are

@@ -47,6 +47,30 @@ def test_implicit_conv_matches_conv2d(ops, case):
     _conv_case(ops, b, c, h, w, n, k, s, p, d, relu, seed=sum(case[:9]))
 
 
+def test_residual_fusion_and_patch_kernel(ops):
+    gen = torch.Generator().manual_seed(77)
+    # residual + ReLU inside the epilogue equals conv, then add, then ReLU
+    x = torch.randn(2, 64, 10, 10, generator=gen).to(torch.bfloat16).cuda().permute(0, 2, 3, 1).contiguous()
+    wgt = torch.randint(-1, 2, (64, 64, 3, 3), generator=gen).float()
+    rows = ops.compactify_ternary(wgt.cuda()).view(64 * 9, -1)
+    k = torch.arange(64 * 9)
+    perm = torch.argsort((k % 9) * 64 + k // 9).cuda()
+    wt = ops.prepack(rows.index_select(0, perm).contiguous(), 64, ops.FMT_BF16)
+    scale = (torch.rand(64, generator=gen) * 0.05 + 0.01).cuda()
+    res = torch.randn(2, 10, 10, 64, generator=gen).to(torch.bfloat16).cuda()
+    plain = ops.ternary_conv2d_nhwc(x, wt, 64, (3, 3), (1, 1), (1, 1), (1, 1), scale)
+    fused = ops.ternary_conv2d_nhwc(x, wt, 64, (3, 3), (1, 1), (1, 1), (1, 1), scale, relu=True, residual=res)
+    want = torch.relu(plain.float() + res.float())
+    assert (fused.float() - want).abs().max() <= 2.0 ** -6 * want.abs().max()
+    # patch kernel against unfold
+    img = torch.randn(3, 3, 20, 17, generator=gen).cuda()
+    a, (b, oh, ow) = ops.conv_patches(img, (7, 7), (2, 2), (3, 3), (1, 1))
+    unf = torch.nn.functional.unfold(img, (7, 7), padding=3, stride=2)            # [B, C*49, L], (c, ky, kx)
+    ref = unf.view(3, 3, 49, -1).permute(0, 3, 2, 1).reshape(b * oh * ow, 147)      # -> (ky, kx, c)
+    assert a.shape == (b * oh * ow, 152)
+    assert torch.equal(a[:, :147], ref.to(torch.bfloat16)) and float(a[:, 147:].abs().max()) == 0.0
+
+
 def test_resnet18_qat_step_runs_and_clamps():
     from tmq_b200 import workloads
     torch.manual_seed(0)

@@ -61,7 +61,8 @@ _SIGNATURES = {
                                          c_int64, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
     "tmq_ternary_gemv_tc_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                        c_size_t, c_void_p, c_void_p]),
-    "tmq_ternary_conv2d_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 14 + [c_void_p, c_void_p]),
+    "tmq_ternary_conv2d_bf16": (c_int, [c_void_p] * 6 + [c_int] * 14 + [c_void_p, c_void_p]),
+    "tmq_conv_patches_bf16": (c_int, [c_void_p, c_void_p] + [c_int] * 13 + [c_void_p]),
     "tmq_ternary_gemm_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p]),
 }

@@ -1,0 +1,54 @@
+// Warp-level epilogue shared by the tcgen05 GEMM and convolution kernels: one tcgen05.ld chunk (32 accumulator rows =
+// output channels, one per lane, x 16 accumulator columns = output rows / pixels) is scaled, transposed through a
+// small shared-memory stage and written as 16-byte bf16 vectors (8 channels of one output row per lane), with an
+// optional residual read the same way and an optional ReLU.  Against one 2-byte store per element this cuts the
+// global instructions eight-fold.
+#pragma once
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace tmq {
+
+// stage: this warp's private 16 x 32 fp32 area (2 KB, 16-byte aligned).  n_base: first channel of the warp's 32.
+__device__ __forceinline__ void epilogue_chunk_bf16(const uint32_t (&v)[16], float sc, float bi, float *stage,
+                                                    __nv_bfloat16 *Y, const __nv_bfloat16 *residual, long long m_base,
+                                                    long long M, long long ldy, long long n_base, long long N, int relu,
+                                                    int lane) {
+#pragma unroll
+    for (int j = 0; j < 16; j++) stage[j * 32 + lane] = fmaf(__uint_as_float(v[j]), sc, bi);
+    __syncwarp();
+    const int cg = (lane & 3) * 8;  // channel offset of this lane's 8-channel vector
+    const long long n = n_base + cg;
+    const bool vec_ok = ((ldy & 7) == 0) && (n + 8 <= N);
+#pragma unroll
+    for (int it = 0; it < 2; it++) {
+        const int p = it * 8 + (lane >> 2);
+        const long long m = m_base + p;
+        if (m < M && n < N) {
+            const float4 lo = *reinterpret_cast<const float4 *>(stage + p * 32 + cg);
+            const float4 hi = *reinterpret_cast<const float4 *>(stage + p * 32 + cg + 4);
+            float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            if (vec_ok) {
+                if (residual) {
+                    const uint4 rv = *reinterpret_cast<const uint4 *>(residual + m * ldy + n);
+                    const __nv_bfloat16 *rb = reinterpret_cast<const __nv_bfloat16 *>(&rv);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) f[e] += __bfloat162float(rb[e]);
+                }
+                __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(relu ? fmaxf(f[e], 0.0f) : f[e]);
+                *reinterpret_cast<uint4 *>(Y + m * ldy + n) = *reinterpret_cast<const uint4 *>(o);
+            } else {
+                for (int e = 0; e < 8 && n + e < N; e++) {
+                    float x = f[e];
+                    if (residual) x += __bfloat162float(residual[m * ldy + n + e]);
+                    Y[m * ldy + n + e] = __float2bfloat16_rn(relu ? fmaxf(x, 0.0f) : x);
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
+}  // namespace tmq

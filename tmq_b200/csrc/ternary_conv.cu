@@ -20,6 +20,7 @@
 
 #include "common.cuh"
 #include "decode.cuh"
+#include "epilogue.cuh"
 #include "ptx.cuh"
 #include "tma_host.cuh"
 
@@ -32,6 +33,7 @@ constexpr int kConvLag = 2;        // a gathered stage is published this many k-
 struct ConvArgs {
     const __nv_bfloat16 *X;
     const float *scale, *bias;
+    const __nv_bfloat16 *residual;  // optional [M][N], added before the ReLU (ResNet skip connection)
     __nv_bfloat16 *Y;
     int B, H, W, C, OH, OW, N;
     int ky, kx, sy, sx, py, px, dy, dx;
@@ -162,30 +164,22 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
         ptx::tc_fence_after_sync();
         const int quarter = warp & 3;
         const long long n = n0 + quarter * 32 + lane;
-        const bool n_ok = ok && n < args.N;
         float sc = 0.5f, bi = 0.0f;                   // operands carried +-2.0
-        if (n_ok) {
+        if (ok && n < args.N) {
             if (args.scale) sc *= args.scale[n];
             if (args.bias) bi = args.bias[n];
         }
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        // all MMAs have completed, so operand stage 0 is free: each warp takes 2 KB of it as its transpose area
+        float *stage = reinterpret_cast<float *>(smem + L::A_OFF) + (warp - 2) * 512;
         if (ok) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 uint32_t v[16];
                 ptx::tmem_ld_x16(lane_addr + (uint32_t)c, v);
                 ptx::tmem_ld_wait();
-                if (n_ok) {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const long long m = m0 + c + j;
-                        if (m < args.M) {
-                            float f = fmaf(__uint_as_float(v[j]), sc, bi);
-                            if (args.relu) f = fmaxf(f, 0.0f);
-                            args.Y[m * args.N + n] = __float2bfloat16_rn(f);
-                        }
-                    }
-                }
+                epilogue_chunk_bf16(v, sc, bi, stage, args.Y, args.residual, m0 + c, args.M, args.N, n0 + quarter * 32,
+                                    args.N, args.relu, lane);
             }
         }
     } else {
@@ -287,9 +281,54 @@ static int launch_conv(const uint32_t *Wt, const ConvArgs &a, long long K, cudaS
 
 using namespace tmq;
 
-extern "C" int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y,
-                                       int B, int H, int W, int C, int N, int ky, int kx, int sy, int sx, int py, int px,
-                                       int dy, int dx, int relu, int *status, void *stream) {
+// Patch matrix for convolutions whose channel count is too small for the implicit path (the 3-channel stem):
+// X fp32 NCHW [B][C][H][W] -> A bf16 [B*OH*OW][Kp], K = ky*kx*C in (ky, kx, c) order, zero padded to Kp (multiple of 8).
+__global__ void __launch_bounds__(256) stem_patches_kernel(const float *__restrict__ X, __nv_bfloat16 *__restrict__ A, int B,
+                                                            int C, int H, int W, int OH, int OW, int ky, int kx, int sy,
+                                                            int sx, int py, int px, int dy, int dx, int Kp) {
+    const int chunks = Kp / 8;
+    const long long total = (long long)B * OH * OW * chunks;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int ch = (int)(idx % chunks);
+    const long long m = idx / chunks;
+    const int ox = (int)(m % OW), oy = (int)((m / OW) % OH), b = (int)(m / ((long long)OW * OH));
+    const int K = ky * kx * C;
+    __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const int k = ch * 8 + e;
+        float f = 0.0f;
+        if (k < K) {
+            const int tap = k / C, c = k % C;
+            const int iy = oy * sy + (tap / kx) * dy - py, ix = ox * sx + (tap % kx) * dx - px;
+            if (iy >= 0 && iy < H && ix >= 0 && ix < W) f = __ldg(X + (((long long)b * C + c) * H + iy) * W + ix);
+        }
+        v[e] = __float2bfloat16_rn(f);
+    }
+    *reinterpret_cast<uint4 *>(A + m * Kp + ch * 8) = *reinterpret_cast<const uint4 *>(v);
+}
+
+extern "C" int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int H, int W, int ky, int kx, int sy, int sx,
+                                     int py, int px, int dy, int dx, int Kp, void *stream) {
+    if (!X || !A || B <= 0 || C <= 0 || H <= 0 || W <= 0 || ky <= 0 || kx <= 0 || sy <= 0 || sx <= 0 || py < 0 || px < 0 ||
+        dy <= 0 || dx <= 0)
+        return TMQ_ERR_ARG;
+    if (Kp % 8 != 0 || Kp < ky * kx * C) return TMQ_ERR_ARG;
+    if (!aligned(A, 16) || !aligned(X, 4)) return TMQ_ERR_ALIGN;
+    const int OH = (H + 2 * py - dy * (ky - 1) - 1) / sy + 1, OW = (W + 2 * px - dx * (kx - 1) - 1) / sx + 1;
+    if (OH <= 0 || OW <= 0) return TMQ_ERR_ARG;
+    const long long total = (long long)B * OH * OW * (Kp / 8);
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
+    stem_patches_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(X, reinterpret_cast<__nv_bfloat16 *>(A), B, C, H, W,
+                                                                           OH, OW, ky, kx, sy, sx, py, px, dy, dx, Kp);
+    return launch_status();
+}
+
+extern "C" int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias,
+                                       const void *residual, void *Y, int B, int H, int W, int C, int N, int ky, int kx,
+                                       int sy, int sx, int py, int px, int dy, int dx, int relu, int *status, void *stream) {
     if (!X || !Wt || !Y || !status) return TMQ_ERR_ARG;
     if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || N <= 0 || ky <= 0 || kx <= 0 || sy <= 0 || sx <= 0 || py < 0 || px < 0 ||
         dy <= 0 || dx <= 0)
@@ -301,6 +340,7 @@ extern "C" int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const 
     ConvArgs a;
     a.X = reinterpret_cast<const __nv_bfloat16 *>(X);
     a.scale = scale; a.bias = bias;
+    a.residual = reinterpret_cast<const __nv_bfloat16 *>(residual);
     a.Y = reinterpret_cast<__nv_bfloat16 *>(Y);
     a.B = B; a.H = H; a.W = W; a.C = C; a.OH = OH; a.OW = OW; a.N = N;
     a.ky = ky; a.kx = kx; a.sy = sy; a.sx = sx; a.py = py; a.px = px; a.dy = dy; a.dx = dx;

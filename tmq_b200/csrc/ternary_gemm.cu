@@ -27,6 +27,7 @@
 
 #include "common.cuh"
 #include "decode.cuh"
+#include "epilogue.cuh"
 #include "tma_host.cuh"
 #include "ptx.cuh"
 
@@ -207,7 +208,12 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 uint32_t v[16];
                 ptx::tmem_ld_x16(lane_addr + (uint32_t)c, v);
                 ptx::tmem_ld_wait();
-                if (n_ok) {
+                if (KIND == KIND_BF16 && !args.out_f32) {
+                    // all MMAs have completed: operand stage 0 doubles as the warps' transpose area
+                    float *stage = reinterpret_cast<float *>(smem + L::A_OFF) + (warp - 2) * 512;
+                    epilogue_chunk_bf16(v, sc, bi, stage, reinterpret_cast<__nv_bfloat16 *>(args.Y), nullptr, m0 + c, args.M,
+                                        args.ldy, n0 + quarter * 32, args.N, 0, lane);
+                } else if (n_ok) {
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const long long m = m0 + c + j;

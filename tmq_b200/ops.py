@@ -434,8 +434,26 @@ def ternary_gemm_i8(x, wt, columns, path="auto", wt_tiled=None):
 HAVE_IMPLICIT_CONV = True
 
 
+def conv_patches(x, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1)):
+    """fp32 NCHW image batch -> bf16 patch matrix [B*OH*OW, Kp] in (ky, kx, c) order, K zero-padded to a multiple
+    of 8; for layers whose channel count the implicit convolution cannot take."""
+    if x.dtype != torch.float32 or x.device.type != "cuda" or x.dim() != 4:
+        raise RuntimeError("conv_patches: expected a 4-D CUDA fp32 NCHW tensor")
+    x = x.contiguous()
+    b, c, h, w = x.shape
+    (ky, kx), (sy, sx), (py, px), (dy, dx) = kernel, stride, padding, dilation
+    oh = (h + 2 * py - dy * (ky - 1) - 1) // sy + 1
+    ow = (w + 2 * px - dx * (kx - 1) - 1) // sx + 1
+    kp = (ky * kx * c + 7) // 8 * 8
+    out = torch.empty((b * oh * ow, kp), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().tmq_conv_patches_bf16(_ptr(x), _ptr(out), b, c, h, w, ky, kx, sy, sx, py, px, dy, dx, kp, _stream(x)),
+              "conv_patches")
+    return out, (b, oh, ow)
+
+
 def ternary_conv2d_nhwc(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None, bias=None,
-                        relu=False):
+                        relu=False, residual=None):
     """Implicit-GEMM convolution: x bf16 NHWC [B, H, W, C] (C % 64 == 0), wt = prepack(FMT_BF16) of the packed weight
     with rows in (ky, kx, c) order -> bf16 NHWC [B, OH, OW, N]."""
     if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 4 or not x.is_contiguous():
@@ -452,10 +470,15 @@ def ternary_conv2d_nhwc(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), d
     y = torch.empty((b, oh, ow, n), dtype=torch.bfloat16, device=x.device)
     sc = None if scale is None else scale.to(device=x.device, dtype=torch.float32).contiguous()
     bi = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
+    if residual is not None and (residual.dtype != torch.bfloat16 or tuple(residual.shape) != tuple(y.shape)
+                                 or not residual.is_contiguous()):
+        raise RuntimeError("ternary_conv2d_nhwc: the residual must be a contiguous bf16 tensor of the output's shape")
     st = gemm_status_word(x.device)
     with torch.cuda.device(x.device):
         check(lib().tmq_ternary_conv2d_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
-                                            _ptr(bi) if bi is not None else None, _ptr(y), b, h, w, c, n, ky, kx, sy, sx,
+                                            _ptr(bi) if bi is not None else None,
+                                            _ptr(residual) if residual is not None else None, _ptr(y), b, h, w, c, n, ky,
+                                            kx, sy, sx,
                                             py, px, dy, dx, 1 if relu else 0, _ptr(st), _stream(x)),
               "ternary_conv2d_nhwc")
     return y

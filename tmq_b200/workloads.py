@@ -84,34 +84,19 @@ class PackedConv:
         self.wt = ops.prepack(p, self.cout, ops.FMT_BF16)
         self.kpad = kpad
 
+    def from_images(self, images):
+        """Stem route: fp32 NCHW images -> bf16 NHWC feature map, patches built by a kernel (no torch glue)."""
+        a, (b, oh, ow) = ops.conv_patches(images, (self.ky, self.kx), self.stride, self.padding, self.dilation)
+        y = ops.ternary_gemm(a, self.wt, self.cout, self.scale, self.bias).view(b, oh, ow, self.cout)
+        return torch.relu_(y) if self.relu else y
+
     def __call__(self, x_nhwc, residual=None):
-        """x_nhwc: bf16 [B, H, W, C] contiguous -> bf16 [B, OH, OW, Cout]; optional residual added before the ReLU."""
-        b, h, w, c = x_nhwc.shape
-        (sy, sx), (py, px), (dy, dx) = self.stride, self.padding, self.dilation
-        oh = (h + 2 * py - dy * (self.ky - 1) - 1) // sy + 1
-        ow = (w + 2 * px - dx * (self.kx - 1) - 1) // sx + 1
-        if self.implicit and ops.HAVE_IMPLICIT_CONV:
-            y = ops.ternary_conv2d_nhwc(x_nhwc, self.wt, self.cout, (self.ky, self.kx), self.stride, self.padding,
-                                        self.dilation, self.scale, self.bias, relu=self.relu and residual is None)
-            y = y.view(b, oh, ow, self.cout)
-        else:
-            # explicit patches (only the 3-channel stem takes this route): (ky, kx, c) order to match the weights
-            xp = torch.nn.functional.pad(x_nhwc, (0, 0, px, px, py, py))
-            cols = []
-            for iy in range(self.ky):
-                for ix in range(self.kx):
-                    cols.append(xp[:, iy * dy: iy * dy + (oh - 1) * sy + 1: sy, ix * dx: ix * dx + (ow - 1) * sx + 1: sx, :])
-            a = torch.cat(cols, dim=3).reshape(b * oh * ow, self.K)
-            if self.kpad:
-                a = torch.nn.functional.pad(a, (0, self.kpad))
-            y = ops.ternary_gemm(a.contiguous(), self.wt, self.cout, self.scale, self.bias).view(b, oh, ow, self.cout)
-            if self.relu and residual is None:
-                y = torch.relu_(y)
-        if residual is not None:
-            y = y + residual
-            if self.relu:
-                y = torch.relu_(y)
-        return y
+        """x_nhwc: bf16 [B, H, W, C] contiguous -> bf16 [B, OH, OW, Cout]; the optional residual is added before the
+        ReLU inside the convolution's epilogue."""
+        if not self.implicit:
+            raise RuntimeError("PackedConv: this layer's channel count needs the from_images() route")
+        return ops.ternary_conv2d_nhwc(x_nhwc, self.wt, self.cout, (self.ky, self.kx), self.stride, self.padding,
+                                       self.dilation, self.scale, self.bias, relu=self.relu, residual=residual)
 
 
 class PackedResNet18:
@@ -137,8 +122,7 @@ class PackedResNet18:
 
     @torch.no_grad()
     def __call__(self, images):
-        x = images.to(torch.bfloat16).permute(0, 2, 3, 1).contiguous()                # NHWC
-        x = self.conv1(x)
+        x = self.conv1.from_images(images.float())                                    # bf16 NHWC
         x = torch.nn.functional.max_pool2d(x.permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1).contiguous()
         for c1, c2, down in self.blocks:
             identity = x if down is None else down(x)
