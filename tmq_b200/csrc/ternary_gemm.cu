@@ -5,9 +5,11 @@
 // activations with a constant-memory LUT decode of the packed words.  Here the packed tile is decoded in shared
 // memory to EXACT bf16 / int8 values and fed to tcgen05.mma with the accumulator in tensor memory:
 //
-//   * roles per CTA (192 threads): warp 0 issues TMA loads (activation tile with 128-byte swizzle + the raw
-//     packed-weight tile), warps 2-5 decode the packed tile into the swizzled K-major operand layout, one thread of
-//     warp 1 issues the MMAs; warps 2-5 then drain the accumulator (tcgen05.ld), apply scale/bias and store.
+//   * persistent CTAs (one per SM, 320 threads) walk the output tiles; roles: warp 0 issues TMA loads (activation
+//     tile with 128-byte swizzle + the raw packed-weight tile), warps 2-5 decode the packed tile into the swizzled
+//     K-major operand layout, one thread of warp 1 issues the MMAs, warps 6-9 drain the accumulator (tcgen05.ld),
+//     apply scale/bias and store.  The accumulator is double-buffered in tensor memory, so the epilogue of one
+//     tile overlaps the multiplication of the next.
 //   * the WEIGHT tile is the 128-row "A" operand and the ACTIVATION tile the N-side "B" operand (BN = 32..256
 //     rows), so one decoded weight tile is reused by up to 256 activation rows and skinny problems use a small BN.
 //     TMEM lane i therefore holds output column n0+i, TMEM column j holds output row m0+j.
@@ -33,9 +35,14 @@
 
 namespace tmq {
 
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2-5: decode, warps 6-9: epilogue
 constexpr int kTileN = 128;    // weight rows (output channels) per CTA = UMMA M
-constexpr int kStages = 4;
+// pipeline depth per activation-tile height (two 128-row CTAs per SM with 3 stages measured 20 % slower than one
+// 256-row CTA with 4)
+template <int BN>
+struct StagesFor {
+    static constexpr int value = 4;
+};
 constexpr int kRowBytes = 128; // bytes of one operand row per k-block (64 bf16 or 128 int8)
 
 enum { KIND_BF16 = 0, KIND_I8 = 1 };
@@ -66,44 +73,58 @@ struct KindTraits<KIND_I8> {
 
 template <int KIND, int BN>
 struct SmemLayout {
+    static constexpr int kStages = StagesFor<BN>::value;
     static constexpr int A_BYTES = kTileN * kRowBytes;                       // 16 KB
     static constexpr int B_BYTES = BN * kRowBytes;
     static constexpr int RAW_BYTES = kTileN * KindTraits<KIND>::RAW_ROW;     // 2 KB / 4 KB
     static constexpr int A_OFF = 0;
     static constexpr int B_OFF = A_OFF + kStages * A_BYTES;
     static constexpr int RAW_OFF = B_OFF + kStages * B_BYTES;
-    static constexpr int BAR_OFF = RAW_OFF + kStages * RAW_BYTES;
+    static constexpr int STAGE_OFF = RAW_OFF + kStages * RAW_BYTES;          // 4 x 2 KB transpose areas of the epilogue warps
+    static constexpr int BAR_OFF = STAGE_OFF + 4 * 2048;
     static constexpr int TOTAL = BAR_OFF + 256 + 1024;                       // + barriers + alignment slack
 };
 
 // ---- the kernel -----------------------------------------------------------------------------------------------------
+//
+// Persistent: min(#tiles, 148) CTAs, CTA c works on tiles c, c + grid, ... (channel-tile index fastest, so the CTAs of
+// one sweep share an activation tile through L2).  The TMA / decode / MMA pipeline runs on across tile boundaries and
+// the accumulator is double-buffered in TMEM (2 x BN columns): four dedicated epilogue warps drain tile i while tile
+// i+1 is being multiplied.
 
 template <int KIND, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, GemmArgs args) {
     using KT = KindTraits<KIND>;
     using L = SmemLayout<KIND, BN>;
+    constexpr int kStages = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *full_raw = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
     uint64_t *full_a = full_raw + kStages;
     uint64_t *empty = full_a + kStages;
-    uint64_t *acc_full = empty + kStages;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    uint64_t *acc_full = empty + kStages;   // [2]
+    uint64_t *acc_empty = acc_full + 2;     // [2]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long n0 = (long long)blockIdx.x * kTileN;
-    const long long m0 = (long long)blockIdx.y * BN;
     const int nkb = (int)((args.K + KT::BK - 1) / KT::BK);
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    const long long tiles_n = (args.N + kTileN - 1) / kTileN;
+    const long long tiles_m = (args.M + BN - 1) / BN;
+    const long long ntiles = tiles_n * tiles_m;
+    constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) {
             ptx::mbar_init(full_raw + s, 1);
-            ptx::mbar_init(full_a + s, 128);
+            ptx::mbar_init(full_a + s, 4);    // one arrival per decode warp
             ptx::mbar_init(empty + s, 1);
         }
-        ptx::mbar_init(acc_full, 1);
+        for (int b = 0; b < 2; b++) {
+            ptx::mbar_init(acc_full + b, 1);
+            ptx::mbar_init(acc_empty + b, 4); // one arrival per epilogue warp
+        }
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_x);
         ptx::prefetch_tensormap(&tmap_w);
@@ -121,96 +142,126 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0 && healthy) {
-            for (int kb = 0; kb < nkb; kb++) {
-                const int s = kb % kStages;
-                const uint32_t ph = (uint32_t)(kb / kStages) & 1u;
-                if (!ptx::mbar_wait(empty + s, ph ^ 1u, args.status)) break;
-                ptx::mbar_arrive_expect_tx(full_raw + s, (uint32_t)(L::RAW_BYTES + L::B_BYTES));
-                ptx::tma_load_2d(smem + L::RAW_OFF + s * L::RAW_BYTES, &tmap_w, full_raw + s, kb * (KT::RAW_ROW / 4), (int)n0);
-                ptx::tma_load_2d(smem + L::B_OFF + s * L::B_BYTES, &tmap_x, full_raw + s, kb * KT::BK, (int)m0);
+            long long it = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int n0 = (int)(tile % tiles_n) * kTileN, m0 = (int)(tile / tiles_n) * BN;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = (int)(it % kStages);
+                    const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+                    ok = ptx::mbar_wait(empty + s, ph ^ 1u, args.status);
+                    if (!ok) break;
+                    ptx::mbar_arrive_expect_tx(full_raw + s, (uint32_t)(L::RAW_BYTES + L::B_BYTES));
+                    ptx::tma_load_2d(smem + L::RAW_OFF + s * L::RAW_BYTES, &tmap_w, full_raw + s, kb * (KT::RAW_ROW / 4), n0);
+                    ptx::tma_load_2d(smem + L::B_OFF + s * L::B_BYTES, &tmap_x, full_raw + s, kb * KT::BK, m0);
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0 && healthy) {
             constexpr uint32_t idesc = (KT::C_FMT << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
+            long long it = 0;
+            int ti = 0;
             bool ok = true;
-            for (int kb = 0; kb < nkb && ok; kb++) {
-                const int s = kb % kStages;
-                const uint32_t ph = (uint32_t)(kb / kStages) & 1u;
-                ok = ptx::mbar_wait(full_a + s, ph, args.status);
+            for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ti++) {
+                const int buf = ti & 1;
+                // the epilogue must have drained this accumulator (two tiles ago)
+                ok = ptx::mbar_wait(acc_empty + buf, ((uint32_t)(ti >> 1) & 1u) ^ 1u, args.status);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
-                const uint64_t a_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::A_OFF + s * L::A_BYTES));
-                const uint64_t b_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES));
+                const uint32_t d_tmem = tmem_base + (uint32_t)buf * ACC_COLS;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = (int)(it % kStages);
+                    const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+                    ok = ptx::mbar_wait(full_a + s, ph, args.status);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    const uint64_t a_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::A_OFF + s * L::A_BYTES));
+                    const uint64_t b_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES));
 #pragma unroll
-                for (int k4 = 0; k4 < kRowBytes / 32; k4++) {  // 32 bytes of K per instruction (16 bf16 / 32 int8)
-                    const uint32_t accum = (kb > 0 || k4 > 0) ? 1u : 0u;
-                    if (KIND == KIND_BF16) ptx::umma_f16(tmem_base, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
-                    else ptx::umma_i8(tmem_base, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                    for (int k4 = 0; k4 < kRowBytes / 32; k4++) {  // 32 bytes of K per instruction (16 bf16 / 32 int8)
+                        const uint32_t accum = (kb > 0 || k4 > 0) ? 1u : 0u;
+                        if (KIND == KIND_BF16) ptx::umma_f16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                        else ptx::umma_i8(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                    }
+                    ptx::umma_commit(empty + s);  // stage reusable once these MMAs have read it
                 }
-                ptx::umma_commit(empty + s);  // stage reusable once these MMAs have read it
+                if (ok) ptx::umma_commit(acc_full + buf);
             }
-            if (ok) ptx::umma_commit(acc_full);
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- decode warps (2..5)
+        const int row = threadIdx.x - 64;  // weight row inside the tile, 0..127
+        const int sw = row & 7;
+        bool ok = healthy;
+        long long it = 0;
+        for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < nkb; kb++, it++) {
+                const int s = (int)(it % kStages);
+                const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+                ok = ptx::mbar_wait(full_raw + s, ph, args.status);
+                if (!ok) break;
+                const uint8_t *raw = smem + L::RAW_OFF + s * L::RAW_BYTES + row * KT::RAW_ROW;
+                uint8_t *arow = smem + L::A_OFF + s * L::A_BYTES + row * kRowBytes;
+                if (KIND == KIND_BF16) {
+                    const uint4 p = *reinterpret_cast<const uint4 *>(raw);
+                    const uint32_t words[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+                    for (int wi = 0; wi < 4; wi++) {
+                        uint32_t r[8];
+                        decode_word_bf16(words[wi], r);
+                        *reinterpret_cast<uint4 *>(arow + (((2 * wi) ^ sw) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
+                        *reinterpret_cast<uint4 *>(arow + (((2 * wi + 1) ^ sw) << 4)) = make_uint4(r[4], r[5], r[6], r[7]);
+                    }
+                } else {
+                    const uint4 p0 = *reinterpret_cast<const uint4 *>(raw);
+                    const uint4 p1 = *reinterpret_cast<const uint4 *>(raw + 16);
+                    const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                    for (int wi = 0; wi < 8; wi++) {
+                        uint32_t r[4];
+                        decode_word_i8(words[wi], r);
+                        *reinterpret_cast<uint4 *>(arow + ((wi ^ sw) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
+                    }
+                }
+                ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(full_a + s);
+            }
         }
     } else {
-        // ---------------------------------------------------------------- decode warps (2..5), then epilogue
-        const int row = threadIdx.x - 64;  // weight row inside the tile, 0..127
-        bool ok = healthy;
-        for (int kb = 0; kb < nkb && ok; kb++) {
-            const int s = kb % kStages;
-            const uint32_t ph = (uint32_t)(kb / kStages) & 1u;
-            ok = ptx::mbar_wait(full_raw + s, ph, args.status);
-            if (!ok) break;
-            const uint8_t *raw = smem + L::RAW_OFF + s * L::RAW_BYTES + row * KT::RAW_ROW;
-            uint8_t *arow = smem + L::A_OFF + s * L::A_BYTES + row * kRowBytes;
-            const int sw = row & 7;
-            if (KIND == KIND_BF16) {
-                const uint4 p = *reinterpret_cast<const uint4 *>(raw);
-                const uint32_t words[4] = {p.x, p.y, p.z, p.w};
-#pragma unroll
-                for (int wi = 0; wi < 4; wi++) {
-                    uint32_t r[8];
-                    decode_word_bf16(words[wi], r);
-                    *reinterpret_cast<uint4 *>(arow + (((2 * wi) ^ sw) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
-                    *reinterpret_cast<uint4 *>(arow + (((2 * wi + 1) ^ sw) << 4)) = make_uint4(r[4], r[5], r[6], r[7]);
-                }
-            } else {
-                const uint4 p0 = *reinterpret_cast<const uint4 *>(raw);
-                const uint4 p1 = *reinterpret_cast<const uint4 *>(raw + 16);
-                const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-#pragma unroll
-                for (int wi = 0; wi < 8; wi++) {
-                    uint32_t r[4];
-                    decode_word_i8(words[wi], r);
-                    *reinterpret_cast<uint4 *>(arow + ((wi ^ sw) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
-                }
-            }
-            ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-            ptx::mbar_arrive(full_a + s);
-        }
-        // ---------------------------------------------------------------- epilogue
-        if (ok) ok = ptx::mbar_wait(acc_full, 0u, args.status);
-        ptx::tc_fence_after_sync();
+        // ---------------------------------------------------------------- epilogue warps (6..9)
         const int quarter = warp & 3;                    // TMEM lanes this warp may touch: 32*quarter .. +31
-        const long long n = n0 + quarter * 32 + lane;
-        const bool n_ok = ok && n < args.N;
-        float sc = 1.0f, bi = 0.0f;
-        if (n_ok) {
-            if (args.scale) sc = args.scale[n];
-            if (args.bias) bi = args.bias[n];
-        }
-        if (KIND == KIND_BF16) sc *= 0.5f;               // operands carried +-2.0
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        if (ok) {
+        float *stage = reinterpret_cast<float *>(smem + L::STAGE_OFF) + (warp - 6) * 512;
+        bool ok = healthy;
+        int ti = 0;
+        for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ti++) {
+            const long long n0 = (tile % tiles_n) * kTileN, m0 = (tile / tiles_n) * BN;
+            const int buf = ti & 1;
+            ok = ptx::mbar_wait(acc_full + buf, (uint32_t)(ti >> 1) & 1u, args.status);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const long long n = n0 + quarter * 32 + lane;
+            const bool n_ok = n < args.N;
+            float sc = 1.0f, bi = 0.0f;
+            if (n_ok) {
+                if (args.scale) sc = args.scale[n];
+                if (args.bias) bi = args.bias[n];
+            }
+            if (KIND == KIND_BF16) sc *= 0.5f;           // operands carried +-2.0
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_COLS;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 uint32_t v[16];
                 ptx::tmem_ld_x16(lane_addr + (uint32_t)c, v);
                 ptx::tmem_ld_wait();
+                if (c + 16 >= BN) {                      // last chunk read: hand the accumulator back to the MMA warp
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(acc_empty + buf);
+                }
                 if (KIND == KIND_BF16 && !args.out_f32) {
-                    // all MMAs have completed: operand stage 0 doubles as the warps' transpose area
-                    float *stage = reinterpret_cast<float *>(smem + L::A_OFF) + (warp - 2) * 512;
                     epilogue_chunk_bf16(v, sc, bi, stage, reinterpret_cast<__nv_bfloat16 *>(args.Y), nullptr, m0 + c, args.M,
                                         args.ldy, n0 + quarter * 32, args.N, 0, lane);
                 } else if (n_ok) {
@@ -218,13 +269,8 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     for (int j = 0; j < 16; j++) {
                         const long long m = m0 + c + j;
                         if (m < args.M) {
-                            if (KIND == KIND_I8) {
-                                reinterpret_cast<int *>(args.Y)[m * args.ldy + n] = (int)v[j];
-                            } else {
-                                const float f = fmaf(__uint_as_float(v[j]), sc, bi);
-                                if (args.out_f32) reinterpret_cast<float *>(args.Y)[m * args.ldy + n] = f;
-                                else reinterpret_cast<__nv_bfloat16 *>(args.Y)[m * args.ldy + n] = __float2bfloat16_rn(f);
-                            }
+                            if (KIND == KIND_I8) reinterpret_cast<int *>(args.Y)[m * args.ldy + n] = (int)v[j];
+                            else reinterpret_cast<float *>(args.Y)[m * args.ldy + n] = fmaf(__uint_as_float(v[j]), sc, bi);
                         }
                     }
                 }
@@ -307,14 +353,18 @@ static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cud
         attr_err = cudaFuncSetAttribute(ternary_gemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     });
     if (attr_err != cudaSuccess) return cuda_status(attr_err);
-    dim3 grid((unsigned)((a.N + kTileN - 1) / kTileN), (unsigned)((a.M + BN - 1) / BN));
+    const long long ntiles = ((a.N + kTileN - 1) / kTileN) * ((a.M + BN - 1) / BN);
+    const unsigned grid = (unsigned)(ntiles < kNumSMs ? ntiles : kNumSMs);
     ternary_gemm_kernel<KIND, BN><<<grid, kGemmThreads, L::TOTAL, st>>>(mx, mw, a);
     return launch_status();
 }
 
 template <int KIND>
 static int dispatch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
-    if (a.M > 128) return launch_gemm<KIND, 256>(X, Wt, a, st);
+#ifndef TMQ_GEMM_BIG_BN
+#define TMQ_GEMM_BIG_BN 256
+#endif
+    if (a.M > 128) return launch_gemm<KIND, TMQ_GEMM_BIG_BN>(X, Wt, a, st);
     if (a.M > 64) return launch_gemm<KIND, 128>(X, Wt, a, st);
     if (a.M > 32) return launch_gemm<KIND, 64>(X, Wt, a, st);
     return launch_gemm<KIND, 32>(X, Wt, a, st);
@@ -327,7 +377,6 @@ static int check_gemm_common(const void *X, const uint32_t *Wt, const void *Y, l
     if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
     if ((K * x_elem_bytes) % 16 != 0) return TMQ_ERR_UNSUPPORTED;  // TMA row pitch must be a multiple of 16 bytes
     if (!aligned(X, 16) || !aligned(Wt, 16) || !aligned(status, 4)) return TMQ_ERR_ALIGN;
-    if ((M + 255) / 256 > 65535) return TMQ_ERR_UNSUPPORTED;
     return TMQ_OK;
 }
 
