@@ -354,12 +354,13 @@ def ternary_sections(peaks):
     for Mg in (1, 8, 32):
         X = torch.randn(Mg, K, device="cuda").to(torch.bfloat16)
         Y = torch.empty(Mg, N, device="cuda", dtype=torch.bfloat16)
+        status = ops.gemm_status_word(X.device)
         stream = torch.cuda.Stream()
 
         def run(i, st):
             for m0 in range(0, Mg, 8):
                 rc = L.tmq_ternary_gemv_bf16(X.data_ptr() + m0 * K * 2, wts[i].data_ptr(), scale.data_ptr(), None,
-                                             Y.data_ptr() + m0 * N * 2, min(8, Mg - m0), N, K, N, 0, st)
+                                             Y.data_ptr() + m0 * N * 2, min(8, Mg - m0), N, K, N, 0, status.data_ptr(), st)
                 assert rc == 0
         with torch.cuda.stream(stream):
             for i in range(NM):
@@ -434,13 +435,14 @@ def run_workload(args):
         scale = torch.rand(N, device=dev) * 0.09 + 0.01
         X = torch.randn(Mg, K, device=dev).to(torch.bfloat16)
         Y = torch.empty(Mg, N, device=dev, dtype=torch.bfloat16)
+        status = ops.gemm_status_word(X.device)
         st = torch.cuda.current_stream().cuda_stream
 
         def sweep(i):
             for wt in wts:
                 for m0 in range(0, Mg, 8):
                     rc = Lb.tmq_ternary_gemv_bf16(X.data_ptr() + m0 * K * 2, wt.data_ptr(), scale.data_ptr(), None,
-                                                  Y.data_ptr() + m0 * N * 2, min(8, Mg - m0), N, K, N, 0, st)
+                                                  Y.data_ptr() + m0 * N * 2, min(8, Mg - m0), N, K, N, 0, status.data_ptr(), st)
                     assert rc == 0
         ms = timed(sweep, args.steps, args.warmup) / NM
         nbytes = N * K // 4 + 2 * Mg * K + 2 * Mg * N + 4 * N

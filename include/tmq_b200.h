@@ -148,7 +148,8 @@ int tmq_unpack2b_f32(const uint32_t *P, float *W, int64_t N, int64_t K, void *st
  * Wt[N][Kp/16] words, Kp = K rounded up to 64, 16 consecutive k of one output channel per word, bit order per
  * activation type (fmt 0: bf16 activations, fmt 1: int8 activations).  tmq_prepack_words gives the word count.
  * ------------------------------------------------------------------------------------------------ */
-size_t tmq_prepack_words(int64_t N, int64_t K);
+size_t tmq_prepack_row_words(int64_t K, int fmt); /* row stride in 32-bit words (valid words + bank padding) */
+size_t tmq_prepack_words(int64_t N, int64_t K, int fmt); /* N * row stride */
 /* fmt 2 / 3: the same words as fmt 0 / 1 stored tile-contiguously, Wt[tile][k-block][128 rows][words], rows padded
  * to whole 128-channel tiles; this is what the skinny tensor-core kernel (tmq_ternary_gemv_tc_*) streams. */
 size_t tmq_prepack_tiled_words(int64_t N, int64_t K, int fmt);
@@ -163,13 +164,18 @@ int tmq_ternary_gemm_bf16(const void *X, const uint32_t *Wt, const float *scale,
 int tmq_ternary_gemm_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
                         int *status, void *stream);
 
-/* Skinny form for M <= 8 activation rows (decode-like GEMV): streams the packed weights once at HBM speed, warp-level
- * MMA on exactly decoded operands, deterministic.  Same operand conventions as the GEMM entry points above.
+/* Skinny form for M <= 8 activation rows (decode-like GEMV): reads the packed weights once, exactly decoded operands
+ * (warp-level MMA; byte dot products for int8 with M <= 2), deterministic.  Same operand conventions as the GEMM
+ * entry points above.  When one SM's share of the packed rows fits half its shared memory the rows are made
+ * resident with bulk copies issued BEFORE the kernel waits for its predecessor in the stream (programmatic dependent
+ * launch), so consecutive launches overlap their weight traffic with the predecessor's arithmetic; `status` (device
+ * int, zero before the first call, may be NULL: then the non-resident streaming kernel is used) receives
+ * TMQ_ERR_TIMEOUT if those copies never complete.
  * replaces: ternary_mvm_cuda, tmq/tmq_cuda.cu:563-603 (kernel :242-286). */
 int tmq_ternary_gemv_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int64_t M,
-                          int64_t N, int64_t K, int64_t ldy, int out_f32, void *stream);
+                          int64_t N, int64_t K, int64_t ldy, int out_f32, int *status, void *stream);
 int tmq_ternary_gemv_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
-                        void *stream);
+                        int *status, void *stream);
 
 /* Skinny form on the tensor cores for 1..32 activation rows: split-K over ~4 CTAs per SM, all of a CTA's packed
  * weight bytes in flight at once (TMA ring), decode in shared memory, tcgen05.mma with N = 16 / 32, deterministic
@@ -197,6 +203,35 @@ int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scal
  * tmq_ternary_gemm_bf16.  replaces: F.unfold in Conv2d.compact_forward, tmq/tmq.py:857-858. */
 int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int H, int W, int ky, int kx, int sy, int sx, int py, int px,
                           int dy, int dx, int Kp, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Depthwise ternary convolutions (groups == channels), fp32, forward and transposed.  W is the reference's packed form
+ * of a [C][1][ky][kx] kernel tensor: int32 [ky*kx][ceil(C/16)].  Arithmetic: taps accumulated in (ky, kx) order from +0
+ * with one fused multiply-add each (x = 0 outside the image), then acc * scale[c] + bias[c] with two roundings
+ * (NULL = skip).
+ *
+ * Direct NCHW forms: X [B][C][H][W] -> Y [B][C][OH][OW], no unfold / fold.
+ *   forward:    OH = (H + 2*py - dy*(ky-1) - 1) / sy + 1                                   (torch conv2d)
+ *   transposed: OH = (H - 1)*sy - 2*py + dy*(ky-1) + 1 + opy                               (torch conv_transpose2d)
+ * replaces: Conv2d.compact_forward groups != 1 branch, tmq/tmq.py:849-854, and ConvTranspose2d.compact_forward
+ * groups != 1 branch, tmq/tmq.py:1025-1029 (F.unfold / F.fold around the operators below).
+ *
+ * Operator-level forms on the reference operators' own layouts:
+ *   tmq_ternary_dwconv_patches_f32:      X [rows][ntaps][C] -> Y [rows][C]          (rows = batch * pixels)
+ *     replaces: ternary_dwconv_cuda, tmq/tmq_cuda.cu:607-644 (kernel :163-238; the reference reads batch element 0 only)
+ *   tmq_ternary_dwconvtrans_patches_f32: X [B][P][C] -> Y [B][C*ntaps][P], Y[b][c*ntaps+t][p] = X[b][p][c] * T[t][c]
+ *     replaces: ternary_dwconvtrans_cuda, tmq/tmq_cuda.cu:647-686 (kernel :118-159)
+ * ------------------------------------------------------------------------------------------------ */
+int tmq_ternary_dwconv2d_f32(const float *X, const uint32_t *W, const float *scale, const float *bias, float *Y, int B,
+                             int C, int H, int Wd, int ky, int kx, int sy, int sx, int py, int px, int dy, int dx,
+                             void *stream);
+int tmq_ternary_dwconvtrans2d_f32(const float *X, const uint32_t *W, const float *scale, const float *bias, float *Y,
+                                  int B, int C, int H, int Wd, int ky, int kx, int sy, int sx, int py, int px, int dy,
+                                  int dx, int opy, int opx, void *stream);
+int tmq_ternary_dwconv_patches_f32(const float *X, const uint32_t *W, float *Y, int64_t rows, int C, int ntaps,
+                                   void *stream);
+int tmq_ternary_dwconvtrans_patches_f32(const float *X, const uint32_t *W, float *Y, int B, int P, int C, int ntaps,
+                                        void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Entropy-coded storage of packed weights (HOST pointers; sequential range coder, no GPU work).  Streams are

@@ -144,3 +144,88 @@ def rc_decode(stream, rows, cols):
     if rc < 0:
         raise RuntimeError("oracle_rc_decode: malformed stream")
     return P.view(np.int32)
+
+
+# ---- depthwise convolutions (numpy fp32, one rounding per line as the reference kernels do) ---------------------------
+
+def _taps(P, C, ntaps):
+    """Packed depthwise kernel int32 [ntaps][ceil(C/16)] (or [1][ky][kx][Q]) -> T [ntaps][C] in {-1, 0, +1}, the
+    coefficient the reference kernels fetch as coeffs[chan/16 + ceil(C/16)*tap] (tmq/tmq_cuda.cu:141, :189)."""
+    P = np.ascontiguousarray(P, dtype=np.int32).reshape(ntaps, (C + 15) // 16).view(np.uint32)
+    c = np.arange(C)
+    code = (P[:, c >> 4] >> (2 * (15 - (c & 15))).astype(np.uint32)) & 3
+    return np.where(code == 1, 1.0, np.where(code == 2, -1.0, 0.0)).astype(np.float32)
+
+
+def dwconv_patches(X, P, C, ntaps):
+    """ternaryDWConvFP32 (tmq/tmq_cuda.cu:163-238): X [rows][ntaps][C] -> Y [rows][C], accu += x * t over taps in
+    order, fp32 (the product with {-1,0,1} is exact, so the kernel's fused multiply-add rounds like this add)."""
+    T = _taps(P, C, ntaps)
+    X = np.asarray(X, dtype=np.float32).reshape(-1, ntaps, C)
+    acc = np.zeros((X.shape[0], C), dtype=np.float32)
+    for t in range(ntaps):
+        acc = acc + X[:, t, :] * T[t][None, :]
+    return acc
+
+
+def dwconvtrans_patches(X, P, C, ntaps):
+    """ternaryDWConvTransFP32 (tmq/tmq_cuda.cu:118-159): X [B][P][C] -> Y [B][C*ntaps][P] with
+    Y[b][c*ntaps + t][p] = X[b][p][c] * T[t][c]."""
+    T = _taps(P, C, ntaps)
+    X = np.asarray(X, dtype=np.float32)
+    Y = X.transpose(0, 2, 1)[:, :, None, :] * T.T[None, :, :, None]       # [B][C][ntaps][P]
+    return Y.reshape(X.shape[0], C * ntaps, X.shape[1]).astype(np.float32)
+
+
+def _finish(acc, scale, bias):
+    if scale is not None:
+        acc = acc * np.asarray(scale, dtype=np.float32)[None, :, None, None]
+    if bias is not None:
+        acc = acc + np.asarray(bias, dtype=np.float32)[None, :, None, None]
+    return acc.astype(np.float32)
+
+
+def dwconv2d(X, P, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None, bias=None):
+    """Depthwise Conv2d.compact_forward (tmq/tmq.py:849-854 around ternaryDWConvFP32), restated on the image itself:
+    taps accumulate in (ky, kx) order from +0 with x = 0 outside the image; output size as torch conv2d."""
+    X = np.asarray(X, dtype=np.float32)
+    B, C, H, W = X.shape
+    (ky, kx), (sy, sx), (py, px), (dy, dx) = kernel, stride, padding, dilation
+    T = _taps(P, C, ky * kx)
+    OH = (H + 2 * py - dy * (ky - 1) - 1) // sy + 1
+    OW = (W + 2 * px - dx * (kx - 1) - 1) // sx + 1
+    Xp = np.zeros((B, C, H + 2 * py + sy, W + 2 * px + sx), dtype=np.float32)
+    Xp[:, :, py:py + H, px:px + W] = X
+    acc = np.zeros((B, C, OH, OW), dtype=np.float32)
+    for i in range(ky):
+        for j in range(kx):
+            v = Xp[:, :, i * dy:i * dy + (OH - 1) * sy + 1:sy, j * dx:j * dx + (OW - 1) * sx + 1:sx]
+            acc = acc + v * T[i * kx + j][None, :, None, None]
+    return _finish(acc, scale, bias)
+
+
+def dwconvtrans2d(X, P, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1), output_padding=(0, 0), scale=None,
+                  bias=None):
+    """Depthwise ConvTranspose2d.compact_forward (tmq/tmq.py:1025-1029: ternaryDWConvTransFP32 + F.fold) in gather
+    form: output (oy, ox) sums, in (ky, kx) order from +0, the taps whose source pixel (oy + py - i*dy) / sy is integral
+    and inside the input (x = 0 otherwise); output size as torch conv_transpose2d."""
+    X = np.asarray(X, dtype=np.float32)
+    B, C, H, W = X.shape
+    (ky, kx), (sy, sx), (py, px), (dy, dx), (opy, opx) = kernel, stride, padding, dilation, output_padding
+    T = _taps(P, C, ky * kx)
+    OH = (H - 1) * sy - 2 * py + dy * (ky - 1) + 1 + opy
+    OW = (W - 1) * sx - 2 * px + dx * (kx - 1) + 1 + opx
+    oy, ox = np.arange(OH), np.arange(OW)
+    acc = np.zeros((B, C, OH, OW), dtype=np.float32)
+    for i in range(ky):
+        ty = oy + py - i * dy
+        iy = ty // sy
+        oky = (ty >= 0) & (iy * sy == ty) & (iy < H)
+        for j in range(kx):
+            tx = ox + px - j * dx
+            ix = tx // sx
+            okx = (tx >= 0) & (ix * sx == tx) & (ix < W)
+            v = X[:, :, np.clip(iy, 0, H - 1)][:, :, :, np.clip(ix, 0, W - 1)]
+            v = np.where((oky[:, None] & okx[None, :])[None, None], v, np.float32(0.0))
+            acc = acc + v * T[i * kx + j][None, :, None, None]
+    return _finish(acc, scale, bias)

@@ -139,6 +139,41 @@ def test_gemv_baseline_shape(ops, M):
     assert torch.equal(y, y2)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 11000, 4096), (2, 2368, 4096), (3, 4096, 11008), (8, 1000, 1088),
+                                   (1, 16, 64), (2, 40, 16384), (1, 12000, 16384), (5, 200, 40000)])
+def test_gemv_resident_and_streaming_forms(ops, M, N, K):
+    """The skinny kernels in both forms: rows resident in shared memory (byte dot products for int8 with M <= 2, warp
+    MMA otherwise; channel counts that are no multiple of 16 or of the CTA count) and, where one SM's share of the
+    rows exceeds the shared-memory budget or no status word is passed, the streaming kernels."""
+    import ctypes
+    from tmq_b200 import _lib
+    W, P = make_weights(N, K, N + K + M)
+    Pd = torch.from_numpy(P).cuda()
+    rng = np.random.default_rng(M)
+    X8 = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    want8 = T.gemm_i8_fast(X8, P, N)
+    wt8 = ops.prepack(Pd, N, ops.FMT_I8)
+    y8 = ops.ternary_gemm_i8(torch.from_numpy(X8).cuda(), wt8, N, path="gemv")
+    ops.check_gemm_status()
+    assert np.array_equal(y8.cpu().numpy(), want8)
+    # no status word: the streaming kernel, same bits
+    x8d = torch.from_numpy(X8).cuda()
+    y8s = torch.empty((M, N), dtype=torch.int32, device="cuda")
+    rc = _lib.lib().tmq_ternary_gemv_i8(x8d.data_ptr(), wt8.data_ptr(), y8s.data_ptr(), M, N, K, N, None,
+                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    assert np.array_equal(y8s.cpu().numpy(), want8)
+    X = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).to(torch.bfloat16)
+    scale = torch.from_numpy((rng.random(N) * 0.09 + 0.01).astype(np.float32))
+    bias = torch.from_numpy(rng.standard_normal(N).astype(np.float32))
+    ref = T.gemm_f64_fast(X.float().numpy(), P, N) * scale.double().numpy()[None, :] + bias.double().numpy()[None, :]
+    y = ops.ternary_gemm(X.cuda(), ops.prepack(Pd, N, ops.FMT_BF16), N, scale.cuda(), bias.cuda(),
+                         out_dtype=torch.float32, path="gemv")
+    ops.check_gemm_status()
+    rms = np.sqrt((ref ** 2).mean(axis=1, keepdims=True))
+    assert np.all(np.abs(y.cpu().double().numpy() - ref) <= 1e-5 * np.maximum(np.abs(ref), rms))
+
+
 def test_full_size_prefill_shape_sampled(ops):
     """BASELINE prefill config (M = 8192, K = 8192, N = 28672) at full size: a random 96 x 96 sample of the outputs
     against fp64 dot products of the same operands (bf16 path: rel 1e-3 bar, 1e-5 expected; int8 path: bit-exact), plus

@@ -89,3 +89,33 @@ def test_nonfinite_pack_follows_x86_conversion():
     P = T.pack(W)
     vals = T.unpack(P, W.shape).flatten().tolist()
     assert vals == [-1.0, -1.0, -1.0, -1.0, -1.0, 1.0, -1.0, 0.0]
+
+
+@pytest.mark.parametrize("C,H,W,k,s,p,d,op", [(20, 9, 11, (3, 3), (1, 1), (1, 1), (1, 1), (0, 0)),
+                                              (33, 12, 10, (3, 5), (2, 1), (1, 2), (1, 1), (1, 0)),
+                                              (16, 8, 8, (5, 5), (2, 2), (2, 2), (1, 1), (1, 1)),
+                                              (7, 10, 9, (3, 3), (1, 2), (2, 1), (2, 1), (0, 1))])
+def test_depthwise_restatements_match_torch(C, H, W, k, s, p, d, op):
+    """The depthwise oracle (fixed tap order, fp32) against torch's conv2d / conv_transpose2d in fp64 on the unpacked
+    weights: equal up to fp32 rounding of at most ky*kx additions."""
+    import torch
+    rng = np.random.default_rng(C)
+    Wt = rng.integers(-1, 2, (C, 1) + k).astype(np.float32)
+    P = T.pack(Wt)
+    assert P.shape == (1,) + k + ((C + 15) // 16,)
+    x = rng.standard_normal((2, C, H, W)).astype(np.float32)
+    sc, bi = rng.random(C).astype(np.float32), rng.standard_normal(C).astype(np.float32)
+    ref = torch.nn.functional.conv2d(torch.from_numpy(x).double(), torch.from_numpy(Wt).double(), None, s, p, d, groups=C)
+    ref = ref.numpy() * sc[None, :, None, None] + bi[None, :, None, None]
+    got = T.dwconv2d(x, P, k, s, p, d, sc, bi)
+    assert got.shape == ref.shape and np.abs(got - ref).max() < 1e-5
+    reft = torch.nn.functional.conv_transpose2d(torch.from_numpy(x).double(), torch.from_numpy(Wt).double(), None, s, p, op,
+                                                C, d).numpy()
+    gott = T.dwconvtrans2d(x, P, k, s, p, d, op)
+    assert gott.shape == reft.shape and np.abs(gott - reft).max() < 1e-5
+    # operator-level forms: unfold -> patches form == image form, bit for bit
+    unf = torch.nn.functional.unfold(torch.from_numpy(x), kernel_size=k, dilation=d, stride=s, padding=p)
+    L = unf.shape[-1]
+    perm = unf.view(2, C, k[0], k[1], L).permute(0, 4, 2, 3, 1).reshape(2, L, -1).numpy()
+    pat = T.dwconv_patches(perm, P, C, k[0] * k[1]).reshape(2, L, C).transpose(0, 2, 1)
+    assert np.array_equal(pat.reshape(got.shape), T.dwconv2d(x, P, k, s, p, d))

@@ -45,17 +45,23 @@ _SIGNATURES = {
     "tmq_pack2b_i32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "tmq_pack2b_i8": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "tmq_unpack2b_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "tmq_ternary_dwconv2d_f32": (c_int, [c_void_p] * 5 + [c_int] * 12 + [c_void_p]),
+    "tmq_ternary_dwconvtrans2d_f32": (c_int, [c_void_p] * 5 + [c_int] * 14 + [c_void_p]),
+    "tmq_ternary_dwconv_patches_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "tmq_ternary_dwconvtrans_patches_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "tmq_rc_encode_bound": (c_size_t, [c_int64, c_int64]),
     "tmq_rc_encode": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_size_t, ctypes.POINTER(c_size_t)]),
     "tmq_rc_decode": (c_int, [c_void_p, c_size_t, c_void_p, c_int64, c_int64]),
-    "tmq_prepack_words": (c_size_t, [c_int64, c_int64]),
+    "tmq_prepack_row_words": (c_size_t, [c_int64, c_int]),
+    "tmq_prepack_words": (c_size_t, [c_int64, c_int64, c_int]),
     "tmq_prepack_tiled_words": (c_size_t, [c_int64, c_int64, c_int]),
     "tmq_prepack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "tmq_ternary_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                       c_int64, c_int, c_void_p, c_void_p]),
     "tmq_ternary_gemv_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-                                      c_int64, c_int, c_void_p]),
-    "tmq_ternary_gemv_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+                                      c_int64, c_int, c_void_p, c_void_p]),
+    "tmq_ternary_gemv_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
+                                    c_void_p]),
     "tmq_gemv_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "tmq_ternary_gemv_tc_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                          c_int64, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),

@@ -30,6 +30,18 @@ inline int cuda_status(cudaError_t e) {
     return TMQ_OK;
 }
 
+// Row-major prepacked weights: a row holds the K/16 packed words of one output channel (K rounded up to 64, zeros
+// beyond K) followed by padding that places consecutive rows 32 bytes (bf16-ready words, kind 0) or 64 bytes (int8-ready
+// words, kind 1) apart modulo 128.  A run of rows copied verbatim into shared memory is then read without bank
+// conflicts by the warp-fragment access pattern of the skinny kernels (8-byte / 16-byte reads, 8 rows per warp), and a
+// CTA's rows stay one contiguous byte range, i.e. one bulk copy.  The stride stays a multiple of 16 bytes (TMA).
+inline long long prepack_valid_words(long long K) { return ((K + 63) / 64) * 4; }
+inline long long prepack_row_words(long long K, int kind) {
+    const long long bytes = prepack_valid_words(K) * 4;
+    const long long want = kind ? 64 : 32;
+    return (bytes + ((want - bytes % 128) + 128) % 128) / 4;
+}
+
 inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 // Resident blocks per SM for a kernel, cached by the caller in a function-local static.

@@ -259,9 +259,9 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
 template <int BN>
 static int launch_conv(const uint32_t *Wt, const ConvArgs &a, long long K, cudaStream_t st) {
     using L = ConvSmem<BN>;
-    const long long KW = ((K + 63) / 64) * 4;
+    const long long KW = prepack_valid_words(K), KS = prepack_row_words(K, 0);
     CUtensorMap mw;
-    if (!make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KW * 4, 4, 128,
+    if (!make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KS * 4, 4, 128,
                      CU_TENSOR_MAP_SWIZZLE_NONE))
         return TMQ_ERR_LAUNCH;
     static std::once_flag once;

@@ -297,16 +297,17 @@ __device__ __forceinline__ uint32_t ref_code(const uint32_t *__restrict__ P, lon
 // Wt[tile][k-block][128 rows][words per row and k-block] (rows beyond N are zero), so that the raw tile of one
 // (128-channel tile, k-block) unit is a single contiguous 2 KB / 4 KB run.
 __global__ void __launch_bounds__(256) prepack_kernel(const uint32_t *__restrict__ P, uint32_t *__restrict__ Wt,
-                                                       long long N, long long K, long long KW, long long rows_out,
-                                                       int fmt) {
+                                                       long long N, long long K, long long KW, long long KS,
+                                                       long long rows_out, int fmt) {
+    // KW: words of a row that carry weights, KS >= KW: row stride of the row-major form (padding words are zeroed)
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= rows_out * KW) return;
+    if (idx >= rows_out * KS) return;
     // consecutive threads take consecutive n for one kw: their reads of P share 32-bit words and rows
     const long long n = idx % rows_out, kw = idx / rows_out;
     const long long Q = (N + 15) / 16;
     const int kind = fmt & 1;
     uint32_t word = 0;
-    if (n < N) {
+    if (n < N && kw < KW) {
 #pragma unroll
         for (int i = 0; i < 16; i++) {
             const uint32_t c = ref_code(P, Q, K, n, kw * 16 + i);  // 0: zero, 1: +1, 2: -1 (3 never produced -> zero)
@@ -327,7 +328,7 @@ __global__ void __launch_bounds__(256) prepack_kernel(const uint32_t *__restrict
         const long long tile = n >> 7, row = n & 127, kb = kw / wpr, wi = kw % wpr, nkb = KW / wpr;
         Wt[((tile * nkb + kb) * 128 + row) * wpr + wi] = word;
     } else {
-        Wt[n * KW + kw] = word;
+        Wt[n * KS + kw] = word;
     }
 }
 
@@ -337,14 +338,14 @@ template <int KIND, int BN>
 static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
     using KT = KindTraits<KIND>;
     using L = SmemLayout<KIND, BN>;
-    const long long KW = ((a.K + 63) / 64) * 4;  // words per prepacked row
+    const long long KW = prepack_valid_words(a.K), KS = prepack_row_words(a.K, KIND);  // words / stride of a row
     CUtensorMap mx, mw;
     const bool okx = (KIND == KIND_BF16)
         ? make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, X, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.K * 2, KT::BK, BN,
                       CU_TENSOR_MAP_SWIZZLE_128B)
         : make_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, X, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.K, KT::BK, BN,
                       CU_TENSOR_MAP_SWIZZLE_128B);
-    const bool okw = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KW * 4,
+    const bool okw = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KS * 4,
                                  KT::RAW_ROW / 4, kTileN, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!okx || !okw) return TMQ_ERR_LAUNCH;
     static std::once_flag once;
@@ -384,9 +385,14 @@ static int check_gemm_common(const void *X, const uint32_t *Wt, const void *Y, l
 
 using namespace tmq;
 
-extern "C" size_t tmq_prepack_words(int64_t N, int64_t K) {
-    if (N <= 0 || K <= 0) return 0;
-    return (size_t)N * (size_t)(((K + 63) / 64) * 4);
+extern "C" size_t tmq_prepack_row_words(int64_t K, int fmt) {
+    if (K <= 0 || fmt < 0 || fmt > 1) return 0;
+    return (size_t)prepack_row_words(K, fmt & 1);
+}
+
+extern "C" size_t tmq_prepack_words(int64_t N, int64_t K, int fmt) {
+    if (N <= 0) return 0;
+    return (size_t)N * tmq_prepack_row_words(K, fmt);
 }
 
 extern "C" size_t tmq_prepack_tiled_words(int64_t N, int64_t K, int fmt) {
@@ -402,10 +408,11 @@ extern "C" int tmq_prepack(const uint32_t *P, uint32_t *Wt, int64_t N, int64_t K
     const bool tiled = (fmt & 2) != 0;
     const long long KW = (tiled && (fmt & 1)) ? ((K + 127) / 128) * 8 : ((K + 63) / 64) * 4;
     const long long rows_out = tiled ? ((N + 127) / 128) * 128 : N;
-    const long long total = rows_out * KW;
+    const long long KS = tiled ? KW : prepack_row_words(K, fmt & 1);
+    const long long total = rows_out * KS;
     const long long blocks = (total + 255) / 256;
     if (blocks > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
-    prepack_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(P, Wt, N, K, KW, rows_out, fmt);
+    prepack_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(P, Wt, N, K, KW, KS, rows_out, fmt);
     return launch_status();
 }
 

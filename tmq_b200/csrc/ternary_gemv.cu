@@ -3,16 +3,17 @@
 //
 // Replaces the reference's batch-1 kernel (tmq/tmq_cuda.cu:242-286, launcher :563-603), which reads the packed words
 // with a stride of N/16 words between threads, multiplies by a constant-memory LUT and finishes with shared atomics.
-// Here the packed weights are streamed exactly once with 128-bit loads and HBM is the resource that should matter:
+// Here the packed weights are read exactly once and HBM is the resource that should matter.  Two forms:
 //
-//   * work split: one small CTA (4 warps) per group of 16 output channels, all of K.  Warp w takes the 256-wide
-//     K slices w, w+4, ...; lane (g, t) streams 64 consecutive k of channels g and g+8 per slice, one 16-byte load
-//     each, and issues the loads of four slices (8 loads, all independent) before it consumes any.
-//   * many CTAs are resident per SM and consecutive launches are chained with programmatic dependent launch: a CTA
-//     of launch i+1 starts as soon as an SM slot frees up and issues its weight loads (which depend on nothing)
-//     while launch i is still computing; activations and outputs are only touched after griddepcontrol.wait, i.e.
-//     after the previous kernel in the stream has completed.  A single launch cannot hide its own ramp-up latency
-//     (about as long as streaming an 11 MB matrix takes), a chain of them - which is what decoding is - can.
+//   * resident (default whenever one SM's share of the rows fits half its shared memory; see "resident variant"
+//     below): a CTA bulk-copies its rows into shared memory before it waits for its predecessor in the stream;
+//   * streaming (fallback): one small CTA (4 warps) per group of 16 output channels or a 16-warp CTA per 5 groups,
+//     weights loaded with 128-bit loads straight into registers, again before griddepcontrol.wait.
+//
+// Common to both:
+//   * consecutive launches are chained with programmatic dependent launch: weights depend on nothing, so they are
+//     requested while the previous launch is still computing; activations and outputs are only touched after
+//     griddepcontrol.wait, i.e. after the previous kernel in the stream has completed.
 //   * arithmetic: a 2-bit code costs about one integer instruction to decode, which already fills half the issue
 //     slots at HBM speed; an fp32 add/sub per weight on top (the CUDA-core formulation) cannot keep up.  The decoded
 //     codes are fed, exact, to warp-level mma (m16n8k16 bf16 / m16n8k32 s8) with the <= 8 activation rows as the 8
@@ -22,9 +23,11 @@
 // Weights use the same prepacked layout as the tensor-core GEMM (tmq_prepack, fmt 0 / 1).
 #include <cuda_bf16.h>
 
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace tmq {
 
@@ -40,7 +43,7 @@ struct GemvArgs {
     const uint32_t *Wt;     // [N][KW]
     const float *scale, *bias;
     void *Y;
-    long long M, N, K, KW, ldy;
+    long long M, N, K, KW, KS, ldy;   // KW: words of a row that carry weights, KS: row stride in words
     int out_f32;
 };
 
@@ -76,7 +79,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, TMQ_GEMV_MINB) ternary_gemv_k
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const long long r0 = (long long)blockIdx.x * 16 + g, r1 = r0 + 8;  // the two output channels of this lane
-    const uint32_t *w0 = a.Wt + r0 * a.KW, *w1 = a.Wt + r1 * a.KW;
+    const uint32_t *w0 = a.Wt + r0 * a.KS, *w1 = a.Wt + r1 * a.KS;
     const bool ok0 = r0 < a.N, ok1 = r1 < a.N;
     const int nslices = (int)((a.K + 255) / 256);
     bool waited = false;
@@ -193,7 +196,7 @@ struct WideArgs {
     const uint32_t *Wt;
     const float *scale, *bias;
     void *Y;
-    long long M, N, K, KW, ldy;
+    long long M, N, K, KW, KS, ldy;
     int groups_per_cta, nwarps, out_f32;
 };
 
@@ -230,8 +233,8 @@ __global__ void __launch_bounds__(kWideWarps * 32, 1) ternary_gemv_wide_kernel(c
             whi[i] = make_uint4(0, 0, 0, 0);
             if (i < G && group0 + i < ngroups && k_ok) {
                 const long long r0 = (group0 + i) * 16 + g, r1 = r0 + 8;
-                if (r0 < a.N) wlo[i] = ldg_stream(a.Wt + r0 * a.KW + (k_lane >> 4));
-                if (r1 < a.N) whi[i] = ldg_stream(a.Wt + r1 * a.KW + (k_lane >> 4));
+                if (r0 < a.N) wlo[i] = ldg_stream(a.Wt + r0 * a.KS + (k_lane >> 4));
+                if (r1 < a.N) whi[i] = ldg_stream(a.Wt + r1 * a.KS + (k_lane >> 4));
             }
         }
         if (!waited) {  // everything before this point read only the weights, which no kernel writes
@@ -336,6 +339,326 @@ static int launch_gemv_wide(WideArgs a, cudaStream_t st) {
     return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_wide_kernel<KIND>, a));
 }
 
+// ---- resident variant ---------------------------------------------------------------------------------------------
+//
+// One CTA per SM owns a contiguous range of channel groups and copies ALL of its packed rows (N*K/4/148 bytes: 76 KB
+// for 11008 x 4096) into shared memory BEFORE it waits for the previous kernel of the stream.  Registers are capped
+// at 64 so that two CTAs fit one SM: the CTA of launch i+1 becomes resident the moment the CTA of launch i-1
+// retires, and its rows stream from HBM while launch i decodes and multiplies.  In a chain of launches (what decoding
+// is) the weight traffic is therefore hidden entirely and the chain runs at the speed of the work that follows the
+// wait: activation fetch, decode + multiply, reduction, plus the hand-over latency between two kernels.
+//
+// The rows travel as ONE bulk copy: the TMA unit spends about 40 ns per bulk copy whatever its size (measured: 80
+// row-sized copies took 4.4 us to issue, 16 four-times larger ones 1 us), so the prepacked format itself carries the
+// row padding that keeps the fragment reads (8 rows x 8 / 16 bytes per warp) free of bank conflicts.
+//
+// Warp-level mma costs the same for 1..8 activation rows; for int8 activations with M <= 2 the four-way byte dot
+// product (dp4a) on the CUDA cores is faster than the legacy mma path on this part and is used instead.  Either way
+// the integer decode (about 0.6 - 0.8 instructions per weight) bounds the arithmetic phase.
+
+constexpr int kResWarps = 16;
+constexpr int kResGroups = 5;                 // channel groups per CTA at most
+constexpr int kResSmemMax = 110 * 1024;       // two CTAs per SM
+
+struct ResArgs {
+    const void *X;
+    const uint32_t *Wt;
+    const float *scale, *bias;
+    void *Y;
+    long long M, N, K, KW, KS, ldy;           // KS: row stride in words, in global and in shared memory
+    int ngroups, out_f32;
+    int bar_offset;                           // byte offset of the mbarrier inside dynamic shared memory
+    int *status;
+};
+
+
+// Prologue shared by both resident kernels, executed by warp 0 only and kept as short as possible: a CTA that has
+// just become resident competes for issue slots with the CTA of the previous launch, which is in the middle of its
+// arithmetic.  The other warps learn of the barrier at the __syncthreads that follows griddepcontrol.wait.
+__device__ __forceinline__ void resident_groups(const ResArgs &a, int &group0, int &G) {
+    // balanced contiguous split of the channel groups (at most 5 * 148 of them) over the CTAs
+    group0 = (int)((blockIdx.x * (unsigned)a.ngroups) / gridDim.x);
+    G = (int)(((blockIdx.x + 1) * (unsigned)a.ngroups) / gridDim.x) - group0;
+}
+__device__ __forceinline__ void resident_prologue(const ResArgs &a, uint32_t *wsm, uint64_t *bar, int group0, int G) {
+    if (threadIdx.x == 0) {
+        long long valid = a.N - (long long)group0 * 16;                // rows of this CTA that exist
+        if (valid > G * 16) valid = G * 16;
+        const uint32_t bytes = (uint32_t)(valid * a.KS * 4);            // one contiguous run: rows keep their stride
+        ptx::mbar_init(bar, 1);
+        ptx::fence_mbar_init();
+        ptx::mbar_arrive_expect_tx(bar, bytes);
+        ptx::bulk_load(wsm, a.Wt + (long long)group0 * 16 * a.KS, bytes, bar);
+    }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kResWarps * 32, 2) ternary_gemv_resident_kernel(const ResArgs a) {
+    using Acc = typename std::conditional<KIND == 0, float, int>::type;
+    constexpr int LK = (KIND == 0) ? 32 : 64;     // k per lane and slice: 2 / 4 packed words per channel
+    constexpr int LW = LK / 16;
+    extern __shared__ __align__(16) uint32_t wsm[];
+    uint64_t *bar = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(wsm) + a.bar_offset);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    int group0, G;
+    resident_groups(a, group0, G);
+    resident_prologue(a, wsm, bar, group0, G);
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // activations and outputs belong to the chain
+    __syncthreads();                                     // the barrier warp 0 initialised is visible to every warp
+
+    Acc acc[kResGroups][4];
+#pragma unroll
+    for (int i = 0; i < kResGroups; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0;
+
+    const int nslices = (int)((a.K + 4 * LK - 1) / (4 * LK));
+    constexpr int XR = 16;                         // 32 bf16 or 64 int8 activations of row g
+    uint32_t xr[XR];
+    auto load_x = [&](int slice) {                 // zero beyond M or K; K % 8 == 0 (bf16) / K % 16 == 0 (int8)
+        const long long k_lane = (long long)slice * (4 * LK) + LK * t;
+#pragma unroll
+        for (int q = 0; q < XR / 4; q++) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            const long long k = k_lane + (long long)q * (KIND == 0 ? 8 : 16);
+            if (g < a.M && k < a.K) {
+                const char *p = reinterpret_cast<const char *>(a.X) + ((long long)g * a.K + k) * (KIND == 0 ? 2 : 1);
+                v = __ldg(reinterpret_cast<const uint4 *>(p));
+            }
+            xr[4 * q + 0] = v.x; xr[4 * q + 1] = v.y; xr[4 * q + 2] = v.z; xr[4 * q + 3] = v.w;
+        }
+    };
+    load_x(warp);                                  // in flight while the last packed rows land
+    const bool ok = __syncthreads_and(ptx::mbar_wait(bar, 0, a.status));
+    for (int slice = warp; ok && slice < nslices; slice += kResWarps) {
+        if (slice != warp) load_x(slice);
+        const long long k_lane = (long long)slice * (4 * LK) + LK * t;
+        const bool k_ok = (k_lane >> 4) < a.KW;    // KW is a multiple of 4 words: a lane's words are all in or all out
+#pragma unroll
+        for (int i = 0; i < kResGroups; i++) {
+            if (i < G) {                            // warp-uniform: every lane takes part in the mma below
+                const uint32_t *p0 = wsm + (size_t)(i * 16 + g) * a.KS + (k_lane >> 4);
+                const uint32_t *p1 = p0 + (size_t)8 * a.KS;
+                uint32_t lo[LW], hi[LW];
+#pragma unroll
+                for (int w = 0; w < LW; w++) lo[w] = hi[w] = 0;
+                if (k_ok) {
+                    if (KIND == 0) {
+                        const uint2 u0 = *reinterpret_cast<const uint2 *>(p0), u1 = *reinterpret_cast<const uint2 *>(p1);
+                        lo[0] = u0.x; lo[1] = u0.y; hi[0] = u1.x; hi[1] = u1.y;
+                    } else {
+                        const uint4 u0 = *reinterpret_cast<const uint4 *>(p0), u1 = *reinterpret_cast<const uint4 *>(p1);
+                        lo[0] = u0.x; lo[1] = u0.y; lo[LW - 2] = u0.z; lo[LW - 1] = u0.w;
+                        hi[0] = u1.x; hi[1] = u1.y; hi[LW - 2] = u1.z; hi[LW - 1] = u1.w;
+                    }
+                }
+#pragma unroll
+                for (int w = 0; w < LW; w++) {
+                    if (KIND == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint32_t a0 = (lo[w] << (4 * j)) & 0xC000C000u, a2 = (lo[w] << (4 * j + 2)) & 0xC000C000u;
+                            const uint32_t a1 = (hi[w] << (4 * j)) & 0xC000C000u, a3 = (hi[w] << (4 * j + 2)) & 0xC000C000u;
+                            mma_bf16(reinterpret_cast<float(&)[4]>(acc[i]), a0, a1, a2, a3, xr[8 * w + 2 * j],
+                                     xr[8 * w + 2 * j + 1]);
+                        }
+                    } else {
+                        const uint32_t table = 0x00FF0100u;
+                        const uint32_t l0 = lo[w] & 0x33333333u, l1 = (lo[w] >> 2) & 0x33333333u;
+                        const uint32_t h0 = hi[w] & 0x33333333u, h1 = (hi[w] >> 2) & 0x33333333u;
+                        mma_s8(reinterpret_cast<int(&)[4]>(acc[i]), __byte_perm(table, 0u, l0), __byte_perm(table, 0u, h0),
+                               __byte_perm(table, 0u, l1), __byte_perm(table, 0u, h1), xr[4 * w + 0], xr[4 * w + 1]);
+                        mma_s8(reinterpret_cast<int(&)[4]>(acc[i]), __byte_perm(table, 0u, l0 >> 16),
+                               __byte_perm(table, 0u, h0 >> 16), __byte_perm(table, 0u, l1 >> 16),
+                               __byte_perm(table, 0u, h1 >> 16), xr[4 * w + 2], xr[4 * w + 3]);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();   // every warp is done reading the packed rows: the area becomes the reduction buffer
+    if (!ok) return;   // uniform: the copies never completed and the status word says so
+    Acc *red = reinterpret_cast<Acc *>(wsm);  // [warp][group][16][8]
+#pragma unroll
+    for (int i = 0; i < kResGroups; i++) {
+        if (i < G) {
+            Acc *r = red + ((size_t)(warp * kResGroups + i) * 16) * 8;
+            r[g * 8 + 2 * t] = acc[i][0];
+            r[g * 8 + 2 * t + 1] = acc[i][1];
+            r[(g + 8) * 8 + 2 * t] = acc[i][2];
+            r[(g + 8) * 8 + 2 * t + 1] = acc[i][3];
+        }
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < G * 128; o += blockDim.x) {
+        const int row = o & 15, col = (o >> 4) & 7, grp = o >> 7;
+        const long long n = ((long long)group0 + grp) * 16 + row;
+        if (n < a.N && col < a.M) {
+            Acc s = 0;
+#pragma unroll
+            for (int w = 0; w < kResWarps; w++) s += red[((size_t)(w * kResGroups + grp) * 16 + row) * 8 + col];
+            if (KIND == 1) {
+                reinterpret_cast<int *>(a.Y)[(long long)col * a.ldy + n] = (int)s;
+            } else {
+                const float sc = (a.scale ? a.scale[n] : 1.0f) * 0.5f;  // operands carried +-2.0
+                const float f = fmaf((float)s, sc, a.bias ? a.bias[n] : 0.0f);
+                if (a.out_f32) reinterpret_cast<float *>(a.Y)[(long long)col * a.ldy + n] = f;
+                else reinterpret_cast<__nv_bfloat16 *>(a.Y)[(long long)col * a.ldy + n] = __float2bfloat16_rn(f);
+            }
+        }
+    }
+}
+
+// int8 activations, MR = 1 or 2 rows: lane (g, t) of warp w owns the 64 k  [256 w + 64 t, +64)  of the channels
+// g, g+8, g+16, ... of the CTA and accumulates them with dp4a; the four t lanes and the 16 warps are then summed.
+template <int MR>
+__global__ void __launch_bounds__(kResWarps * 32, 2) ternary_gemv_resident_dp4a_kernel(const ResArgs a) {
+    constexpr int RL = 2 * kResGroups;             // channels per lane at most
+    extern __shared__ __align__(16) uint32_t wsm[];
+    uint64_t *bar = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(wsm) + a.bar_offset);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    int group0, G;
+    resident_groups(a, group0, G);
+    resident_prologue(a, wsm, bar, group0, G);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __syncthreads();                                     // the barrier warp 0 initialised is visible to every warp
+
+    int acc[RL][MR];
+#pragma unroll
+    for (int i = 0; i < RL; i++)
+#pragma unroll
+        for (int m = 0; m < MR; m++) acc[i][m] = 0;
+    const int nslices = (int)((a.K + 255) / 256);
+    uint32_t xr[MR][16];
+    auto load_x = [&](int slice) {
+        const long long k_lane = (long long)slice * 256 + 64 * t;
+#pragma unroll
+        for (int m = 0; m < MR; m++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                const long long k = k_lane + 16 * q;
+                if (m < a.M && k < a.K)
+                    v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(a.X) + (long long)m * a.K + k));
+                xr[m][4 * q + 0] = v.x; xr[m][4 * q + 1] = v.y; xr[m][4 * q + 2] = v.z; xr[m][4 * q + 3] = v.w;
+            }
+    };
+    load_x(warp);
+    const bool ok = __syncthreads_and(ptx::mbar_wait(bar, 0, a.status));
+    for (int slice = warp; ok && slice < nslices; slice += kResWarps) {
+        if (slice != warp) load_x(slice);
+        const long long k_lane = (long long)slice * 256 + 64 * t;
+        if ((k_lane >> 4) < a.KW) {
+#pragma unroll
+            for (int i = 0; i < RL; i++) {
+                if (i < 2 * G) {
+                    const uint4 u = *reinterpret_cast<const uint4 *>(wsm + (size_t)(i * 8 + g) * a.KS + (k_lane >> 4));
+                    const uint32_t words[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                    for (int w = 0; w < 4; w++) {
+                        // word w = k 16w .. 16w+15 of the lane's 64, in the order the activations sit in memory
+                        const uint32_t table = 0x00FF0100u;
+                        const uint32_t l0 = words[w] & 0x33333333u, l1 = (words[w] >> 2) & 0x33333333u;
+                        const int w0 = (int)__byte_perm(table, 0u, l0), w1 = (int)__byte_perm(table, 0u, l1);
+                        const int w2 = (int)__byte_perm(table, 0u, l0 >> 16), w3 = (int)__byte_perm(table, 0u, l1 >> 16);
+#pragma unroll
+                        for (int m = 0; m < MR; m++) {
+                            acc[i][m] = __dp4a(w0, (int)xr[m][4 * w + 0], acc[i][m]);
+                            acc[i][m] = __dp4a(w1, (int)xr[m][4 * w + 1], acc[i][m]);
+                            acc[i][m] = __dp4a(w2, (int)xr[m][4 * w + 2], acc[i][m]);
+                            acc[i][m] = __dp4a(w3, (int)xr[m][4 * w + 3], acc[i][m]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // the four t lanes of a channel
+#pragma unroll
+    for (int i = 0; i < RL; i++)
+#pragma unroll
+        for (int m = 0; m < MR; m++) {
+            acc[i][m] += __shfl_xor_sync(0xFFFFFFFFu, acc[i][m], 1);
+            acc[i][m] += __shfl_xor_sync(0xFFFFFFFFu, acc[i][m], 2);
+        }
+    __syncthreads();   // every warp is done reading the packed rows: the area becomes the reduction buffer
+    if (!ok) return;
+    int *red = reinterpret_cast<int *>(wsm);       // [warp][channel of the CTA][MR]
+    if (t == 0) {
+#pragma unroll
+        for (int i = 0; i < RL; i++)
+            if (i < 2 * G)
+#pragma unroll
+                for (int m = 0; m < MR; m++) red[(warp * (RL * 8) + i * 8 + g) * MR + m] = acc[i][m];
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < G * 16 * MR; o += blockDim.x) {
+        const int m = o % MR, row = o / MR;
+        const long long n = (long long)group0 * 16 + row;
+        if (n < a.N && m < a.M) {
+            int s = 0;
+#pragma unroll
+            for (int w = 0; w < kResWarps; w++) s += red[(w * (RL * 8) + row) * MR + m];
+            reinterpret_cast<int *>(a.Y)[(long long)m * a.ldy + n] = s;
+        }
+    }
+}
+
+template <typename Kernel>
+static int resident_attributes(Kernel kernel, int slot) {
+    static std::mutex mu;
+    static bool done[8][64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TMQ_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[slot][dev]) return TMQ_OK;
+    int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kResSmemMax));
+    if (rc == TMQ_OK) rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    if (rc == TMQ_OK) done[slot][dev] = true;
+    return rc;
+}
+
+// Returns TMQ_ERR_UNSUPPORTED when the CTA's rows do not fit the shared-memory budget (the caller then streams).
+template <int KIND>
+static int launch_gemv_resident(ResArgs a, cudaStream_t st) {
+    const long long ngroups = (a.N + 15) / 16;
+    const long long grid = ngroups < kNumSMs ? ngroups : kNumSMs;
+    const long long G = (ngroups + grid - 1) / grid;
+    if (G > kResGroups || ngroups > 0x7FFFFFFF || !a.status) return TMQ_ERR_UNSUPPORTED;
+    long long smem = G * 16 * a.KS * 4;            // the row stride already carries the bank padding
+    const long long red_bytes = (long long)kResWarps * kResGroups * 16 * 8 * 4;
+    if (smem < red_bytes) smem = red_bytes;
+    a.bar_offset = (int)smem;                      // multiple of 16
+    smem += 16;
+    if (smem > kResSmemMax) return TMQ_ERR_UNSUPPORTED;
+    a.ngroups = (int)ngroups;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kResWarps * 32);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int rc;
+    if (KIND == 1 && a.M == 1) {
+        if ((rc = resident_attributes(ternary_gemv_resident_dp4a_kernel<1>, 2)) != TMQ_OK) return rc;
+        return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_resident_dp4a_kernel<1>, a));
+    }
+    if (KIND == 1 && a.M == 2) {
+        if ((rc = resident_attributes(ternary_gemv_resident_dp4a_kernel<2>, 3)) != TMQ_OK) return rc;
+        return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_resident_dp4a_kernel<2>, a));
+    }
+    if ((rc = resident_attributes(ternary_gemv_resident_kernel<KIND>, KIND)) != TMQ_OK) return rc;
+    return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_resident_kernel<KIND>, a));
+}
+
 static int check_gemv(const void *X, const uint32_t *Wt, const void *Y, long long M, long long N, long long K,
                       long long ldy, int elem) {
     if (!X || !Wt || !Y) return TMQ_ERR_ARG;
@@ -350,17 +673,27 @@ static int check_gemv(const void *X, const uint32_t *Wt, const void *Y, long lon
 using namespace tmq;
 
 extern "C" int tmq_ternary_gemv_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y,
-                                     int64_t M, int64_t N, int64_t K, int64_t ldy, int out_f32, void *stream) {
+                                     int64_t M, int64_t N, int64_t K, int64_t ldy, int out_f32, int *status, void *stream) {
     int rc = check_gemv(X, Wt, Y, M, N, K, ldy, 2);
     if (rc != TMQ_OK) return rc;
-    WideArgs a = {X, Wt, scale, bias, Y, M, N, K, ((K + 63) / 64) * 4, ldy, 0, 0, out_f32};
+    if (status) {   // resident form; falls through when one SM's share of the rows exceeds the shared-memory budget
+        ResArgs r = {X, Wt, scale, bias, Y, M, N, K, prepack_valid_words(K), prepack_row_words(K, 0), ldy, 0, out_f32, 0, status};
+        rc = launch_gemv_resident<0>(r, (cudaStream_t)stream);
+        if (rc != TMQ_ERR_UNSUPPORTED) return rc;
+    }
+    WideArgs a = {X, Wt, scale, bias, Y, M, N, K, prepack_valid_words(K), prepack_row_words(K, 0), ldy, 0, 0, out_f32};
     return launch_gemv_wide<0>(a, (cudaStream_t)stream);
 }
 
 extern "C" int tmq_ternary_gemv_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K,
-                                   int64_t ldy, void *stream) {
+                                   int64_t ldy, int *status, void *stream) {
     int rc = check_gemv(X, Wt, Y, M, N, K, ldy, 1);
     if (rc != TMQ_OK) return rc;
-    GemvArgs a = {X, Wt, nullptr, nullptr, Y, M, N, K, ((K + 63) / 64) * 4, ldy, 0};
+    if (status) {
+        ResArgs r = {X, Wt, nullptr, nullptr, Y, M, N, K, prepack_valid_words(K), prepack_row_words(K, 1), ldy, 0, 0, 0, status};
+        rc = launch_gemv_resident<1>(r, (cudaStream_t)stream);
+        if (rc != TMQ_ERR_UNSUPPORTED) return rc;
+    }
+    GemvArgs a = {X, Wt, nullptr, nullptr, Y, M, N, K, prepack_valid_words(K), prepack_row_words(K, 1), ldy, 0};
     return launch_gemv<1>(a, (cudaStream_t)stream);
 }

@@ -313,9 +313,16 @@ def gemv_workspace(device, nbytes):
     return buf
 
 
+def prepack_row_words(k, fmt):
+    """Row stride (int32 words) of the row-major prepacked formats for K = k: the K/16 words (K rounded up to 64) plus
+    the padding that keeps rows copied into shared memory free of bank conflicts."""
+    return int(lib().tmq_prepack_row_words(int(k), int(fmt) & 1))
+
+
 def prepack(packed, columns, fmt=FMT_BF16):
-    """Reference-layout packed weights int32 [K, ceil(N/16)] (or the 4-D conv form) -> prepacked int32 [N, Kp/16]
-    in the bit order the GEMM kernels decode (fmt: FMT_BF16 or FMT_I8).  Done once per weight tensor."""
+    """Reference-layout packed weights int32 [K, ceil(N/16)] (or the 4-D conv form) -> prepacked int32
+    [N, prepack_row_words(K, fmt)] in the bit order the GEMM kernels decode (fmt: FMT_BF16 or FMT_I8).  Done once per
+    weight tensor."""
     if packed.dtype != torch.int32 or packed.device.type != "cuda":
         raise RuntimeError("prepack: expected a CUDA int32 tensor")
     N = int(columns)
@@ -325,8 +332,7 @@ def prepack(packed, columns, fmt=FMT_BF16):
     if fmt in (FMT_BF16_TILED, FMT_I8_TILED):
         out = torch.empty(lib().tmq_prepack_tiled_words(N, K, int(fmt)), dtype=torch.int32, device=p.device)
     else:
-        words = lib().tmq_prepack_words(N, K)
-        out = torch.empty((N, words // N), dtype=torch.int32, device=p.device)
+        out = torch.empty((N, lib().tmq_prepack_row_words(K, int(fmt))), dtype=torch.int32, device=p.device)
     with torch.cuda.device(p.device):
         check(lib().tmq_prepack(_ptr(p), _ptr(out), N, K, int(fmt), _stream(p)), "prepack")
     return out
@@ -343,8 +349,8 @@ def _pick_path(path, M, have_tiled):
 
 
 def _check_weights(name, wt, N, K, wt_tiled, fmt_tiled):
-    if wt is not None and (wt.dtype != torch.int32 or wt.dim() != 2 or wt.shape[0] != N
-                           or wt.shape[1] != (K + 63) // 64 * 4):
+    if wt is not None and (wt.dtype != torch.int32 or wt.dim() != 2 or wt.shape[0] != N or not wt.is_contiguous()
+                           or wt.shape[1] != lib().tmq_prepack_row_words(K, fmt_tiled & 1)):
         raise RuntimeError(f"{name}: prepacked weights do not match the problem shape")
     if wt_tiled is not None and (wt_tiled.dtype != torch.int32
                                  or wt_tiled.numel() != lib().tmq_prepack_tiled_words(N, K, fmt_tiled)):
@@ -384,10 +390,11 @@ def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16
                                                  ws.numel(), _ptr(st), _stream(x)), "ternary_gemv_tc")
         elif path == "gemv":
             esz = y.element_size()
+            st = gemm_status_word(x.device)
             for m0 in range(0, M, 8):
                 check(lib().tmq_ternary_gemv_bf16(ctypes.c_void_p(x.data_ptr() + m0 * K * 2), _ptr(wt), psc, pbi,
                                                   ctypes.c_void_p(y.data_ptr() + m0 * N * esz), min(8, M - m0), N, K, N,
-                                                  f32, _stream(x)), "ternary_gemv")
+                                                  f32, _ptr(st), _stream(x)), "ternary_gemv")
         elif path == "tiles":
             st = gemm_status_word(x.device)
             check(lib().tmq_ternary_gemm_bf16(_ptr(x), _ptr(wt), psc, pbi, _ptr(y), M, N, K, N, f32, _ptr(st),
@@ -420,10 +427,11 @@ def ternary_gemm_i8(x, wt, columns, path="auto", wt_tiled=None):
             check(lib().tmq_ternary_gemv_tc_i8(_ptr(x), _ptr(wt_tiled), _ptr(y), M, N, K, N, _ptr(ws), ws.numel(),
                                                _ptr(st), _stream(x)), "ternary_gemv_tc_i8")
         elif path == "gemv":
+            st = gemm_status_word(x.device)
             for m0 in range(0, M, 8):
                 check(lib().tmq_ternary_gemv_i8(ctypes.c_void_p(x.data_ptr() + m0 * K), _ptr(wt),
                                                 ctypes.c_void_p(y.data_ptr() + m0 * N * 4), min(8, M - m0), N, K, N,
-                                                _stream(x)), "ternary_gemv_i8")
+                                                _ptr(st), _stream(x)), "ternary_gemv_i8")
         elif path == "tiles":
             st = gemm_status_word(x.device)
             check(lib().tmq_ternary_gemm_i8(_ptr(x), _ptr(wt), _ptr(y), M, N, K, N, _ptr(st), _stream(x)),
@@ -431,6 +439,8 @@ def ternary_gemm_i8(x, wt, columns, path="auto", wt_tiled=None):
         else:
             raise ValueError(f"ternary_gemm_i8: unknown path {path!r}")
     return y
+
+
 HAVE_IMPLICIT_CONV = True
 
 
@@ -463,7 +473,7 @@ def ternary_conv2d_nhwc(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), d
     n = int(columns)
     if c % 64 != 0:
         raise RuntimeError("ternary_conv2d_nhwc: the channel count must be a multiple of 64")
-    if wt.dtype != torch.int32 or wt.shape[0] != n or wt.shape[1] != (ky * kx * c + 63) // 64 * 4:
+    if wt.dtype != torch.int32 or wt.shape[0] != n or wt.shape[1] != prepack_row_words(ky * kx * c, FMT_BF16):
         raise RuntimeError("ternary_conv2d_nhwc: prepacked weights do not match the problem shape")
     oh = (h + 2 * py - dy * (ky - 1) - 1) // sy + 1
     ow = (w + 2 * px - dx * (kx - 1) - 1) // sx + 1
@@ -482,3 +492,156 @@ def ternary_conv2d_nhwc(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), d
                                             py, px, dy, dx, 1 if relu else 0, _ptr(st), _stream(x)),
               "ternary_conv2d_nhwc")
     return y
+
+
+# ---- depthwise convolutions ------------------------------------------------------------------------------------------
+
+def _dw_args(name, x, weights):
+    if x.dtype != torch.float32 or x.device.type != "cuda":
+        raise RuntimeError(f"{name}: expected a CUDA float32 activation tensor")
+    if weights.dtype != torch.int32 or weights.device != x.device:
+        raise RuntimeError(f"{name}: expected int32 packed weights on the activations' device")
+    return x.contiguous(), weights.contiguous()
+
+
+def _opt_f32(t, device):
+    return None if t is None else t.to(device=device, dtype=torch.float32).contiguous()
+
+
+def ternary_dwconv2d(x, weights, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None, bias=None):
+    """Depthwise ternary convolution straight from the image: x fp32 NCHW [B, C, H, W], weights = packed
+    [1, ky, kx, ceil(C/16)] (the reference's compact form of a [C, 1, ky, kx] kernel) -> fp32 [B, C, OH, OW] with torch
+    conv2d's output size; optional per-channel scale and bias."""
+    x, weights = _dw_args("ternary_dwconv2d", x, weights)
+    if x.dim() != 4:
+        raise RuntimeError("ternary_dwconv2d: expected a 4-D NCHW tensor")
+    b, c, h, w = x.shape
+    (ky, kx), (sy, sx), (py, px), (dy, dx) = kernel, stride, padding, dilation
+    if weights.numel() != ky * kx * ((c + 15) // 16):
+        raise RuntimeError("ternary_dwconv2d: packed weights do not match the channel count and kernel size")
+    oh = (h + 2 * py - dy * (ky - 1) - 1) // sy + 1
+    ow = (w + 2 * px - dx * (kx - 1) - 1) // sx + 1
+    y = torch.empty((b, c, oh, ow), dtype=torch.float32, device=x.device)
+    sc, bi = _opt_f32(scale, x.device), _opt_f32(bias, x.device)
+    with torch.cuda.device(x.device):
+        check(lib().tmq_ternary_dwconv2d_f32(_ptr(x), _ptr(weights), _ptr(sc) if sc is not None else None,
+                                             _ptr(bi) if bi is not None else None, _ptr(y), b, c, h, w, ky, kx, sy, sx,
+                                             py, px, dy, dx, _stream(x)), "ternary_dwconv2d")
+    return y
+
+
+def ternary_dwconvtrans2d(x, weights, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1), output_padding=(0, 0),
+                          scale=None, bias=None):
+    """Depthwise ternary transposed convolution straight from the image (torch conv_transpose2d's output size)."""
+    x, weights = _dw_args("ternary_dwconvtrans2d", x, weights)
+    if x.dim() != 4:
+        raise RuntimeError("ternary_dwconvtrans2d: expected a 4-D NCHW tensor")
+    b, c, h, w = x.shape
+    (ky, kx), (sy, sx), (py, px), (dy, dx), (opy, opx) = kernel, stride, padding, dilation, output_padding
+    if weights.numel() != ky * kx * ((c + 15) // 16):
+        raise RuntimeError("ternary_dwconvtrans2d: packed weights do not match the channel count and kernel size")
+    oh = (h - 1) * sy - 2 * py + dy * (ky - 1) + 1 + opy
+    ow = (w - 1) * sx - 2 * px + dx * (kx - 1) + 1 + opx
+    y = torch.empty((b, c, oh, ow), dtype=torch.float32, device=x.device)
+    sc, bi = _opt_f32(scale, x.device), _opt_f32(bias, x.device)
+    with torch.cuda.device(x.device):
+        check(lib().tmq_ternary_dwconvtrans2d_f32(_ptr(x), _ptr(weights), _ptr(sc) if sc is not None else None,
+                                                  _ptr(bi) if bi is not None else None, _ptr(y), b, c, h, w, ky, kx, sy,
+                                                  sx, py, px, dy, dx, opy, opx, _stream(x)), "ternary_dwconvtrans2d")
+    return y
+
+
+# ---- the reference's operator names (tmq/tmq_cuda.cu:800-809), same argument meaning ----------------------------------
+
+def ternary_dwconv_cuda(x, weights, kx, ky, channels):
+    """x fp32 [B, 1, P, kx*ky*C] / [B, P, kx*ky*C] / [P, kx*ky*C] (taps outermost, channels fastest) -> the same rank
+    with `channels` as the last dimension [tmq/tmq_cuda.cu:607-644].  Every batch element is processed (the
+    reference's launch only covers the first)."""
+    x, weights = _dw_args("ternary_dwconv_cuda", x, weights)
+    ntaps, c = int(kx) * int(ky), int(channels)
+    if x.dim() not in (2, 3, 4) or (x.dim() == 4 and x.shape[1] != 1) or x.shape[-1] != ntaps * c:
+        raise RuntimeError("ternary_dwconv_cuda: expected [.., pixels, kx*ky*channels] activations")
+    if weights.numel() != ntaps * ((c + 15) // 16):
+        raise RuntimeError("ternary_dwconv_cuda: packed weights do not match the channel count and kernel size")
+    y = torch.empty(tuple(x.shape[:-1]) + (c,), dtype=torch.float32, device=x.device)
+    rows = x.numel() // (ntaps * c)
+    if rows:
+        with torch.cuda.device(x.device):
+            check(lib().tmq_ternary_dwconv_patches_f32(_ptr(x), _ptr(weights), _ptr(y), rows, c, ntaps, _stream(x)),
+                  "ternary_dwconv_cuda")
+    return y
+
+
+def ternary_dwconvtrans_cuda(x, weights, kx, ky):
+    """x fp32 [B, 1, P, C] / [B, P, C] / [P, C], weights packed [1, ky, kx, ceil(C/16)] -> [.., C*kx*ky, P] columns for
+    F.fold [tmq/tmq_cuda.cu:647-686]."""
+    x, weights = _dw_args("ternary_dwconvtrans_cuda", x, weights)
+    if x.dim() not in (2, 3, 4) or (x.dim() == 4 and x.shape[1] != 1):
+        raise RuntimeError("ternary_dwconvtrans_cuda: expected [.., pixels, channels] activations")
+    ntaps, c, p = int(kx) * int(ky), int(x.shape[-1]), int(x.shape[-2])
+    if weights.dim() != 4 or tuple(weights.shape) != (1, int(ky), int(kx), (c + 15) // 16):
+        raise RuntimeError("ternary_dwconvtrans_cuda: expected packed weights of shape [1, ky, kx, ceil(C/16)]")
+    b = x.numel() // (p * c)
+    y = torch.empty(tuple(x.shape[:-2]) + (c * ntaps, p), dtype=torch.float32, device=x.device)
+    if x.numel():
+        with torch.cuda.device(x.device):
+            check(lib().tmq_ternary_dwconvtrans_patches_f32(_ptr(x), _ptr(weights), _ptr(y), b, p, c, ntaps, _stream(x)),
+                  "ternary_dwconvtrans_cuda")
+    return y
+
+
+_f32_weights = {}      # (data_ptr, version, shape, columns, k) -> three stacked copies of the weights, prepacked
+
+
+def _stacked_prepack(weights, columns, k8):
+    key = (weights.data_ptr(), weights._version, tuple(weights.shape), int(columns), k8, str(weights.device))
+    hit = _f32_weights.get(key)
+    if hit is None:
+        if len(_f32_weights) >= 64:
+            _f32_weights.clear()
+        p = weights.contiguous().view(-1, weights.shape[-1])
+        if k8 > p.shape[0]:
+            p = torch.nn.functional.pad(p, (0, 0, 0, k8 - p.shape[0]))
+        hit = prepack(torch.cat([p, p, p], dim=0), columns, FMT_BF16)
+        _f32_weights[key] = hit
+    return hit
+
+
+def ternary_gemm_f32(x2d, weights, columns, scale=None, bias=None):
+    """fp32 activations [M, K] x reference-layout packed weights int32 [K, ceil(N/16)] -> fp32 [M, N].  x is split
+    exactly into three bf16 terms (hi + mid + lo) that ride along K against three stacked copies of the weights:
+    every product is exact, accumulation is fp32 on the tensor cores."""
+    if x2d.dtype != torch.float32 or x2d.device.type != "cuda" or x2d.dim() != 2:
+        raise RuntimeError("ternary_gemm_f32: expected a 2-D CUDA float32 tensor")
+    if weights.dtype != torch.int32 or weights.device != x2d.device:
+        raise RuntimeError("ternary_gemm_f32: expected int32 packed weights on the activations' device")
+    k = x2d.shape[1]
+    rows = weights.numel() // weights.shape[-1]
+    if rows != k:
+        raise RuntimeError("ternary_gemm_f32: activation width does not match the packed weights")
+    pad = (-k) % 8
+    if pad:
+        x2d = torch.nn.functional.pad(x2d, (0, pad))
+    hi = x2d.to(torch.bfloat16)
+    r1 = x2d - hi.float()
+    mid = r1.to(torch.bfloat16)
+    lo = (r1 - mid.float()).to(torch.bfloat16)
+    return ternary_gemm(torch.cat([hi, mid, lo], dim=1), _stacked_prepack(weights, columns, k + pad), int(columns), scale,
+                        bias, out_dtype=torch.float32)
+
+
+def ternary_mmm_cuda(x, weights, columns):
+    """x fp32 [M, K] / [B, M, K] / [1, B, M, K], weights int32 [K, ceil(N/16)] -> fp32 [.., M, N]
+    [tmq/tmq_cuda.cu:478-549]; one launch for the whole batch."""
+    if x.dim() not in (2, 3, 4) or (x.dim() == 4 and x.shape[0] != 1):
+        raise RuntimeError("ternary_mmm_cuda: expected [M, K], [B, M, K] or [1, B, M, K] activations")
+    y = ternary_gemm_f32(x.contiguous().view(-1, x.shape[-1]), weights, columns)
+    return y.view(tuple(x.shape[:-1]) + (int(columns),))
+
+
+def ternary_mvm_cuda(x, weights, columns):
+    """x fp32 [K] / [1, K] / [1, 1, K] / [1, 1, 1, K] -> fp32 [.., N] [tmq/tmq_cuda.cu:563-603]."""
+    if x.dim() not in (1, 2, 3, 4) or any(int(s) != 1 for s in x.shape[:-1]):
+        raise RuntimeError("ternary_mvm_cuda: expected a single activation row")
+    y = ternary_gemm_f32(x.contiguous().view(1, -1), weights, columns)
+    return y.view(tuple(x.shape[:-1]) + (int(columns),))

@@ -414,8 +414,8 @@ class TMQLayer:
         tag = (w.data_ptr(), w._version, tuple(w.shape), str(w.device))
         hit = self._prepacked.get(key)
         if hit is None or hit[0] != tag:
-            n_out = int(self.original_shape[0])
-            packed = w.contiguous().view(-1, w.shape[-1])
+            n_out = self._gemm_columns()
+            packed = self._packed_matrix()
             if k_each is not None and k_each > packed.shape[0]:
                 packed = torch.nn.functional.pad(packed, (0, 0, 0, k_each - packed.shape[0]))
             if k_repeat > 1:
@@ -424,21 +424,31 @@ class TMQLayer:
             self._prepacked[key] = hit
         return hit[1]
 
-    def _compact_matmul(self, x2d):
-        """[M, K] activations x packed weights -> [M, N] with post_scale and bias fused into the epilogue.
-        fp32 in -> fp32 out (exact split), bf16 in -> bf16 out, int8 in -> int32 out (no scale / bias)."""
-        n_out = int(self.original_shape[0])
+    def _gemm_columns(self):
+        """Output width N of the layer's GEMM."""
+        return int(self.original_shape[0])
+
+    def _packed_matrix(self):
+        """The layer's weights as the 2-D reference-layout packed matrix int32 [K, ceil(N/16)] of its GEMM."""
+        w = self.weight.data
+        return w.contiguous().view(-1, w.shape[-1])
+
+    def _compact_matmul(self, x2d, fuse=True):
+        """[M, K] activations x packed weights -> [M, N] with post_scale and bias fused into the epilogue (fuse=False:
+        the bare product).  fp32 in -> fp32 out (exact split), bf16 in -> bf16 out, int8 in -> int32 out (no scale /
+        bias)."""
+        n_out = self._gemm_columns()
         k = x2d.shape[1]
         scale = None
-        if self.post_scale_imm != 1.0:
+        if fuse and self.post_scale_imm != 1.0:
             scale = torch.full((n_out,), float(self.post_scale_imm), dtype=torch.float32, device=x2d.device)
-        bias = getattr(self, "bias", None)
+        bias = getattr(self, "bias", None) if fuse else None
         if x2d.dtype == torch.int8:
             pad = (-k) % 16
             if pad:
                 x2d = torch.nn.functional.pad(x2d, (0, pad))
             wt = self._prepacked_weights(ops.FMT_I8)
-            if wt.shape[1] != (x2d.shape[1] + 63) // 64 * 4:
+            if wt.shape[1] != ops.prepack_row_words(x2d.shape[1], ops.FMT_I8):
                 raise RuntimeError("compact inference: activation width does not match the packed weights")
             return ops.ternary_gemm_i8(x2d, wt, n_out)
         if x2d.dtype == torch.bfloat16:
@@ -611,11 +621,19 @@ class Conv2d(nn.Module, TMQLayer):
             return self.compact_forward(x.unsqueeze(0)).squeeze(0)
         if x.dim() != 4:
             raise Exception("Expected a 3D tensor")
-        if self.groups != 1:
-            raise NotImplementedError("compact inference of grouped / depthwise convolutions is not part of tmq_b200")
         b, c, h, w = x.shape
         (ky, kx), (sy, sx) = _pair(self.kernel), _pair(self.stride)
         (py, px), (dy, dx) = _pair(self.padding), _pair(self.dilation)
+        if self.groups != 1:
+            # depthwise: straight from the image, no unfold / fold [tmq/tmq.py:849-854]
+            assert self.groups == self.original_shape[0] == c, \
+                "Grouped convolutions are only supported for group == channels"
+            if x.dtype != torch.float32:
+                raise RuntimeError("compact inference of depthwise convolutions takes float32 activations")
+            scale = None
+            if self.post_scale_imm != 1.0:
+                scale = torch.full((c,), float(self.post_scale_imm), dtype=torch.float32, device=x.device)
+            return ops.ternary_dwconv2d(x, self.weight.data, (ky, kx), (sy, sx), (py, px), (dy, dx), scale, self.bias)
         h_out = (h + 2 * py - dy * (ky - 1) - 1) // sy + 1
         w_out = (w + 2 * px - dx * (kx - 1) - 1) // sx + 1
         if ky == 1 and kx == 1 and py == 0 and px == 0:
@@ -682,10 +700,55 @@ class ConvTranspose2d(Conv2d):
         return torch.nn.functional.conv_transpose2d(x, w, bias, self.stride, self.padding, dilation=self.dilation,
                                                     groups=self.groups)
 
+    def _gemm_columns(self):
+        ky, kx = _pair(self.kernel)
+        return int(self.original_shape[1]) * ky * kx
+
+    def _packed_matrix(self):
+        """groups == 1: out[pixel][(o, ky, kx)] = sum_i x[pixel][i] * w[i][o][ky][kx], so the GEMM's weight matrix is
+        [N = (o, ky, kx)][K = i]; the stored packed tensor [o, ky, kx, ceil(i/16)] is re-packed along N once."""
+        w4 = ops.expand_ternary(self.weight.data, list(self.original_shape))          # fp32 [i, o, ky, kx]
+        return ops.compactify_ternary(w4.reshape(w4.shape[0], -1).t().contiguous())    # [K = i, ceil(N/16)]
+
     @torch.no_grad()
     def compact_forward(self, x):
-        raise NotImplementedError("compact inference of transposed convolutions is not part of tmq_b200; "
-                                  "use expand_compact_layers() to run this layer from fp32 weights")
+        """Transposed convolution from packed weights with torch conv_transpose2d's output geometry.  Depthwise
+        (groups == channels): one gather kernel straight from the image.  groups == 1: tensor-core GEMM to columns,
+        then F.fold [tmq/tmq.py:1007-1042; the reference passes mismatched operands to its GEMM there]."""
+        assert not self.training, "Compact inference is not supported in training mode"
+        assert self.weight.data.dtype == torch.int32, "Compact inference requires 32-bit integer words"
+        _require_cuda(x, "compact_forward")
+        self._update_scale()
+        if x.dim() == 3:
+            return self.compact_forward(x.unsqueeze(0)).squeeze(0)
+        if x.dim() != 4:
+            raise Exception("Expected a 3D tensor")
+        if x.dtype != torch.float32:
+            raise RuntimeError("compact inference of transposed convolutions takes float32 activations")
+        b, c, h, w = x.shape
+        (ky, kx), (sy, sx) = _pair(self.kernel), _pair(self.stride)
+        (py, px), (dy, dx) = _pair(self.padding), _pair(self.dilation)
+        opy, opx = _pair(self.output_padding)
+        assert self.groups == 1 or self.groups == self.in_channels, \
+            "Grouped transpose convolutions are only supported for channels == groupsize"
+        n_out = int(self.original_shape[1]) * self.groups
+        scale = None
+        if self.post_scale_imm != 1.0:
+            scale = torch.full((n_out,), float(self.post_scale_imm), dtype=torch.float32, device=x.device)
+        if self.groups != 1:
+            assert int(self.original_shape[1]) == 1, "depthwise transposed convolutions keep the channel count"
+            return ops.ternary_dwconvtrans2d(x, self.weight.data, (ky, kx), (sy, sx), (py, px), (dy, dx), (opy, opx),
+                                             scale, self.bias)
+        h_out = (h - 1) * sy - 2 * py + dy * (ky - 1) + 1 + opy
+        w_out = (w - 1) * sx - 2 * px + dx * (kx - 1) + 1 + opx
+        cols = self._compact_matmul(x.permute(0, 2, 3, 1).reshape(b * h * w, c), fuse=False)    # [B*H*W, O*ky*kx]
+        final = torch.nn.functional.fold(cols.view(b, h * w, -1).transpose(1, 2), output_size=(h_out, w_out),
+                                         kernel_size=(ky, kx), dilation=(dy, dx), stride=(sy, sx), padding=(py, px))
+        if scale is not None:
+            final = final * self.post_scale_imm
+        if self.bias is not None:
+            final = self.bias.view(1, -1, 1, 1) + final
+        return final
 
     @classmethod
     def from_transconv2d(cls, source: nn.ConvTranspose2d, name: str, ctrl: QuantizationControl):
