@@ -452,6 +452,30 @@ def run_workload(args):
                 "config": {"workload": f"ternary_gemv_M{Mg}_N11008_K4096", "matrices": NM,
                            "note": "stream launches (no CUDA graph): includes launch gaps; the headline GEMV number is "
                                    "the graph protocol of the default run"}}
+    elif args.workload in ("dwconv", "dwconvtrans"):
+        # depthwise compact convolution straight from the image: MobileNet-like 3x3, fp32 NCHW, batch sharded over ranks
+        Bt, C, H, W = 256 // world, 128, 56, 56
+        gen = torch.Generator(device=dev).manual_seed(rank)
+        Wt = torch.randint(-1, 2, (C, 1, 3, 3), generator=gen, device=dev).float()
+        Pk = ops.compactify_ternary(Wt)
+        sc = torch.rand(C, generator=gen, device=dev) + 0.5
+        bi = torch.randn(C, generator=gen, device=dev)
+        xs = [torch.randn(Bt, C, H, W, generator=gen, device=dev) for _ in range(2)]      # 2 x 411 MB > L2
+        if args.workload == "dwconv":
+            fn = lambda x: ops.ternary_dwconv2d(x, Pk, (3, 3), (1, 1), (1, 1), (1, 1), sc, bi)
+        else:
+            fn = lambda x: ops.ternary_dwconvtrans2d(x, Pk, (3, 3), (1, 1), (1, 1), (1, 1), (0, 0), sc, bi)
+        y = fn(xs[0])
+        ms = timed(lambda i: fn(xs[i & 1]), args.steps, args.warmup)
+        nbytes = xs[0].numel() * 4 + y.numel() * 4
+        line = {"metric": f"ternary_{args.workload}2d_f32_GBps", "value": world * nbytes / ms / 1e6, "unit": "GB/s",
+                "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"depthwise_3x3_B{Bt * world}_C{C}_{H}x{W}", "l2": "two alternating inputs of 411 MB"},
+                "gpu_launches": args.steps,
+                "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind,
+                             "algorithmic_bytes_per_launch": nbytes}}
     elif args.workload == "gemm":
         M, K, N = args.gemm_m, args.gemm_k, args.gemm_n
         P = _ternary_packed(ops, N, K, 0)                         # same seed on every rank: the same matrix
@@ -525,7 +549,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-extra", action="store_true", help="skip the ternary GEMM / GEMV sections")
-    ap.add_argument("--workload", default="softstep", choices=["softstep", "gemm", "gemv", "resnet_qat", "resnet_infer"])
+    ap.add_argument("--workload", default="softstep", choices=["softstep", "gemm", "gemv", "resnet_qat", "resnet_infer", "dwconv", "dwconvtrans"])
     ap.add_argument("--gemm-m", type=int, default=8192)
     ap.add_argument("--gemm-k", type=int, default=8192)
     ap.add_argument("--gemm-n", type=int, default=28672)

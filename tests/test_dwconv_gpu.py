@@ -16,6 +16,15 @@ GEOMS = [  # C, H, W, kernel, stride, padding, dilation, output_padding
     (64, 28, 28, (3, 3), (1, 1), (1, 1), (1, 1), (0, 0)),
     (5, 6, 7, (1, 1), (1, 1), (0, 0), (1, 1), (0, 0)),
     (48, 5, 5, (7, 7), (1, 1), (3, 3), (1, 1), (0, 0)),
+    (8, 20, 130, (5, 5), (1, 1), (2, 2), (1, 1), (0, 0)),      # several tiles in x, tiled kernel
+    (3, 17, 70, (3, 3), (1, 1), (0, 0), (1, 1), (0, 0)),       # output width not a multiple of 4
+    (4, 33, 65, (7, 7), (1, 1), (1, 2), (1, 1), (0, 0)),
+    (40, 12, 12, (5, 5), (1, 1), (0, 0), (1, 1), (0, 0)),      # marching kernel: no padding, width shrinks by 4
+    (9, 20, 132, (5, 5), (1, 1), (2, 2), (1, 1), (0, 0)),      # marching kernel: several warps per row
+    (48, 8, 8, (7, 7), (1, 1), (3, 3), (1, 1), (0, 0)),
+    (6, 10, 16, (3, 3), (1, 1), (0, 0), (1, 1), (0, 0)),
+    (130, 7, 4, (3, 3), (1, 1), (1, 1), (1, 1), (0, 0)),       # one chunk per row
+    (5, 6, 8, (3, 3), (1, 1), (2, 1), (1, 1), (0, 0)),         # taller padding than "same"
 ]
 
 

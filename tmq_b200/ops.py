@@ -339,11 +339,12 @@ def prepack(packed, columns, fmt=FMT_BF16):
 
 
 def _pick_path(path, M, have_tiled):
+    """auto: up to 16 rows go through the skinny kernel in passes of 8 (measured faster than one 32-row tensor-core
+    tile there), anything taller through the tiled tensor-core kernel.  "tc" (persistent stream-K skinny kernel on
+    tile-contiguous weights) is never chosen automatically: it measures slower than both."""
     if path != "auto":
         return path
-    if M <= GEMV_MAX_ROWS and have_tiled:
-        return "tc"
-    if M <= 8:
+    if M <= 16:
         return "gemv"
     return "tiles"
 
