@@ -37,11 +37,12 @@ namespace tmq {
 
 constexpr int kGemmThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2-5: decode, warps 6-9: epilogue
 constexpr int kTileN = 128;    // weight rows (output channels) per CTA = UMMA M
-// pipeline depth per activation-tile height (two 128-row CTAs per SM with 3 stages measured 20 % slower than one
-// 256-row CTA with 4)
-template <int BN>
+// Pipeline depth: four stages when the decoded weight tile sits in shared memory (one 256-row CTA with 4 stages
+// measured 20 % faster than two 128-row CTAs per SM with 3); with the weight tile in tensor memory a stage is only the
+// activation tile plus the raw packed words, and shared memory holds six of the largest.
+template <int BN, bool TA>
 struct StagesFor {
-    static constexpr int value = 4;
+    static constexpr int value = TA ? (BN > 128 ? 6 : 8) : 4;
 };
 constexpr int kRowBytes = 128; // bytes of one operand row per k-block (64 bf16 or 128 int8)
 
@@ -71,10 +72,10 @@ struct KindTraits<KIND_I8> {
     static constexpr uint32_t C_FMT = 2u;  // s32 accumulator
 };
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool TA>
 struct SmemLayout {
-    static constexpr int kStages = StagesFor<BN>::value;
-    static constexpr int A_BYTES = kTileN * kRowBytes;                       // 16 KB
+    static constexpr int kStages = StagesFor<BN, TA>::value;
+    static constexpr int A_BYTES = TA ? 0 : kTileN * kRowBytes;              // 16 KB, or none: operand in tensor memory
     static constexpr int B_BYTES = BN * kRowBytes;
     static constexpr int RAW_BYTES = kTileN * KindTraits<KIND>::RAW_ROW;     // 2 KB / 4 KB
     static constexpr int A_OFF = 0;
@@ -92,11 +93,14 @@ struct SmemLayout {
 // the accumulator is double-buffered in TMEM (2 x BN columns): four dedicated epilogue warps drain tile i while tile
 // i+1 is being multiplied.
 
-template <int KIND, int BN>
+// TA: the decoded weight tile (A operand) lives in tensor memory instead of shared memory.  Per k-block that takes the
+// 16 KB decode write and the 16 KB operand read off shared memory, whose bandwidth otherwise bounds the kernel; the
+// accumulator is then single-buffered for 256-row activation tiles (512 TMEM columns: 256 + 4 x 32 for the A ring).
+template <int KIND, int BN, bool TA>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, GemmArgs args) {
     using KT = KindTraits<KIND>;
-    using L = SmemLayout<KIND, BN>;
+    using L = SmemLayout<KIND, BN, TA>;
     constexpr int kStages = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -113,7 +117,13 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     const long long tiles_m = (args.M + BN - 1) / BN;
     const long long ntiles = tiles_n * tiles_m;
     constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;
-    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
+    constexpr int ACC_BUFS = (TA && BN > 128) ? 1 : 2;
+    constexpr uint32_t A_COLS = kRowBytes / 4;                       // one k-block of a row: 32 columns
+    constexpr uint32_t A_BASE = ACC_BUFS * ACC_COLS;                 // A ring behind the accumulators
+    constexpr uint32_t TMEM_NEED = A_BASE + (TA ? kStages * A_COLS : 0);
+    constexpr uint32_t TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128
+                                   : TMEM_NEED <= 256 ? 256 : 512;
+    static_assert(TMEM_NEED <= 512, "tensor memory exceeded");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) {
@@ -165,9 +175,10 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             int ti = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ti++) {
-                const int buf = ti & 1;
-                // the epilogue must have drained this accumulator (two tiles ago)
-                ok = ptx::mbar_wait(acc_empty + buf, ((uint32_t)(ti >> 1) & 1u) ^ 1u, args.status);
+                const int buf = ACC_BUFS == 2 ? (ti & 1) : 0;
+                const uint32_t use = (uint32_t)(ACC_BUFS == 2 ? (ti >> 1) : ti);
+                // the epilogue must have drained this accumulator (its previous use)
+                ok = ptx::mbar_wait(acc_empty + buf, (use & 1u) ^ 1u, args.status);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * ACC_COLS;
@@ -179,11 +190,17 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     ptx::tc_fence_after_sync();
                     const uint64_t a_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::A_OFF + s * L::A_BYTES));
                     const uint64_t b_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES));
+                    const uint32_t a_tmem = tmem_base + A_BASE + (uint32_t)s * A_COLS;
 #pragma unroll
                     for (int k4 = 0; k4 < kRowBytes / 32; k4++) {  // 32 bytes of K per instruction (16 bf16 / 32 int8)
                         const uint32_t accum = (kb > 0 || k4 > 0) ? 1u : 0u;
-                        if (KIND == KIND_BF16) ptx::umma_f16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
-                        else ptx::umma_i8(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                        if (TA) {
+                            if (KIND == KIND_BF16) ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, accum);
+                            else ptx::umma_i8_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, accum);
+                        } else {
+                            if (KIND == KIND_BF16) ptx::umma_f16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                            else ptx::umma_i8(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                        }
                     }
                     ptx::umma_commit(empty + s);  // stage reusable once these MMAs have read it
                 }
@@ -192,7 +209,9 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
     } else if (warp < 6) {
         // ---------------------------------------------------------------- decode warps (2..5)
-        const int row = threadIdx.x - 64;  // weight row inside the tile, 0..127
+        // weight row inside the tile, 0..127.  With the operand in tensor memory a warp may only touch the lane quarter
+        // (warp index % 4), so rows are dealt accordingly.
+        const int row = TA ? ((warp & 3) * 32 + lane) : (threadIdx.x - 64);
         const int sw = row & 7;
         bool ok = healthy;
         long long it = 0;
@@ -204,6 +223,37 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 if (!ok) break;
                 const uint8_t *raw = smem + L::RAW_OFF + s * L::RAW_BYTES + row * KT::RAW_ROW;
                 uint8_t *arow = smem + L::A_OFF + s * L::A_BYTES + row * kRowBytes;
+                if (TA) {
+                    uint32_t cols[32];               // the row's 128 operand bytes, K ascending
+                    if (KIND == KIND_BF16) {
+                        const uint4 p = *reinterpret_cast<const uint4 *>(raw);
+                        const uint32_t words[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+                        for (int wi = 0; wi < 4; wi++) {
+                            uint32_t r[8];
+                            decode_word_bf16(words[wi], r);
+#pragma unroll
+                            for (int j = 0; j < 8; j++) cols[8 * wi + j] = r[j];
+                        }
+                    } else {
+                        const uint4 p0 = *reinterpret_cast<const uint4 *>(raw);
+                        const uint4 p1 = *reinterpret_cast<const uint4 *>(raw + 16);
+                        const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                        for (int wi = 0; wi < 8; wi++) {
+                            uint32_t r[4];
+                            decode_word_i8(words[wi], r);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) cols[4 * wi + j] = r[j];
+                        }
+                    }
+                    ptx::tmem_st_x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + A_BASE + (uint32_t)s * A_COLS, cols);
+                    ptx::tmem_st_wait();
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(full_a + s);
+                    continue;
+                }
                 if (KIND == KIND_BF16) {
                     const uint4 p = *reinterpret_cast<const uint4 *>(raw);
                     const uint32_t words[4] = {p.x, p.y, p.z, p.w};
@@ -238,8 +288,8 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         int ti = 0;
         for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ti++) {
             const long long n0 = (tile % tiles_n) * kTileN, m0 = (tile / tiles_n) * BN;
-            const int buf = ti & 1;
-            ok = ptx::mbar_wait(acc_full + buf, (uint32_t)(ti >> 1) & 1u, args.status);
+            const int buf = ACC_BUFS == 2 ? (ti & 1) : 0;
+            ok = ptx::mbar_wait(acc_full + buf, (uint32_t)(ACC_BUFS == 2 ? (ti >> 1) : ti) & 1u, args.status);
             if (!ok) break;
             ptx::tc_fence_after_sync();
             const long long n = n0 + quarter * 32 + lane;
@@ -334,10 +384,10 @@ __global__ void __launch_bounds__(256) prepack_kernel(const uint32_t *__restrict
 
 // ---- host side --------------------------------------------------------------------------------------------------------
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool TA>
 static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
     using KT = KindTraits<KIND>;
-    using L = SmemLayout<KIND, BN>;
+    using L = SmemLayout<KIND, BN, TA>;
     const long long KW = prepack_valid_words(a.K), KS = prepack_row_words(a.K, KIND);  // words / stride of a row
     CUtensorMap mx, mw;
     const bool okx = (KIND == KIND_BF16)
@@ -351,24 +401,24 @@ static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cud
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(ternary_gemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        attr_err = cudaFuncSetAttribute(ternary_gemm_kernel<KIND, BN, TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     });
     if (attr_err != cudaSuccess) return cuda_status(attr_err);
     const long long ntiles = ((a.N + kTileN - 1) / kTileN) * ((a.M + BN - 1) / BN);
     const unsigned grid = (unsigned)(ntiles < kNumSMs ? ntiles : kNumSMs);
-    ternary_gemm_kernel<KIND, BN><<<grid, kGemmThreads, L::TOTAL, st>>>(mx, mw, a);
+    ternary_gemm_kernel<KIND, BN, TA><<<grid, kGemmThreads, L::TOTAL, st>>>(mx, mw, a);
     return launch_status();
 }
 
 template <int KIND>
 static int dispatch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
-#ifndef TMQ_GEMM_BIG_BN
-#define TMQ_GEMM_BIG_BN 256
-#endif
-    if (a.M > 128) return launch_gemm<KIND, TMQ_GEMM_BIG_BN>(X, Wt, a, st);
-    if (a.M > 64) return launch_gemm<KIND, 128>(X, Wt, a, st);
-    if (a.M > 32) return launch_gemm<KIND, 64>(X, Wt, a, st);
-    return launch_gemm<KIND, 32>(X, Wt, a, st);
+    // bf16: weight operand in tensor memory (+3 .. +13 % measured); int8: in shared memory (the tensor-memory form
+    // measured 20 % slower there)
+    constexpr bool TA = (KIND == KIND_BF16);
+    if (a.M > 128) return launch_gemm<KIND, 256, TA>(X, Wt, a, st);
+    if (a.M > 64) return launch_gemm<KIND, 128, TA>(X, Wt, a, st);
+    if (a.M > 32) return launch_gemm<KIND, 64, TA>(X, Wt, a, st);
+    return launch_gemm<KIND, 32, TA>(X, Wt, a, st);
 }
 
 static int check_gemm_common(const void *X, const uint32_t *Wt, const void *Y, long long M, long long N, long long K,
