@@ -204,6 +204,11 @@ int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scal
 int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int H, int W, int ky, int kx, int sy, int sx, int py, int px,
                           int dy, int dx, int Kp, void *stream);
 
+/* Max pooling between packed layers: X bf16 NHWC [B][H][W][C] (C % 8 == 0) -> Y [B][OH][OW][C], square window k, stride s,
+ * padding p (positions outside the image are ignored), OH = (H + 2p - k) / s + 1.  Keeps the packed inference pipeline
+ * in NHWC bf16 (the reference pipeline runs torch's NCHW fp32 pooling between its compact layers). */
+int tmq_maxpool2d_nhwc_bf16(const void *X, void *Y, int B, int H, int W, int C, int k, int s, int p, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Depthwise ternary convolutions (groups == channels), fp32, forward and transposed.  W is the reference's packed form
  * of a [C][1][ky][kx] kernel tensor: int32 [ky*kx][ceil(C/16)].  Arithmetic: taps accumulated in (ky, kx) order from +0

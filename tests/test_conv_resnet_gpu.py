@@ -69,6 +69,25 @@ def test_residual_fusion_and_patch_kernel(ops):
     ref = unf.view(3, 3, 49, -1).permute(0, 3, 2, 1).reshape(b * oh * ow, 147)      # -> (ky, kx, c)
     assert a.shape == (b * oh * ow, 152)
     assert torch.equal(a[:, :147], ref.to(torch.bfloat16)) and float(a[:, 147:].abs().max()) == 0.0
+    # other geometries: row-staged kernel (unit dilation) and the generic one (dilation 2)
+    for (c, h, w, k, s_, p_, d_) in [(4, 9, 33, (3, 3), (1, 1), (1, 1), (1, 1)), (3, 12, 10, (5, 3), (2, 3), (0, 1), (1, 1)),
+                                     (2, 11, 13, (3, 3), (1, 1), (2, 2), (2, 2)), (1, 8, 8, (1, 1), (1, 1), (0, 0), (1, 1))]:
+        img = torch.randn(2, c, h, w, generator=gen).cuda()
+        a, (b, oh, ow) = ops.conv_patches(img, k, s_, p_, d_)
+        unf = torch.nn.functional.unfold(img, k, dilation=d_, padding=p_, stride=s_)
+        kk = k[0] * k[1]
+        ref = unf.view(2, c, kk, -1).permute(0, 3, 2, 1).reshape(b * oh * ow, kk * c)
+        assert torch.equal(a[:, :kk * c], ref.to(torch.bfloat16)), (c, h, w, k, s_, p_, d_)
+        assert a.shape[1] == (kk * c + 7) // 8 * 8 and (a.shape[1] == kk * c or float(a[:, kk * c:].abs().max()) == 0.0)
+
+
+def test_maxpool_nhwc_matches_torch():
+    from tmq_b200 import ops
+    gen = torch.Generator().manual_seed(3)
+    for (b, h, w, c, k, s, p) in [(2, 13, 11, 64, 3, 2, 1), (1, 8, 8, 8, 2, 2, 0), (3, 7, 9, 24, 3, 1, 1)]:
+        x = torch.randn(b, h, w, c, generator=gen).to(torch.bfloat16).cuda()
+        want = torch.nn.functional.max_pool2d(x.permute(0, 3, 1, 2).float(), k, s, p).permute(0, 2, 3, 1).to(torch.bfloat16)
+        assert torch.equal(ops.maxpool2d_nhwc(x, k, s, p), want.contiguous())
 
 
 def test_resnet18_qat_step_runs_and_clamps():

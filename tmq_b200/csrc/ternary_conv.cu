@@ -5,8 +5,9 @@
 // (K/C times the input), a CUDA-core GEMM multiplies it (tmq/tmq_cuda.cu:289-427) and F.fold reshapes the result.
 // Here activations are bf16 NHWC, K runs as (ky, kx, c) so that 64 consecutive k of one filter tap are 128
 // contiguous bytes of the input, and the patch rows of a tile are gathered straight into the swizzled operand layout:
-//   * same CTA organisation as the tiled GEMM (ternary_gemm.cu): weights are the 128-row A operand decoded in shared
-//     memory from a TMA-loaded raw tile, output pixels are the N side (BN = 128 or 256), accumulator in TMEM;
+//   * same CTA organisation as the tiled GEMM (ternary_gemm.cu): weights are the 128-row A operand, decoded from a
+//     TMA-loaded raw tile into TENSOR memory (tcgen05.st, MMA with A from TMEM: no shared-memory traffic for it), output
+//     pixels are the N side (BN = 128 or 256), accumulator in TMEM next to the ring of decoded weight tiles;
 //   * 4 gather warps replace the activation TMA: per k-block each thread issues 16-byte cp.async copies (zero-filled
 //     outside the image = padding) for its rows, then publishes a stage two k-blocks later, once the copies have landed
 //     and a proxy fence has made them visible to the tensor core;
@@ -27,7 +28,7 @@
 namespace tmq {
 
 constexpr int kConvThreads = 320;  // warp 0: weight TMA, warp 1: MMA, warps 2-5: decode + epilogue, warps 6-9: gather
-constexpr int kConvStages = 4;
+constexpr int kConvStages = 6;       // a stage = gathered activation tile + raw packed words (the decoded weights sit in TMEM)
 constexpr int kConvLag = 2;        // a gathered stage is published this many k-blocks after it was issued
 
 struct ConvArgs {
@@ -44,11 +45,11 @@ struct ConvArgs {
 
 template <int BN>
 struct ConvSmem {
-    static constexpr int A_BYTES = 128 * 128;
+    static constexpr int STAGE_BYTES = 4 * 2048;     // transpose areas of the four epilogue warps
     static constexpr int B_BYTES = BN * 128;
     static constexpr int RAW_BYTES = 128 * 16;
-    static constexpr int A_OFF = 0;
-    static constexpr int B_OFF = A_OFF + kConvStages * A_BYTES;
+    static constexpr int STAGE_OFF = 0;
+    static constexpr int B_OFF = STAGE_OFF + STAGE_BYTES;
     static constexpr int RAW_OFF = B_OFF + kConvStages * B_BYTES;
     static constexpr int BAR_OFF = RAW_OFF + kConvStages * RAW_BYTES;
     static constexpr int TOTAL = BAR_OFF + 256 + 1024;
@@ -81,7 +82,10 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
     const long long m0 = (long long)blockIdx.y * BN;
     const int cpb = args.C / 64;                       // k-blocks per filter tap
     const int nkb = args.ky * args.kx * cpb;
-    constexpr uint32_t TMEM_COLS = BN;
+    constexpr uint32_t A_COLS = 32;                                   // one k-block of a weight row: 64 bf16
+    constexpr uint32_t TMEM_NEED = BN + kConvStages * A_COLS;         // accumulator, then the ring of decoded weight tiles
+    constexpr uint32_t TMEM_COLS = TMEM_NEED <= 256 ? 256 : 512;
+    static_assert(TMEM_NEED <= 512, "tensor memory exceeded");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kConvStages; s++) {
@@ -127,19 +131,20 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
                 if (ok) ok = ptx::mbar_wait(full_b + s, ph, args.status);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
-                const uint64_t a_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::A_OFF + s * L::A_BYTES));
+                const uint32_t a_tmem = tmem_base + BN + (uint32_t)s * A_COLS;
                 const uint64_t b_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES));
 #pragma unroll
                 for (int k4 = 0; k4 < 4; k4++)
-                    ptx::umma_f16(tmem_base, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                    ptx::umma_f16_ts(tmem_base, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
                 ptx::umma_commit(empty + s);
             }
             if (ok) ptx::umma_commit(acc_full);
         }
     } else if (warp < 6) {
         // ---------------------------------------------------------------- decode warps, then epilogue
-        const int row = threadIdx.x - 64;
-        const int sw = row & 7;
+        // the decoded weight tile goes to tensor memory (row m of the tile in lane m); a warp may only touch the lane
+        // quarter (warp index % 4), so rows are dealt accordingly
+        const int row = (warp & 3) * 32 + lane;
         bool ok = healthy;
         for (int kb = 0; kb < nkb && ok; kb++) {
             const int s = kb % kConvStages;
@@ -147,16 +152,18 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
             ok = ptx::mbar_wait(full_raw + s, ph, args.status);
             if (!ok) break;
             const uint4 p = *reinterpret_cast<const uint4 *>(smem + L::RAW_OFF + s * L::RAW_BYTES + row * 16);
-            uint8_t *arow = smem + L::A_OFF + s * L::A_BYTES + row * 128;
             const uint32_t words[4] = {p.x, p.y, p.z, p.w};
+            uint32_t cols[32];                        // the row's 64 bf16 of this k-block, K ascending
 #pragma unroll
             for (int wi = 0; wi < 4; wi++) {
                 uint32_t r[8];
                 decode_word_bf16(words[wi], r);
-                *reinterpret_cast<uint4 *>(arow + (((2 * wi) ^ sw) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
-                *reinterpret_cast<uint4 *>(arow + (((2 * wi + 1) ^ sw) << 4)) = make_uint4(r[4], r[5], r[6], r[7]);
+#pragma unroll
+                for (int j = 0; j < 8; j++) cols[8 * wi + j] = r[j];
             }
-            ptx::fence_proxy_async_smem();
+            ptx::tmem_st_x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + BN + (uint32_t)s * A_COLS, cols);
+            ptx::tmem_st_wait();
+            ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(full_a + s);
         }
@@ -170,8 +177,7 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
             if (args.bias) bi = args.bias[n];
         }
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        // all MMAs have completed, so operand stage 0 is free: each warp takes 2 KB of it as its transpose area
-        float *stage = reinterpret_cast<float *>(smem + L::A_OFF) + (warp - 2) * 512;
+        float *stage = reinterpret_cast<float *>(smem + L::STAGE_OFF) + (warp - 2) * 512;   // this warp's transpose area
         if (ok) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
@@ -309,6 +315,52 @@ __global__ void __launch_bounds__(256) stem_patches_kernel(const float *__restri
     *reinterpret_cast<uint4 *>(A + m * Kp + ch * 8) = *reinterpret_cast<const uint4 *>(v);
 }
 
+// Row-staged form of the same patch matrix for unit dilation: one block per (image, output row).  The C*ky input rows
+// the output row touches are converted to bf16 into shared memory once (zero outside the image); a table maps each
+// k of the patch to its offset in that tile, so a thread assembles eight consecutive k from shared memory and writes one
+// 16-byte vector.  Every input element is then fetched once per output row from L2 instead of once per use, and the
+// index arithmetic per element shrinks to one table lookup.
+__global__ void __launch_bounds__(256) stem_patches_rows_kernel(const float *__restrict__ X, __nv_bfloat16 *__restrict__ A,
+                                                                 int C, int H, int W, int OH, int OW, int ky, int kx, int sy,
+                                                                 int sx, int py, int px, int Kp, int RW) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    int *lut = reinterpret_cast<int *>(dyn);                                     // [Kp] tile offset of k, -1 = padding
+    __nv_bfloat16 *tile = reinterpret_cast<__nv_bfloat16 *>(dyn + (size_t)Kp * 4);  // [C][ky][RW]
+    const int oy = blockIdx.x % OH, b = blockIdx.x / OH;
+    const int K = ky * kx * C;
+    for (int k = threadIdx.x; k < Kp; k += 256) {
+        int off = -1;
+        if (k < K) {
+            const int tap = k / C, c = k - tap * C;
+            off = (c * ky + tap / kx) * RW + tap % kx;
+        }
+        lut[k] = off;
+    }
+    const int rows = C * ky;
+    for (int i = threadIdx.x; i < rows * RW; i += 256) {
+        const int r = i / RW, col = i - r * RW;            // tile column col <-> input column col - px
+        const int c = r / ky, iy = oy * sy - py + (r - c * ky), ix = col - px;
+        float f = 0.0f;
+        if (iy >= 0 && iy < H && ix >= 0 && ix < W) f = __ldg(X + (((long long)b * C + c) * H + iy) * W + ix);
+        tile[i] = __float2bfloat16_rn(f);
+    }
+    __syncthreads();
+    const int chunks = Kp >> 3;
+    __nv_bfloat16 *out = A + ((long long)b * OH + oy) * OW * Kp;
+    const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);
+    for (int i = threadIdx.x; i < OW * chunks; i += 256) {
+        const int ox = i / chunks, ch = i - ox * chunks;
+        const int base = ox * sx;
+        __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int off = lut[ch * 8 + e];
+            v[e] = off >= 0 ? tile[off + base] : zero;
+        }
+        *reinterpret_cast<uint4 *>(out + (long long)i * 8) = *reinterpret_cast<const uint4 *>(v);
+    }
+}
+
 extern "C" int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int H, int W, int ky, int kx, int sy, int sx,
                                      int py, int px, int dy, int dx, int Kp, void *stream) {
     if (!X || !A || B <= 0 || C <= 0 || H <= 0 || W <= 0 || ky <= 0 || kx <= 0 || sy <= 0 || sx <= 0 || py < 0 || px < 0 ||
@@ -318,11 +370,63 @@ extern "C" int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int 
     if (!aligned(A, 16) || !aligned(X, 4)) return TMQ_ERR_ALIGN;
     const int OH = (H + 2 * py - dy * (ky - 1) - 1) / sy + 1, OW = (W + 2 * px - dx * (kx - 1) - 1) / sx + 1;
     if (OH <= 0 || OW <= 0) return TMQ_ERR_ARG;
+    // row-staged form: unit dilation and a tile of C*ky padded input rows that fits 40 KB of shared memory
+    const long long RW = (long long)(OW - 1) * sx + kx;   // tile columns an output row can touch
+    const long long dyn = (long long)Kp * 4 + (long long)C * ky * RW * 2;
+    if (dy == 1 && dx == 1 && dyn <= 40 * 1024 && (long long)B * OH <= 0x7FFFFFFF) {
+        stem_patches_rows_kernel<<<(unsigned)(B * OH), 256, (size_t)dyn, (cudaStream_t)stream>>>(
+            X, reinterpret_cast<__nv_bfloat16 *>(A), C, H, W, OH, OW, ky, kx, sy, sx, py, px, Kp, (int)RW);
+        return launch_status();
+    }
     const long long total = (long long)B * OH * OW * (Kp / 8);
     const long long blocks = (total + 255) / 256;
     if (blocks > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
     stem_patches_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(X, reinterpret_cast<__nv_bfloat16 *>(A), B, C, H, W,
                                                                            OH, OW, ky, kx, sy, sx, py, px, dy, dx, Kp);
+    return launch_status();
+}
+
+// Max pooling on bf16 NHWC activations (the layer between the stem and the first residual stage): one thread per
+// 8 channels of an output pixel, 16-byte loads, window positions outside the image ignored (torch semantics).
+__global__ void __launch_bounds__(256) maxpool_nhwc_kernel(const uint4 *__restrict__ X, uint4 *__restrict__ Y, int B, int H,
+                                                            int W, int C8, int OH, int OW, int k, int s, int p) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)B * OH * OW * C8;
+    if (idx >= total) return;
+    const int c8 = (int)(idx % C8);
+    long long m = idx / C8;
+    const int ox = (int)(m % OW);
+    m /= OW;
+    const int oy = (int)(m % OH), b = (int)(m / OH);
+    const __nv_bfloat162 lowest = __float2bfloat162_rn(-INFINITY);
+    __nv_bfloat162 best[4] = {lowest, lowest, lowest, lowest};
+    for (int i = 0; i < k; i++) {
+        const int iy = oy * s - p + i;
+        if (iy < 0 || iy >= H) continue;
+        for (int j = 0; j < k; j++) {
+            const int ix = ox * s - p + j;
+            if (ix < 0 || ix >= W) continue;
+            const uint4 v = __ldg(X + (((long long)b * H + iy) * W + ix) * C8 + c8);
+            const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+            for (int q = 0; q < 4; q++) best[q] = __hmax2_nan(best[q], h[q]);
+        }
+    }
+    Y[idx] = *reinterpret_cast<const uint4 *>(best);
+}
+
+extern "C" int tmq_maxpool2d_nhwc_bf16(const void *X, void *Y, int B, int H, int W, int C, int k, int s, int p,
+                                       void *stream) {
+    if (!X || !Y || B <= 0 || H <= 0 || W <= 0 || C <= 0 || k <= 0 || s <= 0 || p < 0 || 2 * p > k) return TMQ_ERR_ARG;
+    if (C % 8 != 0) return TMQ_ERR_UNSUPPORTED;
+    if (!aligned(X, 16) || !aligned(Y, 16)) return TMQ_ERR_ALIGN;
+    const int OH = (H + 2 * p - k) / s + 1, OW = (W + 2 * p - k) / s + 1;
+    if (OH <= 0 || OW <= 0) return TMQ_ERR_ARG;
+    const long long total = (long long)B * OH * OW * (C / 8);
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
+    maxpool_nhwc_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const uint4 *>(X), reinterpret_cast<uint4 *>(Y), B, H, W, C / 8, OH, OW, k, s, p);
     return launch_status();
 }
 

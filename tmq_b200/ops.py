@@ -495,6 +495,19 @@ def ternary_conv2d_nhwc(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), d
     return y
 
 
+def maxpool2d_nhwc(x, kernel, stride, padding):
+    """Max pooling on a contiguous bf16 NHWC tensor [B, H, W, C] (C % 8 == 0), torch's max_pool2d semantics."""
+    if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 4 or not x.is_contiguous():
+        raise RuntimeError("maxpool2d_nhwc: expected a contiguous 4-D CUDA bf16 NHWC tensor")
+    b, h, w, c = x.shape
+    k, s, p = int(kernel), int(stride), int(padding)
+    oh, ow = (h + 2 * p - k) // s + 1, (w + 2 * p - k) // s + 1
+    y = torch.empty((b, oh, ow, c), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().tmq_maxpool2d_nhwc_bf16(_ptr(x), _ptr(y), b, h, w, c, k, s, p, _stream(x)), "maxpool2d_nhwc")
+    return y
+
+
 # ---- depthwise convolutions ------------------------------------------------------------------------------------------
 
 def _dw_args(name, x, weights):

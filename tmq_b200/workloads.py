@@ -123,7 +123,7 @@ class PackedResNet18:
     @torch.no_grad()
     def __call__(self, images):
         x = self.conv1.from_images(images.float())                                    # bf16 NHWC
-        x = torch.nn.functional.max_pool2d(x.permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1).contiguous()
+        x = ops.maxpool2d_nhwc(x, 3, 2, 1)
         for c1, c2, down in self.blocks:
             identity = x if down is None else down(x)
             x = c2(c1(x), residual=identity)
