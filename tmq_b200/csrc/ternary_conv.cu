@@ -190,19 +190,37 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
         }
     } else {
         // ---------------------------------------------------------------- gather warps: patches -> swizzled B tile
+        // Eight consecutive lanes fetch the eight 16-byte chunks of ONE pixel's 128 bytes, so a warp instruction reads
+        // four full 128-byte lines.  (One thread per pixel row made every 16-byte copy its own request: 2048 requests
+        // per k-block through the load/store unit, 1.25 us where the MMAs need 0.43.)  A thread serves the pixel rows
+        // rg, rg + 16, ... of the tile and keeps their geometry in registers.
         const int g = threadIdx.x - 192;              // 0..127
-        constexpr int RPT = BN / 128;                 // rows per thread
-        int rb[RPT], roy[RPT], rox[RPT];
-        bool rvalid[RPT];
-#pragma unroll
-        for (int j = 0; j < RPT; j++) {
-            const long long m = m0 + g + 128 * j;
-            rvalid[j] = m < args.M;
-            const long long mm = rvalid[j] ? m : 0;
-            rb[j] = (int)(mm / ((long long)args.OH * args.OW));
+        const int chunk = g & 7, rg = g >> 3;
+        constexpr int RPT = BN / 16;                  // pixel rows per thread
+        int roff[RPT];                                // element offset of the pixel at filter tap (0, 0); -1: row past the end
+        int ryx[RPT];                                 // (iy0 + 32768) << 16 | (ix0 + 32768)
+        {
+            // first row by division, the others by stepping 16 pixels at a time (16 divisions per thread took 3.5 us)
+            const long long m_first = m0 + rg;
+            const long long mm = m_first < args.M ? m_first : 0;
+            int b = (int)(mm / ((long long)args.OH * args.OW));
             const int rem = (int)(mm % ((long long)args.OH * args.OW));
-            roy[j] = (rem / args.OW) * args.sy - args.py;
-            rox[j] = (rem % args.OW) * args.sx - args.px;
+            int oy = rem / args.OW, ox = rem % args.OW;
+#pragma unroll
+            for (int i = 0; i < RPT; i++) {
+                const bool valid = m_first + 16 * i < args.M;
+                const int iy0 = oy * args.sy - args.py, ix0 = ox * args.sx - args.px;
+                roff[i] = valid ? ((b * args.H + iy0) * args.W + ix0) * args.C : -1;
+                ryx[i] = ((iy0 + 32768) << 16) | (ix0 + 32768);
+                ox += 16;
+                while (ox >= args.OW) {
+                    ox -= args.OW;
+                    if (++oy == args.OH) {
+                        oy = 0;
+                        b++;
+                    }
+                }
+            }
         }
         bool ok = healthy;
         int published = 0;
@@ -214,16 +232,15 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
             const int tap = kb / cpb, c0 = (kb % cpb) * 64;
             const int fy = (tap / args.kx) * args.dy, fx = (tap % args.kx) * args.dx;
             const uint32_t bbase = ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES);
+            const int delta = (fy * args.W + fx) * args.C + c0 + chunk * 8;   // the tap's distance from tap (0, 0)
 #pragma unroll
-            for (int j = 0; j < RPT; j++) {
-                const int r = g + 128 * j;
-                const int iy = roy[j] + fy, ix = rox[j] + fx;
-                const bool inb = rvalid[j] && iy >= 0 && iy < args.H && ix >= 0 && ix < args.W;
-                const __nv_bfloat16 *src = inb ? args.X + (((long long)rb[j] * args.H + iy) * args.W + ix) * args.C + c0 : args.X;
-                const uint32_t dst = bbase + r * 128;
-                const uint32_t nbytes = inb ? 16u : 0u;  // 0 source bytes = zero fill (padding, rows past the end)
-#pragma unroll
-                for (int c = 0; c < 8; c++) cp_async_16(dst + ((c ^ (r & 7)) << 4), src + c * 8, nbytes);
+            for (int i = 0; i < RPT; i++) {
+                const int r = rg + 16 * i;
+                const int iy = (int)((unsigned)ryx[i] >> 16) - 32768 + fy, ix = (ryx[i] & 0xFFFF) - 32768 + fx;
+                const bool inb = roff[i] != -1 && (unsigned)iy < (unsigned)args.H && (unsigned)ix < (unsigned)args.W;
+                const __nv_bfloat16 *src = inb ? args.X + (roff[i] + delta) : args.X;
+                // 0 source bytes = zero fill (padding, rows past the end)
+                cp_async_16(bbase + r * 128 + ((chunk ^ (r & 7)) << 4), src, inb ? 16u : 0u);
             }
             cp_async_commit();
             if (kb >= kConvLag) {
@@ -438,6 +455,8 @@ extern "C" int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const 
         dy <= 0 || dx <= 0)
         return TMQ_ERR_ARG;
     if (C % 64 != 0) return TMQ_ERR_UNSUPPORTED;
+    // the gather keeps 32-bit element offsets and 16-bit pixel coordinates
+    if ((long long)B * H * W * C > 0x7FFFFFFFll || H > 30000 || W > 30000 || py > 2000 || px > 2000) return TMQ_ERR_UNSUPPORTED;
     const int OH = (H + 2 * py - dy * (ky - 1) - 1) / sy + 1, OW = (W + 2 * px - dx * (kx - 1) - 1) / sx + 1;
     if (OH <= 0 || OW <= 0) return TMQ_ERR_ARG;
     if (!aligned(X, 16) || !aligned(Wt, 16) || !aligned(Y, 2) || !aligned(status, 4)) return TMQ_ERR_ALIGN;
