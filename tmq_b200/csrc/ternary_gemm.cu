@@ -415,7 +415,10 @@ static int dispatch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, c
     // bf16: weight operand in tensor memory (+3 .. +13 % measured); int8: in shared memory (the tensor-memory form
     // measured 20 % slower there)
     constexpr bool TA = (KIND == KIND_BF16);
-    if (a.M > 128) return launch_gemm<KIND, 256, TA>(X, Wt, a, st);
+    // short reductions (a handful of k-blocks per tile) are bound by the epilogue: 128-row tiles keep the accumulator
+    // double-buffered in the tensor-memory-operand form, so the drain of one tile hides under the next
+    if (a.M > 128 && !(TA && a.K <= 512)) return launch_gemm<KIND, 256, TA>(X, Wt, a, st);
+    if (a.M > 128) return launch_gemm<KIND, 128, TA>(X, Wt, a, st);
     if (a.M > 64) return launch_gemm<KIND, 128, TA>(X, Wt, a, st);
     if (a.M > 32) return launch_gemm<KIND, 64, TA>(X, Wt, a, st);
     return launch_gemm<KIND, 32, TA>(X, Wt, a, st);
