@@ -205,9 +205,11 @@ int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int H, int W, i
                           int dy, int dx, int Kp, void *stream);
 
 /* Max pooling between packed layers: X bf16 NHWC [B][H][W][C] (C % 8 == 0) -> Y [B][OH][OW][C], square window k, stride s,
- * padding p (positions outside the image are ignored), OH = (H + 2p - k) / s + 1.  Keeps the packed inference pipeline
- * in NHWC bf16 (the reference pipeline runs torch's NCHW fp32 pooling between its compact layers). */
-int tmq_maxpool2d_nhwc_bf16(const void *X, void *Y, int B, int H, int W, int C, int k, int s, int p, void *stream);
+ * padding p (positions outside the image are ignored), OH = (H + 2p - k) / s + 1; relu != 0 applies max(0, .) as well
+ * (ReLU and max pooling commute, so a preceding ReLU can be folded in).  Keeps the packed inference pipeline in NHWC bf16
+ * (the reference pipeline runs torch's NCHW fp32 pooling between its compact layers). */
+int tmq_maxpool2d_nhwc_bf16(const void *X, void *Y, int B, int H, int W, int C, int k, int s, int p, int relu,
+                            void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Depthwise ternary convolutions (groups == channels), fp32, forward and transposed.  W is the reference's packed form

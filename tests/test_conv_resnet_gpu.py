@@ -88,6 +88,7 @@ def test_maxpool_nhwc_matches_torch():
         x = torch.randn(b, h, w, c, generator=gen).to(torch.bfloat16).cuda()
         want = torch.nn.functional.max_pool2d(x.permute(0, 3, 1, 2).float(), k, s, p).permute(0, 2, 3, 1).to(torch.bfloat16)
         assert torch.equal(ops.maxpool2d_nhwc(x, k, s, p), want.contiguous())
+        assert torch.equal(ops.maxpool2d_nhwc(x, k, s, p, relu=True), torch.relu(want).contiguous())
 
 
 def test_resnet18_qat_step_runs_and_clamps():

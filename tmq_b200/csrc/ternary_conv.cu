@@ -410,7 +410,7 @@ extern "C" int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int 
 // Max pooling on bf16 NHWC activations (the layer between the stem and the first residual stage): one thread per
 // 8 channels of an output pixel, 16-byte loads, window positions outside the image ignored (torch semantics).
 __global__ void __launch_bounds__(256) maxpool_nhwc_kernel(const uint4 *__restrict__ X, uint4 *__restrict__ Y, int B, int H,
-                                                            int W, int C8, int OH, int OW, int k, int s, int p) {
+                                                            int W, int C8, int OH, int OW, int k, int s, int p, int relu) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long total = (long long)B * OH * OW * C8;
     if (idx >= total) return;
@@ -419,7 +419,8 @@ __global__ void __launch_bounds__(256) maxpool_nhwc_kernel(const uint4 *__restri
     const int ox = (int)(m % OW);
     m /= OW;
     const int oy = (int)(m % OH), b = (int)(m / OH);
-    const __nv_bfloat162 lowest = __float2bfloat162_rn(-INFINITY);
+    // relu: max(0, max(window)) equals the pooled ReLU (both are monotone), so the activation costs nothing extra
+    const __nv_bfloat162 lowest = __float2bfloat162_rn(relu ? 0.0f : -INFINITY);
     __nv_bfloat162 best[4] = {lowest, lowest, lowest, lowest};
     for (int i = 0; i < k; i++) {
         const int iy = oy * s - p + i;
@@ -436,7 +437,7 @@ __global__ void __launch_bounds__(256) maxpool_nhwc_kernel(const uint4 *__restri
     Y[idx] = *reinterpret_cast<const uint4 *>(best);
 }
 
-extern "C" int tmq_maxpool2d_nhwc_bf16(const void *X, void *Y, int B, int H, int W, int C, int k, int s, int p,
+extern "C" int tmq_maxpool2d_nhwc_bf16(const void *X, void *Y, int B, int H, int W, int C, int k, int s, int p, int relu,
                                        void *stream) {
     if (!X || !Y || B <= 0 || H <= 0 || W <= 0 || C <= 0 || k <= 0 || s <= 0 || p < 0 || 2 * p > k) return TMQ_ERR_ARG;
     if (C % 8 != 0) return TMQ_ERR_UNSUPPORTED;
@@ -447,7 +448,7 @@ extern "C" int tmq_maxpool2d_nhwc_bf16(const void *X, void *Y, int B, int H, int
     const long long blocks = (total + 255) / 256;
     if (blocks > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
     maxpool_nhwc_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<const uint4 *>(X), reinterpret_cast<uint4 *>(Y), B, H, W, C / 8, OH, OW, k, s, p);
+        reinterpret_cast<const uint4 *>(X), reinterpret_cast<uint4 *>(Y), B, H, W, C / 8, OH, OW, k, s, p, relu);
     return launch_status();
 }
 

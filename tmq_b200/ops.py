@@ -495,8 +495,9 @@ def ternary_conv2d_nhwc(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), d
     return y
 
 
-def maxpool2d_nhwc(x, kernel, stride, padding):
-    """Max pooling on a contiguous bf16 NHWC tensor [B, H, W, C] (C % 8 == 0), torch's max_pool2d semantics."""
+def maxpool2d_nhwc(x, kernel, stride, padding, relu=False):
+    """Max pooling on a contiguous bf16 NHWC tensor [B, H, W, C] (C % 8 == 0), torch's max_pool2d semantics; relu=True
+    also applies max(0, .), i.e. folds a ReLU that preceded the pooling."""
     if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 4 or not x.is_contiguous():
         raise RuntimeError("maxpool2d_nhwc: expected a contiguous 4-D CUDA bf16 NHWC tensor")
     b, h, w, c = x.shape
@@ -504,7 +505,8 @@ def maxpool2d_nhwc(x, kernel, stride, padding):
     oh, ow = (h + 2 * p - k) // s + 1, (w + 2 * p - k) // s + 1
     y = torch.empty((b, oh, ow, c), dtype=torch.bfloat16, device=x.device)
     with torch.cuda.device(x.device):
-        check(lib().tmq_maxpool2d_nhwc_bf16(_ptr(x), _ptr(y), b, h, w, c, k, s, p, _stream(x)), "maxpool2d_nhwc")
+        check(lib().tmq_maxpool2d_nhwc_bf16(_ptr(x), _ptr(y), b, h, w, c, k, s, p, 1 if relu else 0, _stream(x)),
+              "maxpool2d_nhwc")
     return y
 
 

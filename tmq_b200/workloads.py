@@ -84,11 +84,12 @@ class PackedConv:
         self.wt = ops.prepack(p, self.cout, ops.FMT_BF16)
         self.kpad = kpad
 
-    def from_images(self, images):
-        """Stem route: fp32 NCHW images -> bf16 NHWC feature map, patches built by a kernel (no torch glue)."""
+    def from_images(self, images, defer_relu=False):
+        """Stem route: fp32 NCHW images -> bf16 NHWC feature map, patches built by a kernel (no torch glue).
+        defer_relu: leave the activation to the caller (a max pooling that follows applies it for free)."""
         a, (b, oh, ow) = ops.conv_patches(images, (self.ky, self.kx), self.stride, self.padding, self.dilation)
         y = ops.ternary_gemm(a, self.wt, self.cout, self.scale, self.bias).view(b, oh, ow, self.cout)
-        return torch.relu_(y) if self.relu else y
+        return torch.relu_(y) if (self.relu and not defer_relu) else y
 
     def __call__(self, x_nhwc, residual=None):
         """x_nhwc: bf16 [B, H, W, C] contiguous -> bf16 [B, OH, OW, Cout]; the optional residual is added before the
@@ -122,8 +123,8 @@ class PackedResNet18:
 
     @torch.no_grad()
     def __call__(self, images):
-        x = self.conv1.from_images(images.float())                                    # bf16 NHWC
-        x = ops.maxpool2d_nhwc(x, 3, 2, 1)
+        x = self.conv1.from_images(images.float(), defer_relu=True)                   # bf16 NHWC
+        x = ops.maxpool2d_nhwc(x, 3, 2, 1, relu=True)                                 # ReLU folded into the pooling
         for c1, c2, down in self.blocks:
             identity = x if down is None else down(x)
             x = c2(c1(x), residual=identity)
