@@ -389,7 +389,76 @@ def ternary_sections(peaks):
                                                "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"],
                                                "tops_equiv": 2 * Mg * N * K / us / 1e6, "algorithmic_bytes": nbytes,
                                                "protocol": "32 distinct matrices in one CUDA graph, time/32"}
+    # the same protocol with int8 activations (exact int32 results; byte dot products at M = 1)
+    wts8 = []
+    for i in range(NM):
+        wts8.append(ops.prepack(_ternary_packed(ops, N, K, 100 + i), N, ops.FMT_I8))
+    del wts
+    for Mg in (1, 8):
+        X8 = torch.randint(-127, 128, (Mg, K), device="cuda", dtype=torch.int8)
+        Y8 = torch.empty(Mg, N, device="cuda", dtype=torch.int32)
+        status = ops.gemm_status_word(X8.device)
+        stream = torch.cuda.Stream()
+
+        def run8(i, st):
+            rc = L.tmq_ternary_gemv_i8(X8.data_ptr(), wts8[i].data_ptr(), Y8.data_ptr(), Mg, N, K, N, status.data_ptr(), st)
+            assert rc == 0
+        with torch.cuda.stream(stream):
+            for i in range(NM):
+                run8(i, stream.cuda_stream)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(NM):
+                    run8(i, stream.cuda_stream)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(10):
+                graph.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / 10 / NM * 1e3
+        nbytes = N * K // 4 + Mg * K + 4 * Mg * N
+        res[f"gemv_i8_M{Mg}_N11008_K4096"] = {"us_per_matrix": us, "gbs": nbytes / us / 1e3,
+                                             "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"],
+                                             "tops_equiv": 2 * Mg * N * K / us / 1e6, "algorithmic_bytes": nbytes,
+                                             "protocol": "32 distinct matrices in one CUDA graph, time/32"}
+    ops.check_gemm_status()
+    del wts8
+    res["cpu_baselines"] = ternary_cpu_baselines()
     return res
+
+
+def ternary_cpu_baselines():
+    """What the reference offers on the host for the inference path: un-compacted layers through PyTorch CPU eager
+    (F.linear on the expanded fp32 weights) and its single-threaded packer (restated in oracle/oracle.c).  Bounded
+    samples: 64 activation rows of the M=8192 K=8192 N=28672 problem; one 11008 x 4096 matrix for the packer."""
+    import time
+    import numpy as np
+    from oracle import ternary as T
+    out = {"cores": torch.get_num_threads()}
+    M, K, N = 64, 8192, 28672
+    gen = torch.Generator().manual_seed(0)
+    W = torch.randint(-1, 2, (N, K), generator=gen).float()
+    X = torch.randn(M, K, generator=gen)
+    torch.nn.functional.linear(X, W)
+    t0 = time.perf_counter()
+    torch.nn.functional.linear(X, W)
+    dt = time.perf_counter() - t0
+    out["linear_f32_K8192_N28672"] = {"tops_equiv": 2 * M * N * K / dt / 1e12, "seconds": dt,
+                                      "sample": "64 of 8192 activation rows, torch CPU eager F.linear on expanded weights",
+                                      "kind": "port"}
+    del W, X
+    Wp = np.random.default_rng(0).integers(-1, 2, (11008, 4096)).astype(np.float32)
+    t0 = time.perf_counter()
+    T.pack(Wp)
+    dt = time.perf_counter() - t0
+    out["pack_11008x4096"] = {"seconds": dt, "sample": "one matrix, single-threaded C restatement of the reference packer",
+                              "kind": "port", "cores": 1}
+    return out
 
 
 # ------------------------------------------------------------------------------------------------ other workloads

@@ -204,6 +204,16 @@ int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scal
 int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int H, int W, int ky, int kx, int sy, int sx, int py, int px,
                           int dy, int dx, int Kp, void *stream);
 
+/* Convolution for layers with few input channels (the image stem), patches kept on chip: X fp32 NCHW [B][C][H][W],
+ * Wt = tmq_prepack(fmt 0) of the packed weights with rows in (ky, kx, c) order (k_rows of them, zero rows beyond
+ * ky*kx*C allowed), Y bf16 NHWC [B][OH][OW][N] = act(scale[n] * conv + bias[n]), unit dilation.  One CTA per (image,
+ * output row): limits ky*kx*C <= 256, OW <= 128, C*ky*((OW-1)*sx+kx)*2 <= 16 KB, N % 8 == 0; TMQ_ERR_UNSUPPORTED beyond
+ * them (then: tmq_conv_patches_bf16 + tmq_ternary_gemm_bf16).
+ * replaces: Conv2d.compact_forward for such layers, tmq/tmq.py:822-871. */
+int tmq_ternary_conv2d_stem_bf16(const float *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int B,
+                                 int C, int H, int W, int N, int ky, int kx, int sy, int sx, int py, int px, int k_rows,
+                                 int relu, int *status, void *stream);
+
 /* Max pooling between packed layers: X bf16 NHWC [B][H][W][C] (C % 8 == 0) -> Y [B][OH][OW][C], square window k, stride s,
  * padding p (positions outside the image are ignored), OH = (H + 2p - k) / s + 1; relu != 0 applies max(0, .) as well
  * (ReLU and max pooling commute, so a preceding ReLU can be folded in).  Keeps the packed inference pipeline in NHWC bf16

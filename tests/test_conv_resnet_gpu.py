@@ -81,6 +81,38 @@ def test_residual_fusion_and_patch_kernel(ops):
         assert a.shape[1] == (kk * c + 7) // 8 * 8 and (a.shape[1] == kk * c or float(a[:, kk * c:].abs().max()) == 0.0)
 
 
+@pytest.mark.parametrize("c,h,w,n,k,s,p", [(3, 40, 36, 64, 7, 2, 3), (3, 224, 224, 64, 7, 2, 3), (4, 17, 30, 72, 3, 1, 1),
+                                           (1, 9, 128, 8, 5, 1, 2), (2, 12, 20, 136, 3, 2, 0)])
+def test_fused_stem_convolution(c, h, w, n, k, s, p):
+    """Few-channel convolution with the patches kept on chip, against torch conv2d on the bf16-rounded image (fp64) and
+    against the explicit patch-matrix + GEMM route (same products, same k-block order)."""
+    from tmq_b200 import ops
+    gen = torch.Generator().manual_seed(c * 100 + n)
+    wgt = torch.randint(-1, 2, (n, c, k, k), generator=gen).float()
+    img = torch.randn(2, c, h, w, generator=gen)
+    scale = torch.rand(n, generator=gen) * 0.05 + 0.01
+    bias = torch.randn(n, generator=gen)
+    rows = ops.compactify_ternary(wgt.cuda()).view(c * k * k, -1)                    # (c, ky, kx) order
+    kk = torch.arange(c * k * k)
+    perm = torch.argsort((kk % (k * k)) * c + kk // (k * k)).cuda()                   # -> (ky, kx, c)
+    rows = rows.index_select(0, perm).contiguous()
+    pad = (-rows.shape[0]) % 8
+    if pad:
+        rows = torch.nn.functional.pad(rows, (0, 0, 0, pad))
+    wt = ops.prepack(rows, n, ops.FMT_BF16)
+    y = ops.ternary_conv2d_stem(img.cuda(), wt, n, (k, k), (s, s), (p, p), scale.cuda(), bias.cuda(), relu=True)
+    ops.check_gemm_status()
+    assert y is not None and y.dtype == torch.bfloat16
+    ref = torch.nn.functional.conv2d(img.to(torch.bfloat16).double(), wgt.double(), None, s, p)
+    ref = torch.relu(ref * scale.double().view(1, -1, 1, 1) + bias.double().view(1, -1, 1, 1)).permute(0, 2, 3, 1)
+    assert y.shape == ref.shape
+    err = (y.cpu().double() - ref).abs()
+    assert float(err.max()) <= 2.0 ** -7 * float(ref.abs().max()) + 1e-6            # one bf16 rounding of the output
+    a, (b, oh, ow) = ops.conv_patches(img.cuda(), (k, k), (s, s), (p, p), (1, 1))
+    via_patches = torch.relu(ops.ternary_gemm(a, wt, n, scale.cuda(), bias.cuda()).view(b, oh, ow, n))
+    assert torch.equal(y, via_patches)
+
+
 def test_maxpool_nhwc_matches_torch():
     from tmq_b200 import ops
     gen = torch.Generator().manual_seed(3)

@@ -45,6 +45,7 @@ _SIGNATURES = {
     "tmq_pack2b_i32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "tmq_pack2b_i8": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "tmq_unpack2b_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "tmq_ternary_conv2d_stem_bf16": (c_int, [c_void_p] * 5 + [c_int] * 13 + [c_void_p, c_void_p]),
     "tmq_maxpool2d_nhwc_bf16": (c_int, [c_void_p, c_void_p] + [c_int] * 8 + [c_void_p]),
     "tmq_ternary_dwconv2d_f32": (c_int, [c_void_p] * 5 + [c_int] * 12 + [c_void_p]),
     "tmq_ternary_dwconvtrans2d_f32": (c_int, [c_void_p] * 5 + [c_int] * 14 + [c_void_p]),

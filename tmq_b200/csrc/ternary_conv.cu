@@ -407,6 +407,243 @@ extern "C" int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int 
     return launch_status();
 }
 
+// ---- fused stem: few input channels, fp32 NCHW images -------------------------------------------------------------
+//
+// The implicit kernel above needs 64-channel runs; a 3-channel stem has none.  Writing its patch matrix to memory and
+// multiplying it costs about 2 GB of traffic per 256 images (976 MB written, read again, for 154 MB of input).  This
+// kernel keeps the patches on chip: one CTA per (image, output row).  The C*ky input rows that row touches are
+// converted to bf16 into shared memory once; the gather warps assemble the (up to four) 128-pixel x 64-k operand tiles
+// from that window through a k -> offset table, directly in the swizzled layout the MMA reads; weights are decoded into
+// tensor memory as in the implicit kernel; the epilogue writes NHWC bf16 with scale / bias / ReLU.  All k-blocks are
+// resident at once, so the barriers are single-use.  81 KB of shared memory and 256 TMEM columns: two CTAs per SM.
+struct StemArgs {
+    const float *X;
+    const float *scale, *bias;
+    __nv_bfloat16 *Y;
+    int B, C, H, W, OH, OW, N, ky, kx, sy, sx, py, px;
+    int K, RW;        // K = ky*kx*C (patch length, (ky, kx, c) order); RW = window row width = (OW-1)*sx + kx
+    int relu;
+    int *status;
+};
+
+constexpr int kStemMaxKb = 4;                  // K up to 256
+constexpr int kStemWindowBytes = 16 * 1024;
+
+struct StemSmem {
+    static constexpr int STAGE_OFF = 0;                                   // 4 x 2 KB transpose areas
+    static constexpr int B_OFF = STAGE_OFF + 4 * 2048;                    // kStemMaxKb operand tiles of 128 x 128 B
+    static constexpr int RAW_OFF = B_OFF + kStemMaxKb * 128 * 128;
+    static constexpr int WIN_OFF = RAW_OFF + kStemMaxKb * 128 * 16;
+    static constexpr int LUT_OFF = WIN_OFF + kStemWindowBytes;
+    static constexpr int BAR_OFF = LUT_OFF + kStemMaxKb * 64 * 4;
+    static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__global__ void __launch_bounds__(kConvThreads, 2)
+ternary_stem_kernel(const __grid_constant__ CUtensorMap tmap_w, const StemArgs args) {
+    using L = StemSmem;
+    constexpr int BN = 128;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *full_raw = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
+    uint64_t *full_a = full_raw + kStemMaxKb;
+    uint64_t *full_b = full_a + kStemMaxKb;
+    uint64_t *acc_full = full_b + kStemMaxKb;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nkb = (args.K + 63) / 64;
+    const int oy = blockIdx.x % args.OH, b = blockIdx.x / args.OH;
+    const long long n0 = (long long)blockIdx.y * 128;
+    constexpr uint32_t A_COLS = 32, TMEM_COLS = 256;                     // 128 accumulator columns + 4 x 32
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStemMaxKb; s++) {
+            ptx::mbar_init(full_raw + s, 1);
+            ptx::mbar_init(full_a + s, 4);
+            ptx::mbar_init(full_b + s, 8);   // warps 2-9 all build operand tiles
+        }
+        ptx::mbar_init(acc_full, 1);
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_w);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const bool healthy = (*reinterpret_cast<volatile int *>(args.status) == 0);
+
+    if (warp >= 2) {
+        // ---------------------------------------------------------------- warps 2-9: window, then the operand tiles
+        const int g = threadIdx.x - 64;               // 0..255
+        int *lut = reinterpret_cast<int *>(smem + L::LUT_OFF);
+        __nv_bfloat16 *win = reinterpret_cast<__nv_bfloat16 *>(smem + L::WIN_OFF);
+        for (int k = g; k < nkb * 64; k += 256) {
+            int off = -1;
+            if (k < args.K) {
+                const int tap = k / args.C, c = k - tap * args.C;
+                off = (c * args.ky + tap / args.kx) * args.RW + tap % args.kx;
+            }
+            lut[k] = off;
+        }
+        // one warp per window row at a time: no division per element, loads of a row are consecutive
+        const int rows = args.C * args.ky;
+        for (int r = warp - 2; r < rows; r += 8) {
+            const int c = r / args.ky, iy = oy * args.sy - args.py + (r - c * args.ky);
+            const bool y_ok = iy >= 0 && iy < args.H;
+            const float *src = args.X + (((long long)b * args.C + c) * args.H + (y_ok ? iy : 0)) * args.W - args.px;
+            __nv_bfloat16 *dst = win + r * args.RW;
+            for (int col0 = lane; col0 < args.RW; col0 += 256) {   // eight loads in flight per lane, then the stores
+                float f[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int col = col0 + 32 * u, ix = col - args.px;
+                    f[u] = (y_ok && col < args.RW && ix >= 0 && ix < args.W) ? __ldg(src + col) : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int col = col0 + 32 * u;
+                    if (col < args.RW) dst[col] = __float2bfloat16_rn(f[u]);
+                }
+            }
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // warps 2-9 only
+        const int chunk = g & 7, rg = g >> 3;            // eight lanes write the eight 16-byte chunks of one pixel row
+        const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);
+        for (int kb = 0; kb < nkb; kb++) {
+            int loff[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) loff[e] = lut[kb * 64 + chunk * 8 + e];
+            uint8_t *tile = smem + L::B_OFF + kb * 128 * 128;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int r = rg + 32 * i;               // pixel ox = r of this output row
+                __align__(16) __nv_bfloat16 v[8];
+                const int base = r * args.sx;
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] = (r < args.OW && loff[e] >= 0) ? win[loff[e] + base] : zero;
+                *reinterpret_cast<uint4 *>(tile + r * 128 + ((chunk ^ (r & 7)) << 4)) = *reinterpret_cast<const uint4 *>(v);
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(full_b + kb);
+        }
+    }
+
+    if (warp == 0) {
+        if (lane == 0 && healthy) {
+            for (int kb = 0; kb < nkb; kb++) {
+                ptx::mbar_arrive_expect_tx(full_raw + kb, 128 * 16);
+                ptx::tma_load_2d(smem + L::RAW_OFF + kb * 128 * 16, &tmap_w, full_raw + kb, kb * 4, (int)n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && healthy) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; kb++) {
+                ok = ptx::mbar_wait(full_a + kb, 0u, args.status);
+                if (ok) ok = ptx::mbar_wait(full_b + kb, 0u, args.status);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t a_tmem = tmem_base + BN + (uint32_t)kb * A_COLS;
+                const uint64_t b_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::B_OFF + kb * 128 * 128));
+#pragma unroll
+                for (int k4 = 0; k4 < 4; k4++)
+                    ptx::umma_f16_ts(tmem_base, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+            }
+            if (ok) ptx::umma_commit(acc_full);
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- weights -> tensor memory, then the epilogue
+        const int row = (warp & 3) * 32 + lane;
+        bool ok = healthy;
+        for (int kb = 0; kb < nkb && ok; kb++) {
+            ok = ptx::mbar_wait(full_raw + kb, 0u, args.status);
+            if (!ok) break;
+            const uint4 p = *reinterpret_cast<const uint4 *>(smem + L::RAW_OFF + kb * 128 * 16 + row * 16);
+            const uint32_t words[4] = {p.x, p.y, p.z, p.w};
+            uint32_t cols[32];
+#pragma unroll
+            for (int wi = 0; wi < 4; wi++) {
+                uint32_t r[8];
+                decode_word_bf16(words[wi], r);
+#pragma unroll
+                for (int j = 0; j < 8; j++) cols[8 * wi + j] = r[j];
+            }
+            ptx::tmem_st_x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + BN + (uint32_t)kb * A_COLS, cols);
+            ptx::tmem_st_wait();
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(full_a + kb);
+        }
+        if (ok) ok = ptx::mbar_wait(acc_full, 0u, args.status);
+        ptx::tc_fence_after_sync();
+        const int quarter = warp & 3;
+        const long long n = n0 + quarter * 32 + lane;
+        float sc = 0.5f, bi = 0.0f;                   // operands carried +-2.0
+        if (ok && n < args.N) {
+            if (args.scale) sc *= args.scale[n];
+            if (args.bias) bi = args.bias[n];
+        }
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float *stage = reinterpret_cast<float *>(smem + L::STAGE_OFF) + (warp - 2) * 512;
+        const long long m_base = ((long long)b * args.OH + oy) * args.OW;    // first pixel of this output row
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN && c < args.OW; c += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld_x16(lane_addr + (uint32_t)c, v);
+                ptx::tmem_ld_wait();
+                epilogue_chunk_bf16(v, sc, bi, stage, args.Y, nullptr, m_base + c, m_base + args.OW, args.N,
+                                    n0 + quarter * 32, args.N, args.relu, lane);
+            }
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+extern "C" int tmq_ternary_conv2d_stem_bf16(const float *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y,
+                                            int B, int C, int H, int W, int N, int ky, int kx, int sy, int sx, int py, int px,
+                                            int k_rows, int relu, int *status, void *stream) {
+    if (!X || !Wt || !Y || !status) return TMQ_ERR_ARG;
+    if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || N <= 0 || ky <= 0 || kx <= 0 || sy <= 0 || sx <= 0 || py < 0 || px < 0)
+        return TMQ_ERR_ARG;
+    const int K = ky * kx * C;
+    if (k_rows < K) return TMQ_ERR_ARG;
+    const int OH = (H + 2 * py - ky) / sy + 1, OW = (W + 2 * px - kx) / sx + 1;
+    if (OH <= 0 || OW <= 0) return TMQ_ERR_ARG;
+    const long long RW = (long long)(OW - 1) * sx + kx;
+    if (K > kStemMaxKb * 64 || OW > 128 || (long long)C * ky * RW * 2 > kStemWindowBytes || (N & 7) != 0)
+        return TMQ_ERR_UNSUPPORTED;
+    if ((long long)B * OH > 0x7FFFFFFF || (N + 127) / 128 > 65535) return TMQ_ERR_UNSUPPORTED;
+    if (!aligned(X, 4) || !aligned(Wt, 16) || !aligned(Y, 16) || !aligned(status, 4)) return TMQ_ERR_ALIGN;
+    StemArgs a = {X, scale, bias, reinterpret_cast<__nv_bfloat16 *>(Y), B, C, H, W, OH, OW, N, ky, kx, sy, sx, py, px, K, (int)RW,
+                  relu, status};
+    const long long KW = prepack_valid_words(k_rows), KS = prepack_row_words(k_rows, 0);
+    CUtensorMap mw;
+    if (!make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)N, (uint64_t)KS * 4, 4, 128,
+                     CU_TENSOR_MAP_SWIZZLE_NONE))
+        return TMQ_ERR_LAUNCH;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(ternary_stem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, StemSmem::TOTAL);
+    });
+    if (attr_err != cudaSuccess) return cuda_status(attr_err);
+    dim3 grid((unsigned)(B * OH), (unsigned)((N + 127) / 128));
+    ternary_stem_kernel<<<grid, kConvThreads, StemSmem::TOTAL, (cudaStream_t)stream>>>(mw, a);
+    return launch_status();
+}
+
 // Max pooling on bf16 NHWC activations (the layer between the stem and the first residual stage): one thread per
 // 8 channels of an output pixel, 16-byte loads, window positions outside the image ignored (torch semantics).
 __global__ void __launch_bounds__(256) maxpool_nhwc_kernel(const uint4 *__restrict__ X, uint4 *__restrict__ Y, int B, int H,

@@ -495,6 +495,37 @@ def ternary_conv2d_nhwc(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), d
     return y
 
 
+def ternary_conv2d_stem(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), scale=None, bias=None, relu=False):
+    """Fused convolution for layers with few input channels: x fp32 NCHW [B, C, H, W]; wt = prepack(FMT_BF16) of the
+    packed weights with rows in (ky, kx, c) order -> bf16 NHWC [B, OH, OW, N].  Returns None when the shape is outside the
+    kernel's limits (the caller then builds patches and runs the GEMM)."""
+    if x.dtype != torch.float32 or x.device.type != "cuda" or x.dim() != 4:
+        raise RuntimeError("ternary_conv2d_stem: expected a 4-D CUDA fp32 NCHW tensor")
+    x = x.contiguous()
+    b, c, h, w = x.shape
+    (ky, kx), (sy, sx), (py, px) = kernel, stride, padding
+    n = int(columns)
+    k_rows = None
+    for cand in range(ky * kx * c, ky * kx * c + 64):          # the prepacked K may carry a few zero rows of padding
+        if wt.shape[1] == prepack_row_words(cand, FMT_BF16):
+            k_rows = cand
+            break
+    if wt.dtype != torch.int32 or wt.shape[0] != n or k_rows is None:
+        raise RuntimeError("ternary_conv2d_stem: prepacked weights do not match the problem shape")
+    oh, ow = (h + 2 * py - ky) // sy + 1, (w + 2 * px - kx) // sx + 1
+    y = torch.empty((b, oh, ow, n), dtype=torch.bfloat16, device=x.device)
+    sc, bi = _opt_f32(scale, x.device), _opt_f32(bias, x.device)
+    st = gemm_status_word(x.device)
+    with torch.cuda.device(x.device):
+        rc = lib().tmq_ternary_conv2d_stem_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
+                                                _ptr(bi) if bi is not None else None, _ptr(y), b, c, h, w, n, ky, kx, sy, sx,
+                                                py, px, k_rows, 1 if relu else 0, _ptr(st), _stream(x))
+    if rc == -6:
+        return None
+    check(rc, "ternary_conv2d_stem")
+    return y
+
+
 def maxpool2d_nhwc(x, kernel, stride, padding, relu=False):
     """Max pooling on a contiguous bf16 NHWC tensor [B, H, W, C] (C % 8 == 0), torch's max_pool2d semantics; relu=True
     also applies max(0, .), i.e. folds a ReLU that preceded the pooling."""

@@ -87,9 +87,15 @@ class PackedConv:
     def from_images(self, images, defer_relu=False):
         """Stem route: fp32 NCHW images -> bf16 NHWC feature map, patches built by a kernel (no torch glue).
         defer_relu: leave the activation to the caller (a max pooling that follows applies it for free)."""
+        relu = self.relu and not defer_relu
+        if self.dilation == (1, 1):
+            y = ops.ternary_conv2d_stem(images, self.wt, self.cout, (self.ky, self.kx), self.stride, self.padding,
+                                        self.scale, self.bias, relu=relu)
+            if y is not None:
+                return y
         a, (b, oh, ow) = ops.conv_patches(images, (self.ky, self.kx), self.stride, self.padding, self.dilation)
         y = ops.ternary_gemm(a, self.wt, self.cout, self.scale, self.bias).view(b, oh, ow, self.cout)
-        return torch.relu_(y) if (self.relu and not defer_relu) else y
+        return torch.relu_(y) if relu else y
 
     def __call__(self, x_nhwc, residual=None):
         """x_nhwc: bf16 [B, H, W, C] contiguous -> bf16 [B, OH, OW, Cout]; the optional residual is added before the
