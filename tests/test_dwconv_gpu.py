@@ -25,6 +25,8 @@ GEOMS = [  # C, H, W, kernel, stride, padding, dilation, output_padding
     (6, 10, 16, (3, 3), (1, 1), (0, 0), (1, 1), (0, 0)),
     (130, 7, 4, (3, 3), (1, 1), (1, 1), (1, 1), (0, 0)),       # one chunk per row
     (5, 6, 8, (3, 3), (1, 1), (2, 1), (1, 1), (0, 0)),         # taller padding than "same"
+    (24, 56, 56, (3, 3), (2, 2), (1, 1), (1, 1), (1, 1)),      # stride-2 tiles (forward), generic gather (transposed)
+    (10, 31, 140, (5, 5), (2, 2), (2, 2), (1, 1), (0, 0)),
 ]
 
 

@@ -104,9 +104,11 @@ __global__ void __launch_bounds__(256) dwconvtrans2d_kernel(const DwArgs a, int 
 // adjacent outputs from a KY x (KX + 3) register window: about 1.5 shared-memory reads and KY*KX multiply-adds per
 // output instead of KY*KX bounds-checked global reads.  TRANS selects the transposed convolution, which for unit stride
 // is the same window walked backwards; the taps are still accumulated in (ky, kx) order.
-template <int KY, int KX, bool TRANS>
+template <int KY, int KX, bool TRANS, int ST>
 __global__ void __launch_bounds__(256) dw_tile_kernel(const DwArgs a, int tiles_x, int tiles_y) {
-    constexpr int TH = 16, TW = 64, SH = TH + KY - 1, SW = TW + KX - 1, S = (SW + 3) / 4 * 4;
+    // ST: stride (both directions) of the forward convolution, 1 or 2; the transposed form is tiled for stride 1 only
+    static_assert(!TRANS || ST == 1, "transposed tiles are unit-stride");
+    constexpr int TH = 16, TW = 64, SH = (TH - 1) * ST + KY, SW = (TW - 1) * ST + KX, S = (SW + 3) / 4 * 4;
     __shared__ __align__(16) float tile[SH * S];
     __shared__ float taps[KY * KX];
     int b = blockIdx.x;
@@ -116,7 +118,7 @@ __global__ void __launch_bounds__(256) dw_tile_kernel(const DwArgs a, int tiles_
     const int c = plane % a.C, Q = (a.C + 15) >> 4;
     if (threadIdx.x < KY * KX) taps[threadIdx.x] = tap_value(a.W, Q, threadIdx.x, c);
     const int oy0 = ty * TH, ox0 = tx * TW;
-    const int iy0 = TRANS ? oy0 + a.py - (KY - 1) : oy0 - a.py, ix0 = TRANS ? ox0 + a.px - (KX - 1) : ox0 - a.px;
+    const int iy0 = TRANS ? oy0 + a.py - (KY - 1) : oy0 * ST - a.py, ix0 = TRANS ? ox0 + a.px - (KX - 1) : ox0 * ST - a.px;
     const float *x = a.X + (size_t)plane * a.H * a.Wd;
     for (int i = threadIdx.x; i < SH * SW; i += 256) {
         const int r = i / SW, col = i - r * SW;
@@ -130,18 +132,18 @@ __global__ void __launch_bounds__(256) dw_tile_kernel(const DwArgs a, int tiles_
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int i = 0; i < KY; i++) {
-        const float *row = tile + (r + (TRANS ? KY - 1 - i : i)) * S + 4 * cg;
-        float win[KX + 3];
+        const float *row = tile + (r * ST + (TRANS ? KY - 1 - i : i)) * S + 4 * cg * ST;
+        float win[KX + 3 * ST];
         const float4 v = *reinterpret_cast<const float4 *>(row);
         win[0] = v.x; win[1] = v.y; win[2] = v.z; win[3] = v.w;
 #pragma unroll
-        for (int j = 4; j < KX + 3; j++) win[j] = row[j];
+        for (int j = 4; j < KX + 3 * ST; j++) win[j] = row[j];
 #pragma unroll
         for (int j = 0; j < KX; j++) {
             const float t = taps[i * KX + j];
             const int col = TRANS ? KX - 1 - j : j;
 #pragma unroll
-            for (int q = 0; q < 4; q++) acc[q] = __fmaf_rn(win[q + col], t, acc[q]);
+            for (int q = 0; q < 4; q++) acc[q] = __fmaf_rn(win[q * ST + col], t, acc[q]);
         }
     }
     float *y = a.Y + ((size_t)plane * a.OH + oy) * a.OW + ox;
@@ -327,14 +329,23 @@ static int launch_march(const DwArgs &a, cudaStream_t st, bool &taken) {
 template <bool TRANS>
 static int launch_tiles(const DwArgs &a, cudaStream_t st, bool &taken) {
     taken = false;
-    if (a.sy != 1 || a.sx != 1 || a.dy != 1 || a.dx != 1 || a.ky != a.kx || (a.ky != 3 && a.ky != 5 && a.ky != 7)) return TMQ_OK;
+    if (a.dy != 1 || a.dx != 1 || a.ky != a.kx || (a.ky != 3 && a.ky != 5 && a.ky != 7)) return TMQ_OK;
+    const bool unit = a.sy == 1 && a.sx == 1, two = !TRANS && a.sy == 2 && a.sx == 2 && a.ky <= 5;
+    if (!unit && !two) return TMQ_OK;
     const long long tiles_x = (a.OW + 63) / 64, tiles_y = (a.OH + 15) / 16;
     const long long blocks = tiles_x * tiles_y * a.B * a.C;
     if (blocks > 0x7FFFFFFF) return TMQ_OK;
     taken = true;
-    if (a.ky == 3) dw_tile_kernel<3, 3, TRANS><<<(unsigned)blocks, 256, 0, st>>>(a, (int)tiles_x, (int)tiles_y);
-    else if (a.ky == 5) dw_tile_kernel<5, 5, TRANS><<<(unsigned)blocks, 256, 0, st>>>(a, (int)tiles_x, (int)tiles_y);
-    else dw_tile_kernel<7, 7, TRANS><<<(unsigned)blocks, 256, 0, st>>>(a, (int)tiles_x, (int)tiles_y);
+    const unsigned grid = (unsigned)blocks;
+    const int tx = (int)tiles_x, ty = (int)tiles_y;
+    if (unit) {
+        if (a.ky == 3) dw_tile_kernel<3, 3, TRANS, 1><<<grid, 256, 0, st>>>(a, tx, ty);
+        else if (a.ky == 5) dw_tile_kernel<5, 5, TRANS, 1><<<grid, 256, 0, st>>>(a, tx, ty);
+        else dw_tile_kernel<7, 7, TRANS, 1><<<grid, 256, 0, st>>>(a, tx, ty);
+    } else {
+        if (a.ky == 3) dw_tile_kernel<3, 3, false, 2><<<grid, 256, 0, st>>>(a, tx, ty);
+        else dw_tile_kernel<5, 5, false, 2><<<grid, 256, 0, st>>>(a, tx, ty);
+    }
     return launch_status();
 }
 
