@@ -405,6 +405,20 @@ __global__ void __launch_bounds__(kResWarps * 32, 2) ternary_gemv_resident_kerne
     int group0, G;
     resident_groups(a, group0, G);
     resident_prologue(a, wsm, bar, group0, G);
+    // per-channel scale / bias of the outputs this thread will write (they belong to the weights, not to the chain):
+    // fetched here so that their latency is not paid after the arithmetic
+    float psc[2] = {0.5f, 0.5f}, pbi[2] = {0.0f, 0.0f};      // operands carried +-2.0
+    if (KIND == 0) {
+#pragma unroll
+        for (int q = 0; q < 2; q++) {
+            const int o = threadIdx.x + q * (kResWarps * 32);
+            const long long n = ((long long)group0 + (o >> 7)) * 16 + (o & 15);
+            if (o < G * 128 && n < a.N) {
+                if (a.scale) psc[q] *= a.scale[n];
+                if (a.bias) pbi[q] = a.bias[n];
+            }
+        }
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");   // activations and outputs belong to the chain
     __syncthreads();                                     // the barrier warp 0 initialised is visible to every warp
 
@@ -492,7 +506,10 @@ __global__ void __launch_bounds__(kResWarps * 32, 2) ternary_gemv_resident_kerne
         }
     }
     __syncthreads();
-    for (int o = threadIdx.x; o < G * 128; o += blockDim.x) {
+#pragma unroll
+    for (int q = 0; q < 2; q++) {                        // G * 128 <= 640 outputs, 512 threads
+        const int o = threadIdx.x + q * (kResWarps * 32);
+        if (o >= G * 128) break;
         const int row = o & 15, col = (o >> 4) & 7, grp = o >> 7;
         const long long n = ((long long)group0 + grp) * 16 + row;
         if (n < a.N && col < a.M) {
@@ -502,8 +519,7 @@ __global__ void __launch_bounds__(kResWarps * 32, 2) ternary_gemv_resident_kerne
             if (KIND == 1) {
                 reinterpret_cast<int *>(a.Y)[(long long)col * a.ldy + n] = (int)s;
             } else {
-                const float sc = (a.scale ? a.scale[n] : 1.0f) * 0.5f;  // operands carried +-2.0
-                const float f = fmaf((float)s, sc, a.bias ? a.bias[n] : 0.0f);
+                const float f = fmaf((float)s, psc[q], pbi[q]);
                 if (a.out_f32) reinterpret_cast<float *>(a.Y)[(long long)col * a.ldy + n] = f;
                 else reinterpret_cast<__nv_bfloat16 *>(a.Y)[(long long)col * a.ldy + n] = __float2bfloat16_rn(f);
             }
