@@ -467,6 +467,34 @@ def _finish(dist, line):
     print(json.dumps(line), flush=True)
 
 
+def _resnet_layer_roofline(net, images, peaks, measured_ms):
+    """Per-layer floor of the packed ResNet-18 pass on one GPU: each convolution / linear layer can be no faster than
+    max(2*M*N*K / bf16 peak, (activations in + out at 2 bytes + packed weights) / HBM peak); the sum over the layers against
+    the measured time of the whole pass (which also holds the pooling layers and the launch gaps)."""
+    layers, size = [], 224
+
+    def add(conv, size_in):
+        size_out = (size_in + 2 * conv.padding[0] - conv.dilation[0] * (conv.ky - 1) - 1) // conv.stride[0] + 1
+        m, n, k = images * size_out * size_out, conv.cout, conv.cin * conv.ky * conv.kx
+        in_bytes = images * size_in * size_in * conv.cin * (4 if conv.cin < 64 else 2)      # the stem reads fp32 images
+        nbytes = in_bytes + 2 * m * n + n * k / 4
+        layers.append(max(2.0 * m * n * k / (peaks["bf16_tflops"] * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)))
+        return size_out
+
+    size = add(net.conv1, size)
+    size = (size + 2 - 3) // 2 + 1                       # 3 x 3 / 2 max pooling
+    for c1, c2, down in net.blocks:
+        if down is not None:
+            add(down, size)
+        mid = add(c1, size)
+        size = add(c2, mid)
+    layers.append(max(2.0 * images * net.fc_n * net.fc_k / (peaks["bf16_tflops"] * 1e12),
+                      (2 * images * (net.fc_n + net.fc_k) + net.fc_n * net.fc_k / 4) / (peaks["hbm_gbs"] * 1e9)))
+    ideal_ms = sum(layers) * 1e3
+    return {"bound": "per layer max(tensor, hbm)", "achieved": measured_ms, "peak": ideal_ms, "unit": "ms per pass",
+            "frac": ideal_ms / measured_ms, "traffic": None, "layers": len(layers)}
+
+
 def run_workload(args):
     """Secondary workloads, same launch contract: --workload gemm | resnet_qat | resnet_infer (strong scaling)."""
     if not torch.cuda.is_available():
@@ -572,7 +600,7 @@ def run_workload(args):
                              "frac": 2 * M * (N / world) * K / ms_local / 1e9 / peaks["bf16_tflops"], "traffic": None,
                              "peak_kind": peak_kind, "kernel": "ternary_gemm_kernel<bf16,256>"}}
     elif args.workload in ("resnet_qat", "resnet_infer"):
-        batch = 256
+        batch = args.batch
         b0, b1 = tdist.shard_range(batch, rank, world)
         gen = torch.Generator(device=dev).manual_seed(10 + rank)
         x = torch.randn(b1 - b0, 3, 224, 224, generator=gen, device=dev)
@@ -599,11 +627,14 @@ def run_workload(args):
             ms = timed(lambda i: net(x), args.steps, args.warmup)
             ops.check_gemm_status(dev)
             metric, sharding = "resnet18_packed_inference_images_per_s", "batch sharded, no collective"
+            infer_roofline = _resnet_layer_roofline(net, b1 - b0, peaks, ms)
         line = {"metric": metric, "value": batch / (ms * 1e-3), "unit": "images/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32" if args.workload == "resnet_qat" else "bf16", "data": "synthetic",
-                "config": {"workload": "resnet18_101cls_batch256_224x224", "sharding": sharding,
-                           "macs_per_batch": 4.643e11}}
+                "config": {"workload": f"resnet18_101cls_batch{batch}_224x224", "sharding": sharding,
+                           "macs_per_batch": 4.643e11 * batch / 256}}
+        if args.workload == "resnet_infer":
+            line["roofline"] = infer_roofline
     else:
         raise SystemExit(f"unknown workload {args.workload}")
     if rank == 0:
@@ -626,6 +657,7 @@ def main():
     ap.add_argument("--gemm-m", type=int, default=8192)
     ap.add_argument("--gemm-k", type=int, default=8192)
     ap.add_argument("--gemm-n", type=int, default=28672)
+    ap.add_argument("--batch", type=int, default=256, help="images per step of the ResNet workloads")
     ap.add_argument("--gemv-rows", type=int, default=1)
     ap.add_argument("--gemv-matrices", type=int, default=32)
     args = ap.parse_args()
