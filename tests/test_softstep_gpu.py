@@ -167,3 +167,19 @@ def test_multi_tensor_forms(ops):
     plan.clamp_(-1.0, 1.0)
     for w, b in zip(ws, before):
         assert torch.equal(w, torch.clamp(b, -1.0, 1.0))
+
+
+def test_fused_step_host_matches_device_call():
+    """The pipelined host-buffer entry point: elementwise outputs bit-equal to the device call, loss sum equal to fp64
+    rounding (the chunks' sums are added in order), odd sizes and a chunk size that does not divide the length."""
+    from tmq_b200 import ops
+    gen = torch.Generator().manual_seed(11)
+    for n, chunk in ((1 << 20) + 12345, 1 << 18), (70000, 1 << 16), (1 << 16, 1 << 20):
+        hw = (torch.rand(n, generator=gen) * 3 - 1.5).pin_memory()
+        hg = torch.randn(n, generator=gen).pin_memory()
+        hy, hgw, hwc = (torch.empty(n).pin_memory() for _ in range(3))
+        for d in (0.5, 3.0):
+            loss = ops.fused_step_host(hw, hg, hy, hgw, hwc, d, 5.0, 5e-4, -1.0, 1.0, chunk_elems=chunk)
+            y, gw, wc, want = ops.fused_step(hw.cuda(), hg.cuda(), d, 5.0, 5e-4, -1.0, 1.0)
+            assert torch.equal(hy, y.cpu()) and torch.equal(hgw, gw.cpu()) and torch.equal(hwc, wc.cpu())
+            assert abs(loss - float(want.item())) <= 1e-12 * abs(float(want.item()))

@@ -128,6 +128,81 @@ def fused_step(weights, grad, digamma, sharpness, strength, lo, hi, scale=1.0, g
     return y, gw, wc, loss
 
 
+_host_pipes = {}
+
+
+class _HostPipe:
+    """Streams, events and device staging buffers of fused_step_host for one (device, chunk size)."""
+
+    SLOTS = 3
+
+    def __init__(self, device, chunk):
+        self.device, self.chunk = device, chunk
+        with torch.cuda.device(device):
+            self.s_in, self.s_k, self.s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+            self.buf = [[torch.empty(chunk, dtype=torch.float32, device=device) for _ in range(5)]
+                        for _ in range(self.SLOTS)]           # per slot: w, g, y, gw, wc
+            self.ev_in = [torch.cuda.Event() for _ in range(self.SLOTS)]
+            self.ev_k = [torch.cuda.Event() for _ in range(self.SLOTS)]
+            self.ev_out = [torch.cuda.Event() for _ in range(self.SLOTS)]
+            self.loss = torch.zeros(1, dtype=torch.float64, device=device)
+
+
+def fused_step_host(hw, hg, hy, hgw, hwc, digamma, sharpness, strength, lo, hi, scale=1.0, gq=None, device="cuda",
+                    chunk_elems=1 << 23):
+    """The fused element pass on HOST buffers: hw, hg (inputs) and hy, hgw, hwc (outputs) are flat float32 CPU tensors,
+    pinned for full speed.  The tensors are cut into chunks that flow through three streams - host-to-device copies,
+    the kernel, device-to-host copies - so that the two PCIe directions and the kernel overlap; at most three chunks of
+    staging live on the device.  Returns the loss sum as a Python float (per-chunk fp64 sums added in chunk order) after
+    every output has arrived: the call is synchronous."""
+    for t in (hw, hg, hy, hgw, hwc):
+        if t.dtype != torch.float32 or t.device.type != "cpu" or not t.is_contiguous() or t.numel() != hw.numel():
+            raise RuntimeError("fused_step_host: expected equally sized contiguous float32 CPU tensors")
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    n = hw.numel()
+    chunk = int(min(max(chunk_elems, 1 << 16), max(n, 1)))
+    pipe = _host_pipes.get((device.index, chunk))
+    if pipe is None:
+        pipe = _HostPipe(device, chunk)
+        _host_pipes[(device.index, chunk)] = pipe
+    if gq is None:
+        gq = float(torch.tensor(1.0, dtype=torch.float32) / torch.tensor(float(n), dtype=torch.float32))
+    nchunks = (n + chunk - 1) // chunk
+    if pipe.loss.numel() < nchunks:
+        pipe.loss = torch.zeros(nchunks, dtype=torch.float64, device=device)
+    hw1, hg1, hy1, hgw1, hwc1 = (t.view(-1) for t in (hw, hg, hy, hgw, hwc))
+    with torch.cuda.device(device):
+        start = torch.cuda.Event()
+        start.record()
+        for s in (pipe.s_in, pipe.s_k, pipe.s_out):
+            s.wait_event(start)                   # everything the caller queued before this call comes first
+        for c in range(nchunks):
+            a, b = c * chunk, min(n, (c + 1) * chunk)
+            m, slot = b - a, c % pipe.SLOTS
+            dw, dg, dy, dgw, dwc = (t[:m] for t in pipe.buf[slot])
+            if c >= pipe.SLOTS:
+                pipe.s_in.wait_event(pipe.ev_out[slot])   # the slot's previous outputs have left the device
+            with torch.cuda.stream(pipe.s_in):
+                dw.copy_(hw1[a:b], non_blocking=True)
+                dg.copy_(hg1[a:b], non_blocking=True)
+                pipe.ev_in[slot].record()
+            pipe.s_k.wait_event(pipe.ev_in[slot])
+            with torch.cuda.stream(pipe.s_k):
+                fused_step(dw, dg, digamma, sharpness, strength, lo, hi, scale=scale, gq=gq,
+                           out=(dy, dgw, dwc, pipe.loss[c]))
+                pipe.ev_k[slot].record()
+            pipe.s_out.wait_event(pipe.ev_k[slot])
+            with torch.cuda.stream(pipe.s_out):
+                hy1[a:b].copy_(dy, non_blocking=True)
+                hgw1[a:b].copy_(dgw, non_blocking=True)
+                hwc1[a:b].copy_(dwc, non_blocking=True)
+                pipe.ev_out[slot].record()
+        pipe.s_out.synchronize()
+        return float(pipe.loss[:nchunks].cpu().sum().item()) if nchunks > 1 else float(pipe.loss[0].item())
+
+
 def selftest_const_div(digamma, device="cuda"):
     cnt = torch.zeros((), dtype=torch.int64, device=device)
     with torch.cuda.device(cnt.device):
