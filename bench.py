@@ -624,10 +624,15 @@ def run_workload(args):
             model.to(dev).train()
             for e in range(1, 45):
                 ctrl.step(e)
-            opt = torch.optim.Adam(model.parameters(), lr=1e-3)
             bucket = tdist.FlatGradBucket(model.parameters()) if world > 1 else None
+            if args.fused_optimizer:      # Adam + clamp as one multi-tensor launch (plus one for the unclamped parameters)
+                opt = workloads.fused_optimizer(model, ctrl, lr=1e-3, bucket=bucket)
+            else:
+                opt = torch.optim.Adam(model.parameters(), lr=1e-3)
             ms = timed(lambda i: workloads.qat_step(model, ctrl, opt, x, y, bucket), args.steps, args.warmup)
             metric, sharding = "resnet18_qat_images_per_s", "data parallel, one flat fp32 gradient all-reduce per step"
+            if args.fused_optimizer:
+                sharding += "; fused multi-tensor Adam + clamp"
         else:
             model, ctrl = workloads.build_resnet18(101, ctrl=tmq.QuantizationControl())
             with torch.no_grad():
@@ -671,6 +676,7 @@ def main():
     ap.add_argument("--gemm-k", type=int, default=8192)
     ap.add_argument("--gemm-n", type=int, default=28672)
     ap.add_argument("--batch", type=int, default=256, help="images per step of the ResNet workloads")
+    ap.add_argument("--fused-optimizer", action="store_true", help="resnet_qat: multi-tensor Adam with the clamp fused in")
     ap.add_argument("--gemv-rows", type=int, default=1)
     ap.add_argument("--gemv-matrices", type=int, default=32)
     args = ap.parse_args()

@@ -108,6 +108,13 @@ int tmq_mt_qloss(const void *d_plan, int ntensors, int nchunks, double sharpness
 int tmq_mt_qloss_bwd(const void *d_plan, int ntensors, int nchunks, double sharpness, double strength,
                      const float *d_upstream, float *out_base, void *stream);
 /* w_l = clamp(w_l, lo, hi) in place */
+/* Fused optimizer of the QAT step: torch.optim.Adam's update (single-tensor sequence, fp32, one rounding per operation)
+ * of every tensor of a plan in one launch, followed by clamp(w, lo, hi) when `clamp` is set - the optimizer step and
+ * QuantizationControl.clamp (tmq/tmq.py:263-272) read and write the weights once between them.  In THIS plan a tensor's
+ * `out` field is its gradient and `out_offset` its slice of the flat moment buffers m_base / v_base (exp_avg,
+ * exp_avg_sq); `step` is the 1-based step count of the bias corrections. */
+int tmq_mt_adam_clamp(const void *d_plan, int ntensors, int nchunks, float *m_base, float *v_base, double lr, double beta1,
+                      double beta2, double eps, long long step, int clamp, float lo, float hi, void *stream);
 int tmq_mt_clamp(const void *d_plan, int ntensors, int nchunks, float lo, float hi, void *stream);
 
 /* Device self-check of the constant-divisor fast path used inside the kernels above: counts, over every finite

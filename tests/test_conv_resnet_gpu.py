@@ -113,6 +113,40 @@ def test_fused_stem_convolution(c, h, w, n, k, s, p):
     assert torch.equal(y, via_patches)
 
 
+def test_qat_step_with_fused_optimizer_matches_adam_plus_clamp():
+    """One QAT step of a small TMQ model with ops.MultiTensorAdam (clamp fused in) against torch.optim.Adam followed by
+    QuantizationControl.clamp, from identical initial states."""
+    import copy
+    import tmq_b200 as tmq
+    from tmq_b200 import workloads
+    torch.manual_seed(3)
+    net = torch.nn.Sequential(torch.nn.Linear(48, 64), torch.nn.ReLU(), torch.nn.Linear(64, 10)).cuda()
+    ctrl = tmq.QuantizationControl(epoch_knots=tmq.QuantizationScheduleBuilder.default_schedule(50),
+                                   qpenalty_range=(0.0, 1e-3), device="cuda")
+    tmq.quantize_model(net, ctrl)
+    for e in range(1, 30):
+        ctrl.step(e)
+    with torch.no_grad():
+        for node in ctrl._registry.values():
+            node.weight.mul_(1.3)                      # some weights beyond the clamp range
+    net_b = copy.deepcopy(net)                        # copies the controller along with the layers that hold it
+    ctrl_b = next(m for m in net_b.modules() if isinstance(m, tmq.TMQLayer))._ctrl
+    assert ctrl_b is not ctrl and len(ctrl_b._registry) == len(ctrl._registry)
+    x = torch.randn(32, 48, device="cuda")
+    y = torch.randint(0, 10, (32,), device="cuda")
+    net.train(); net_b.train()
+    opt_a = torch.optim.Adam(net.parameters(), lr=1e-2)
+    opt_b = workloads.fused_optimizer(net_b, ctrl_b, lr=1e-2)
+    for _ in range(3):
+        la = workloads.qat_step(net, ctrl, opt_a, x, y)[0]
+        lb = workloads.qat_step(net_b, ctrl_b, opt_b, x, y)[0]
+        assert abs(float(la) - float(lb)) <= 1e-5 * max(1.0, abs(float(la)))
+    for pa, pb in zip(net.parameters(), net_b.parameters()):
+        assert torch.allclose(pa, pb, rtol=1e-5, atol=1e-6)
+    for node in ctrl_b._registry.values():
+        assert float(node.weight.detach().min()) >= -1.0 and float(node.weight.detach().max()) <= 1.0
+
+
 def test_maxpool_nhwc_matches_torch():
     from tmq_b200 import ops
     gen = torch.Generator().manual_seed(3)

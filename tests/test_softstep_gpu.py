@@ -183,3 +183,37 @@ def test_fused_step_host_matches_device_call():
             y, gw, wc, want = ops.fused_step(hw.cuda(), hg.cuda(), d, 5.0, 5e-4, -1.0, 1.0)
             assert torch.equal(hy, y.cpu()) and torch.equal(hgw, gw.cpu()) and torch.equal(hwc, wc.cpu())
             assert abs(loss - float(want.item())) <= 1e-12 * abs(float(want.item()))
+
+
+def test_multi_tensor_adam_with_clamp_matches_torch_adam():
+    """Fused Adam + clamp over several tensors (ragged sizes) against torch.optim.Adam on the CPU followed by
+    torch.clamp, six steps with fresh gradients each: parameters and both moments to a few fp32 ulps."""
+    from tmq_b200 import ops
+    gen = torch.Generator().manual_seed(5)
+    shapes = [(64, 33), (128,), (7, 3, 3, 3), (4099,), (1,)]
+    ref = [torch.nn.Parameter(torch.rand(s, generator=gen) * 2.4 - 1.2) for s in shapes]
+    dev = [torch.nn.Parameter(p.detach().clone().cuda()) for p in ref]
+    opt_ref = torch.optim.Adam(ref, lr=0.05, betas=(0.9, 0.999), eps=1e-8, foreach=False)
+    clamp_idx = (0, 2, 3)
+    opt = ops.MultiTensorAdam(dev, lr=0.05, betas=(0.9, 0.999), eps=1e-8, clamp_params=[dev[i] for i in clamp_idx],
+                              clamp=(-1.0, 1.0))
+    for step in range(6):
+        grads = [torch.randn(s, generator=gen) * (0.1 if step % 2 else 3.0) for s in shapes]
+        opt.zero_grad()
+        for p, q, g in zip(ref, dev, grads):
+            p.grad = g.clone()
+            q.grad.copy_(g)                                   # .grad views the flat buffer
+        opt_ref.step()
+        with torch.no_grad():
+            for i in clamp_idx:
+                ref[i].copy_(torch.clamp(ref[i], -1.0, 1.0))
+        opt.step()
+        for i, (p, q) in enumerate(zip(ref, dev)):
+            assert torch.allclose(q.detach().cpu(), p.detach(), rtol=2e-6, atol=1e-7), (step, i)
+    for i, p in enumerate(ref):
+        st = opt_ref.state[p]
+        a, b = opt.offsets[i], opt.offsets[i] + p.numel()
+        assert torch.allclose(opt.exp_avg[a:b].cpu().view_as(p), st["exp_avg"], rtol=1e-5, atol=1e-6)     # O(1) values, cancellation
+        assert torch.allclose(opt.exp_avg_sq[a:b].cpu().view_as(p), st["exp_avg_sq"], rtol=1e-5, atol=1e-9)
+    for i in clamp_idx:
+        assert float(dev[i].min()) >= -1.0 and float(dev[i].max()) <= 1.0

@@ -38,6 +38,8 @@ _SIGNATURES = {
     "tmq_mt_plan_build": (c_int, [ctypes.POINTER(MtTensor), c_int, c_void_p, c_size_t, ctypes.POINTER(c_int)]),
     "tmq_mt_qloss": (c_int, [c_void_p, c_int, c_int, c_double, c_double, c_void_p, c_void_p, c_size_t, c_void_p]),
     "tmq_mt_qloss_bwd": (c_int, [c_void_p, c_int, c_int, c_double, c_double, c_void_p, c_void_p, c_void_p]),
+    "tmq_mt_adam_clamp": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_double, c_double, c_double, c_double,
+                                  ctypes.c_longlong, c_int, c_float, c_float, c_void_p]),
     "tmq_mt_clamp": (c_int, [c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
     "tmq_selftest_div": (c_int, [ctypes.c_uint, ctypes.c_uint64, ctypes.c_uint64, c_void_p, c_void_p]),
     "tmq_selftest_const_div": (c_int, [c_double, c_void_p, c_void_p]),

@@ -528,6 +528,83 @@ __global__ void __launch_bounds__(kThreads) softstep_mt_kernel(const MtTensor *_
     }
 }
 
+// ---------------------------------------------------------------------------------------------------- fused optimizer
+
+// Adam update of every tensor of a plan in one launch, optionally followed by the clamp of the QAT step, so that the
+// weights are read and written once for both: per element 16 bytes read (w, g, m, v) and 12 written (w, m, v).
+// The plan's `out` field of a tensor carries its GRADIENT, `out_offset` its slice of the flat moment buffers.
+// Arithmetic: torch.optim.Adam's single-tensor sequence (torch/optim/adam.py, _single_tensor_adam) in fp32, one rounding
+// per operation:   m += (g - m) * (1 - b1);  v = v * b2 + ((1 - b2) * g) * g;
+//                  w += -(lr / (1 - b1^t)) * (m / (sqrt(v) / sqrt(1 - b2^t) + eps));   w = clamp(w, lo, hi)
+struct AdamArgs {
+    float w1, b2, w2, bc2_sqrt, eps, neg_step, lo, hi;
+    int clamp;
+};
+
+__global__ void __launch_bounds__(kThreads) adam_clamp_mt_kernel(const MtTensor *__restrict__ tensors,
+                                                                  const MtChunk *__restrict__ chunks, int nchunks,
+                                                                  float *__restrict__ m_base, float *__restrict__ v_base,
+                                                                  const AdamArgs a) {
+    auto update = [&](float &w, float g, float &m, float &v) {
+        m = __fadd_rn(m, __fmul_rn(__fsub_rn(g, m), a.w1));
+        v = __fadd_rn(__fmul_rn(v, a.b2), __fmul_rn(__fmul_rn(a.w2, g), g));
+        const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(v), a.bc2_sqrt), a.eps);
+        w = __fadd_rn(w, __fmul_rn(a.neg_step, __fdiv_rn(m, denom)));
+        if (a.clamp) w = clamp_nan(w, a.lo, a.hi);
+    };
+    for (int c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const MtChunk ch = chunks[c];
+        const MtTensor t = tensors[ch.tensor];
+        const size_t begin = (size_t)ch.index * kChunk;
+        const size_t count = (t.n - begin) < (size_t)kChunk ? (size_t)(t.n - begin) : (size_t)kChunk;
+        float *w = const_cast<float *>(t.w) + begin;
+        const float *g = t.out + begin;
+        float *m = m_base + t.out_offset + begin, *v = v_base + t.out_offset + begin;
+        const size_t nv = count / 4;
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const size_t i = threadIdx.x + (size_t)u * kThreads;
+            if (i < nv) {
+                float4 wv = reinterpret_cast<float4 *>(w)[i], gv = __ldg(reinterpret_cast<const float4 *>(g) + i);
+                float4 mv = reinterpret_cast<float4 *>(m)[i], vv = reinterpret_cast<float4 *>(v)[i];
+                update(wv.x, gv.x, mv.x, vv.x);
+                update(wv.y, gv.y, mv.y, vv.y);
+                update(wv.z, gv.z, mv.z, vv.z);
+                update(wv.w, gv.w, mv.w, vv.w);
+                reinterpret_cast<float4 *>(w)[i] = wv;
+                reinterpret_cast<float4 *>(m)[i] = mv;
+                reinterpret_cast<float4 *>(v)[i] = vv;
+            }
+        }
+        const size_t i = nv * 4 + threadIdx.x;
+        if (i < count) update(w[i], g[i], m[i], v[i]);
+    }
+}
+
+extern "C" int tmq_mt_adam_clamp(const void *d_plan, int ntensors, int nchunks, float *m_base, float *v_base, double lr,
+                                 double beta1, double beta2, double eps, long long step, int clamp, float lo, float hi,
+                                 void *stream) {
+    if (!d_plan || ntensors <= 0 || nchunks <= 0 || !m_base || !v_base || step < 1) return TMQ_ERR_ARG;
+    if (!(lr >= 0.0) || !(beta1 >= 0.0 && beta1 < 1.0) || !(beta2 >= 0.0 && beta2 < 1.0) || !(eps >= 0.0)) return TMQ_ERR_ARG;
+    if (clamp && !(lo <= hi)) return TMQ_ERR_ARG;
+    if (!aligned(d_plan, 8) || !aligned(m_base, 16) || !aligned(v_base, 16)) return TMQ_ERR_ALIGN;
+    // scalars as torch forms them: Python doubles, cast to the tensors' fp32 inside the kernel
+    const double bc1 = 1.0 - pow(beta1, (double)step), bc2 = 1.0 - pow(beta2, (double)step);
+    AdamArgs a;
+    a.w1 = (float)(1.0 - beta1);
+    a.b2 = (float)beta2;
+    a.w2 = (float)(1.0 - beta2);
+    a.bc2_sqrt = (float)sqrt(bc2);
+    a.eps = (float)eps;
+    a.neg_step = (float)(-(lr / bc1));
+    a.lo = lo; a.hi = hi; a.clamp = clamp;
+    const MtTensor *T = reinterpret_cast<const MtTensor *>(d_plan);
+    const MtChunk *C = reinterpret_cast<const MtChunk *>(T + ntensors);
+    const unsigned grid = (unsigned)(nchunks < kMaxPartials ? nchunks : kMaxPartials);
+    adam_clamp_mt_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>(T, C, nchunks, m_base, v_base, a);
+    return launch_status();
+}
+
 // ---------------------------------------------------------------------------------------------------- self-test
 
 __global__ void const_div_selftest_kernel(float D, float rD, unsigned long long *mismatches) {

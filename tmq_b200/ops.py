@@ -292,6 +292,81 @@ class MultiTensorPlan:
 
 # ------------------------------------------------------------------------------------------------ packing
 
+class MultiTensorAdam:
+    """torch.optim.Adam (no weight decay, no amsgrad) for a fixed list of fp32 CUDA parameters as ONE launch per step,
+    with the QAT clamp fused in for the parameters listed in `clamp_params` (one more launch for the others).
+    Gradients live in a flat buffer (each parameter's .grad is a view into it, as with dist.FlatGradBucket - pass that
+    bucket to share its buffer), the moments in two more flat buffers."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, clamp_params=(), clamp=(-1.0, 1.0), bucket=None):
+        self.params = [p for p in params if p.requires_grad]
+        if not self.params:
+            raise ValueError("MultiTensorAdam: no trainable parameters")
+        self.lr, self.betas, self.eps, self.clamp, self.steps = float(lr), (float(betas[0]), float(betas[1])), float(eps), clamp, 0
+        dev = self.params[0].device
+        for p in self.params:
+            if p.device != dev or dev.type != "cuda" or p.dtype != torch.float32 or not p.is_contiguous():
+                raise RuntimeError("MultiTensorAdam: parameters must be contiguous fp32 tensors on one CUDA device")
+        self.device = dev
+        if bucket is not None:
+            if [id(p) for p in bucket.params] != [id(p) for p in self.params]:
+                raise ValueError("MultiTensorAdam: the bucket must hold the same parameters in the same order")
+            self.offsets, self.grad = list(bucket.offsets), bucket.flat
+        else:
+            self.offsets, total = [], 0
+            for p in self.params:
+                self.offsets.append(total)
+                total += (p.numel() + 3) // 4 * 4
+            self.grad = torch.zeros(total, dtype=torch.float32, device=dev)
+            for p, off in zip(self.params, self.offsets):
+                p.grad = self.grad[off:off + p.numel()].view_as(p)
+        self.exp_avg = torch.zeros_like(self.grad)
+        self.exp_avg_sq = torch.zeros_like(self.grad)
+        clamp_ids = {id(p) for p in clamp_params}
+        groups = ([i for i, p in enumerate(self.params) if id(p) in clamp_ids],
+                  [i for i, p in enumerate(self.params) if id(p) not in clamp_ids])
+        self.groups = groups
+        self.plans = [self._plan(idx) if idx else None for idx in groups]     # [clamped, plain]
+
+    def _plan(self, idx):
+        n = len(idx)
+        arr = (_lib.MtTensor * n)()
+        for j, i in enumerate(idx):
+            p = self.params[i]
+            arr[j].w = p.data_ptr()
+            arr[j].out = self.grad.data_ptr() + 4 * self.offsets[i]
+            arr[j].n = p.numel()
+            arr[j].out_offset = self.offsets[i]
+        nbytes = lib().tmq_mt_plan_bytes(arr, n)
+        host = torch.empty(nbytes, dtype=torch.uint8)
+        nchunks = ctypes.c_int(0)
+        check(lib().tmq_mt_plan_build(arr, n, ctypes.c_void_p(host.data_ptr()), nbytes, ctypes.byref(nchunks)),
+              "mt_plan_build")
+        return host.to(self.device), n, nchunks.value, [self.params[i].data_ptr() for i in idx]
+
+    def zero_grad(self):
+        self.grad.zero_()
+
+    @torch.no_grad()
+    def step(self):
+        for p, off in zip(self.params, self.offsets):
+            if p.grad is None or p.grad.data_ptr() != self.grad.data_ptr() + 4 * off:
+                raise RuntimeError("MultiTensorAdam: a parameter's .grad no longer views the flat gradient buffer "
+                                   "(use zero_grad() of this object, not set_to_none)")
+        self.steps += 1
+        for k, plan in enumerate(self.plans):
+            if plan is None:
+                continue
+            table, n, nchunks, ptrs = plan
+            if any(q != r for q, r in zip(ptrs, [self.params[i].data_ptr() for i in self.groups[k]])):
+                raise RuntimeError("MultiTensorAdam: a parameter's storage was rebound since construction")
+            with torch.cuda.device(self.device):
+                check(lib().tmq_mt_adam_clamp(_ptr(table), n, nchunks, _ptr(self.exp_avg), _ptr(self.exp_avg_sq), self.lr,
+                                              self.betas[0], self.betas[1], self.eps, self.steps, 1 if k == 0 else 0,
+                                              float(self.clamp[0]), float(self.clamp[1]), _stream(self.grad)),
+                      "mt_adam_clamp")
+
+
 def _work_device(t):
     """Packing runs on the GPU; host tensors make a round trip through the current device."""
     if t.device.type == "cuda":

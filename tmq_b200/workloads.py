@@ -28,11 +28,22 @@ def build_resnet18(num_classes=101, ctrl=None, max_epochs=50, qpenalty_range=(0.
     return model, ctrl
 
 
+def fused_optimizer(model, ctrl, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, bucket=None):
+    """ops.MultiTensorAdam over the model's parameters with the QAT clamp fused in for every registered TMQ layer."""
+    lo, hi = ctrl.clamp_values
+    return ops.MultiTensorAdam(model.parameters(), lr=lr, betas=betas, eps=eps, bucket=bucket,
+                               clamp_params=[node.weight for node in ctrl._registry.values()], clamp=(lo, hi))
+
+
 def qat_step(model, ctrl, optimizer, x, y, bucket=None):
     """One training step on this rank's slice of the batch.  With a FlatGradBucket the gradients are averaged over
-    the ranks with a single all-reduce before the optimizer runs.  Returns (loss, cross-entropy, quantization loss)."""
+    the ranks with a single all-reduce before the optimizer runs.  `optimizer` may be an ops.MultiTensorAdam (see
+    fused_optimizer): it then also performs the clamp.  Returns (loss, cross-entropy, quantization loss)."""
+    fused = isinstance(optimizer, ops.MultiTensorAdam)
     if bucket is not None:
         bucket.zero()
+    elif fused:
+        optimizer.zero_grad()
     else:
         optimizer.zero_grad(set_to_none=True)
     logits = model(x)
@@ -43,7 +54,8 @@ def qat_step(model, ctrl, optimizer, x, y, bucket=None):
     if bucket is not None:
         bucket.allreduce_mean()
     optimizer.step()
-    ctrl.clamp()
+    if not fused:
+        ctrl.clamp()
     return loss.detach(), ce.detach(), (ql.detach() if ql is not None else None)
 
 
