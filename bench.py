@@ -363,6 +363,11 @@ def ternary_sections(peaks):
                                          "frac_of_nominal_4500": tf / 4500.0}
     del wt8, X8, P
     # ---- config 3: 32 distinct matrices (352 MB > L2) back to back in one CUDA graph
+    # (a few idle seconds first: the GEMMs above ran into the power cap, and these latency-bound launches should not
+    # inherit their clocks)
+    torch.cuda.synchronize()
+    import time
+    time.sleep(4.0)
     N, K, NM = 11008, 4096, 32
     wts = []
     for i in range(NM):
