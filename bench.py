@@ -595,6 +595,22 @@ def run_workload(args):
                 "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind,
                              "algorithmic_bytes_per_launch": nbytes}}
+    elif args.workload == "adam":
+        # fused multi-tensor Adam + clamp: 64 tensors of 2^19 elements (w, g, m, v: 537 MB > L2), 28 bytes per element
+        gen = torch.Generator(device=dev).manual_seed(rank)
+        params = [torch.nn.Parameter(torch.rand(1 << 19, generator=gen, device=dev) * 2.4 - 1.2) for _ in range(64)]
+        opt = ops.MultiTensorAdam(params, lr=1e-3, clamp_params=params, clamp=(-1.0, 1.0))
+        opt.grad.copy_(torch.randn(opt.grad.numel(), generator=gen, device=dev))
+        ms = timed(lambda i: opt.step(), args.steps, args.warmup)
+        nbytes = 28 * sum(p.numel() for p in params)
+        line = {"metric": "fused_adam_clamp_GBps", "value": world * nbytes / ms / 1e6, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "multi_tensor_adam_clamp_64x2^19", "l2": "537 MB of state per step"},
+                "gpu_launches": args.steps,
+                "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind,
+                             "algorithmic_bytes_per_launch": nbytes}}
     elif args.workload == "gemm":
         M, K, N = args.gemm_m, args.gemm_k, args.gemm_n
         P = _ternary_packed(ops, N, K, 0)                         # same seed on every rank: the same matrix
@@ -676,7 +692,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-extra", action="store_true", help="skip the ternary GEMM / GEMV sections")
-    ap.add_argument("--workload", default="softstep", choices=["softstep", "gemm", "gemv", "resnet_qat", "resnet_infer", "dwconv", "dwconvtrans"])
+    ap.add_argument("--workload", default="softstep", choices=["softstep", "gemm", "gemv", "resnet_qat", "resnet_infer", "dwconv", "dwconvtrans", "adam"])
     ap.add_argument("--gemm-m", type=int, default=8192)
     ap.add_argument("--gemm-k", type=int, default=8192)
     ap.add_argument("--gemm-n", type=int, default=28672)
