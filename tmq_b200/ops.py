@@ -149,7 +149,7 @@ class _HostPipe:
 
 
 def fused_step_host(hw, hg, hy, hgw, hwc, digamma, sharpness, strength, lo, hi, scale=1.0, gq=None, device="cuda",
-                    chunk_elems=1 << 23):
+                    chunk_elems=1 << 22):
     """The fused element pass on HOST buffers: hw, hg (inputs) and hy, hgw, hwc (outputs) are flat float32 CPU tensors,
     pinned for full speed.  The tensors are cut into chunks that flow through three streams - host-to-device copies,
     the kernel, device-to-host copies - so that the two PCIe directions and the kernel overlap; at most three chunks of
