@@ -10,8 +10,12 @@ cycling through {0.1, 0.5, 0.9, 1.0}).  Algorithmic traffic 20 B/element (read w
 Prints one JSON line (rank 0).  `value` is device-resident throughput; `e2e` is the same pass through the public
 operator call with pinned HOST buffers (H2D of w and g, D2H of the three outputs and the loss, every step).
 With --gpus N every rank processes its own 2^26-element shard (weak scaling) and the loss scalar is all-reduced
-over NCCL inside the step.  `--impl reference` times the reference's CPU path (PyTorch CPU eager op sequence,
-restated in oracle/softstep_torch.py) on the host cores, on a bounded sample.
+over NCCL inside the step.  `--impl reference` times the reference's CPU path for the same workload on all host
+threads: the reference's own tmq/tmq.py (SoftStep / SoftStepDerivative autograd functions, torch.mean, backward,
+torch.clamp: PyTorch CPU eager) when a checkout is present (TMQ_REFERENCE_DIR or a checkout beside this repository), else
+its restatement oracle/softstep_torch.py; one step = the full 2^26-element pass.  For N > 1 the default run also measures
+the three partitionings that move data (column-sharded prefill GEMM, data-parallel ResNet-18 QAT, batch-sharded packed
+ResNet-18 inference) and reports them under `extra`.
 """
 import argparse
 import json
@@ -27,6 +31,7 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+GEMV_ROWS_PER_PASS = 8      # activation rows one skinny-kernel launch takes
 HARDNESS = [0.1, 0.5, 0.9, 1.0]
 SHARPNESS, STRENGTH, LO, HI = 5.0, 5e-4, -1.0, 1.0
 BYTES_PER_ELEM = 20
@@ -105,39 +110,99 @@ def dist_setup(n_gpus):
 
 # ------------------------------------------------------------------------------------------------ CPU arm
 
-def cpu_softstep_baseline(sample_elems, reps):
-    """Reference CPU path (PyTorch eager op sequence) on all host threads; returns GB/s at 20 B/elem."""
-    from oracle import softstep_torch as OT
+def softstep_config(n, world):
+    """`config` of the headline workload; both arms print exactly this."""
+    return {"workload": "softstep_fused_2^26_f32", "elements_per_gpu": n, "hardness": HARDNESS,
+            "sharpness": SHARPNESS, "strength": STRENGTH, "bytes_per_element": BYTES_PER_ELEM,
+            "l2": "inputs (w, g: 2 x 256 MiB) exceed the 126 MB L2; no flush needed",
+            "sharding": ("one shard per GPU, fp64 loss scalar all-reduced (NCCL, asynchronous: overlaps the next step, "
+                         "drained inside the timed region)") if world > 1 else "single GPU"}
+
+
+def host_threads():
+    """Every host thread this process may run on (torchrun exports OMP_NUM_THREADS=1; the CPU arm must not inherit it)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(n, 1))
+    return torch.get_num_threads()
+
+
+def load_reference():
+    """The reference's own Python module when its checkout is on this machine, else None."""
+    import contextlib
+    import io
+    ref_dir = os.environ.get("TMQ_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
+    if not os.path.isfile(os.path.join(ref_dir, "tmq", "tmq.py")):
+        return None
+    sys.path.insert(0, ref_dir)
+    try:
+        with contextlib.redirect_stdout(io.StringIO()), contextlib.redirect_stderr(io.StringIO()):
+            import tmq as ref
+    except Exception:
+        return None
+    finally:
+        sys.path.remove(ref_dir)
+    return ref
+
+
+class _Ctrl:
+    def __init__(self, digamma):
+        self.digamma = digamma
+
+
+def cpu_element_pass(ref):
+    """One QAT element pass on CPU tensors: forward, loss mean, both backwards (autograd, accumulated into .grad),
+    clamp - through the reference's autograd functions (tmq/tmq.py:404-493, :696-699) or their restatement."""
+    if ref is None:
+        from oracle import softstep_torch as OT
+        return "port", OT.qat_element_pass
+
+    def run(w, g, digamma, sharpness, strength, lo, hi):
+        w = w.detach().requires_grad_(True)
+        y = ref.SoftStep.apply(w, 1.0, _Ctrl(digamma))
+        loss = torch.mean(ref.SoftStepDerivative.apply(w, sharpness, strength))
+        torch.autograd.backward([y, loss], [g, torch.ones_like(loss)])
+        with torch.no_grad():
+            wc = torch.clamp(w, lo, hi)
+        return y.detach(), w.grad, wc, loss.detach()
+    return "reference", run
+
+
+def cpu_softstep_baseline(elems, reps, warm=1):
+    """The reference CPU path on all host threads; returns (GB/s at 20 B/elem, seconds per pass, kind, threads)."""
+    cores = host_threads()
+    kind, run = cpu_element_pass(load_reference())
     gen = torch.Generator().manual_seed(0)
-    w = torch.rand(sample_elems, generator=gen) * 3 - 1.5
-    g = torch.randn(sample_elems, generator=gen)
-    OT.qat_element_pass(w, g, HARDNESS[0], SHARPNESS, STRENGTH, LO, HI)       # warm
+    w = torch.rand(elems, generator=gen) * 3 - 1.5
+    g = torch.randn(elems, generator=gen)
+    for i in range(warm):
+        run(w, g, HARDNESS[i % 4], SHARPNESS, STRENGTH, LO, HI)
     t0 = time.perf_counter()
     for i in range(reps):
-        OT.qat_element_pass(w, g, HARDNESS[i % 4], SHARPNESS, STRENGTH, LO, HI)
+        run(w, g, HARDNESS[i % 4], SHARPNESS, STRENGTH, LO, HI)
     dt = (time.perf_counter() - t0) / reps
-    return sample_elems * BYTES_PER_ELEM / dt / 1e9, dt
+    return elems * BYTES_PER_ELEM / dt / 1e9, dt, kind, cores
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 1 << 24
-    cores = torch.get_num_threads()
-    for i in range(args.warmup):
-        cpu_softstep_baseline(sample, 1)
-    gbs, dt = cpu_softstep_baseline(sample, args.steps)
-    n_full = args.n
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    n = args.n
+    gbs, dt, kind, cores = cpu_softstep_baseline(n, args.steps, warm=args.warmup)
+    what = ("the reference's own tmq/tmq.py autograd functions" if kind == "reference"
+            else "restatement of the reference's autograd functions (no reference checkout on this machine)")
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3 * (n_full / sample), "higher_is_better": True,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "softstep_fused_2^26_f32", "elements": n_full, "hardness": HARDNESS,
-                   "bytes_per_element": BYTES_PER_ELEM},
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"2^24 of 2^26 elements per step; PyTorch CPU eager op sequence of the reference "
-                                   f"(forward, loss mean, both backwards, clamp); ms_per_step scaled x4"},
+        "config": softstep_config(n, max(world, args.gpus)),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
+                         "sample": f"every step is one full pass over {n} elements on one host process ({what}; PyTorch "
+                                   f"CPU eager: forward, loss mean, both backwards through autograd, clamp)"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -247,7 +312,54 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item()) / max(e2e_steps, 1)
     e2e_value = world * n * BYTES_PER_ELEM / (e2e_ms * 1e-3) / 1e9 if e2e_steps else None
+
+    # where the end-to-end time goes: each copy direction alone, every rank at once (the ranks share the host's memory
+    # and its PCIe root complexes), max over ranks like every other multi-GPU time here
+    legs = {}
+    if e2e_steps:
+        def leg(fn):
+            fn()
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(3):
+                fn()
+            a1.record()
+            barrier()
+            tt = torch.tensor([a0.elapsed_time(a1) / 3], dtype=torch.float64, device=dev)
+            if dist is not None:
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return float(tt.item())
+        ms_in = leg(lambda: (w.copy_(hw, non_blocking=True), g.copy_(hg, non_blocking=True)))
+        ms_out = leg(lambda: (hy.copy_(out[0], non_blocking=True), hgw.copy_(out[1], non_blocking=True),
+                              hwc.copy_(out[2], non_blocking=True)))
+        legs = {"h2d_only_ms": ms_in, "h2d_only_GBps_aggregate": world * 2 * n * 4 / ms_in / 1e6,
+                "d2h_only_ms": ms_out, "d2h_only_GBps_aggregate": world * 3 * n * 4 / ms_out / 1e6,
+                "kernel_only_ms": kernel_ms,
+                "reading": "the step cannot beat max(h2d_only, d2h_only): the two directions overlap, the kernel hides under both"}
     clocks = sampler.stop() if rank == 0 else None
+
+    # the workloads that move data between GPUs (N > 1), or that complete the single-GPU picture (N = 1); every rank
+    # takes part, rank 0 reports
+    extra = {}
+    if not args.no_extra:
+        del hw, hg, hy, hgw, hwc
+        del w, g, out, loss_ring
+        torch.cuda.empty_cache()
+        ctx = _Ctx(dist, rank, world, dev)
+        xs, xw = max(3, min(args.steps, 10)), 3
+        if world == 1:
+            extra = ternary_sections(ctx.peaks)
+            extra["resnet18_packed_inference_batch256"] = wl_resnet(ctx, "infer", xs, xw, per_layer=True)
+            torch.cuda.empty_cache()
+            extra["resnet18_qat_batch256"] = wl_resnet(ctx, "qat", xs, xw)
+        else:
+            extra["column_sharded_gemm_M8192_K8192_N28672"] = wl_gemm(ctx, xs, xw)
+            torch.cuda.empty_cache()
+            extra["resnet18_packed_inference_batch256"] = wl_resnet(ctx, "infer", xs, xw)
+            torch.cuda.empty_cache()
+            extra["resnet18_qat_batch256"] = wl_resnet(ctx, "qat", xs, xw)
+        torch.cuda.empty_cache()
 
     if rank != 0:
         if dist is not None:
@@ -260,13 +372,11 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "softstep_fused_2^26_f32", "elements_per_gpu": n, "hardness": HARDNESS,
-                   "sharpness": SHARPNESS, "strength": STRENGTH, "bytes_per_element": BYTES_PER_ELEM,
-                   "l2": "inputs (w, g: 2 x 256 MiB) exceed the 126 MB L2; no flush needed",
-                   "sharding": "one shard per GPU, fp64 loss scalar all-reduced (NCCL, asynchronous: overlaps the next step, drained inside the timed region)" if world > 1 else "single GPU"},
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 2 * n * 4, "d2h_bytes_per_step": 3 * n * 4 + 8 * 16,
-                "ms_per_step": e2e_ms, "steps": e2e_steps,
-                "call": "ops.fused_step_host: pinned host buffers, 16 chunks of 2^22 elements pipelined over three streams"},
+        "config": softstep_config(n, world),
+        "e2e": dict({"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 2 * n * 4, "d2h_bytes_per_step": 3 * n * 4 + 8 * 16,
+                     "ms_per_step": e2e_ms, "steps": e2e_steps,
+                     "call": "ops.fused_step_host: pinned host buffers, 16 chunks of 2^22 elements pipelined over three streams"},
+                    **legs),
         "gpu_launches": args.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -277,15 +387,13 @@ def run_ours(args):
                      "kernel": "softstep_kernel<FWD|BWD|QSUM|QGRAD|CLAMP>", "kernel_ms": kernel_ms,
                      "algorithmic_bytes": n * BYTES_PER_ELEM},
     }
-    if world == 1 and not args.no_extra:
-        del w, g, out
-        torch.cuda.empty_cache()
-        line["extra"] = ternary_sections(peaks)
+    if extra:
+        line["extra"] = extra
     if world == 1 and not args.no_cpu:
-        gbs, dt = cpu_softstep_baseline(1 << 24, 3)
-        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-                                "sample": "3 passes over 2^24 of the 2^26 elements; PyTorch CPU eager op sequence of "
-                                          "the reference (tmq/tmq.py:417-493, :696-699)"}
+        gbs, dt, kind, cores = cpu_softstep_baseline(1 << 24, 3)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
+                                "sample": "3 passes over 2^24 of the 2^26 elements; the reference's PyTorch CPU eager "
+                                          "sequence (tmq/tmq.py:404-493, :696-699: autograd functions, mean, backward, clamp)"}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -481,69 +589,200 @@ def ternary_cpu_baselines():
 
 # ------------------------------------------------------------------------------------------------ other workloads
 
-def _finish(dist, line):
-    print(json.dumps(line), flush=True)
+def _conv_layers(net, images):
+    """(name, PackedConv or None, M, N, K, bytes) of every matrix-shaped layer of the packed ResNet-18 at 224 x 224."""
+    out, size = [], 224
+
+    def add(name, conv, size_in):
+        size_out = (size_in + 2 * conv.padding[0] - conv.dilation[0] * (conv.ky - 1) - 1) // conv.stride[0] + 1
+        m, n, k = images * size_out * size_out, conv.cout, conv.cin * conv.ky * conv.kx
+        in_bytes = images * size_in * size_in * conv.cin * (4 if conv.cin < 64 else 2)      # the stem reads fp32 images
+        out.append((name, conv, m, n, k, in_bytes + 2 * m * n + n * k / 4))
+        return size_out
+
+    size = add("conv1", net.conv1, size)
+    size = (size + 2 - 3) // 2 + 1                       # 3 x 3 / 2 max pooling
+    for i, (c1, c2, down) in enumerate(net.blocks):
+        if down is not None:
+            add(f"block{i}.down", down, size)
+        mid = add(f"block{i}.conv1", c1, size)
+        size = add(f"block{i}.conv2", c2, mid)
+    out.append(("fc", None, images, net.fc_n, net.fc_k, 2 * images * (net.fc_n + net.fc_k) + net.fc_n * net.fc_k / 4))
+    return out
 
 
 def _resnet_layer_roofline(net, images, peaks, measured_ms):
     """Per-layer floor of the packed ResNet-18 pass on one GPU: each convolution / linear layer can be no faster than
     max(2*M*N*K / bf16 peak, (activations in + out at 2 bytes + packed weights) / HBM peak); the sum over the layers against
     the measured time of the whole pass (which also holds the pooling layers and the launch gaps)."""
-    layers, size = [], 224
-
-    def add(conv, size_in):
-        size_out = (size_in + 2 * conv.padding[0] - conv.dilation[0] * (conv.ky - 1) - 1) // conv.stride[0] + 1
-        m, n, k = images * size_out * size_out, conv.cout, conv.cin * conv.ky * conv.kx
-        in_bytes = images * size_in * size_in * conv.cin * (4 if conv.cin < 64 else 2)      # the stem reads fp32 images
-        nbytes = in_bytes + 2 * m * n + n * k / 4
-        layers.append(max(2.0 * m * n * k / (peaks["bf16_tflops"] * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)))
-        return size_out
-
-    size = add(net.conv1, size)
-    size = (size + 2 - 3) // 2 + 1                       # 3 x 3 / 2 max pooling
-    for c1, c2, down in net.blocks:
-        if down is not None:
-            add(down, size)
-        mid = add(c1, size)
-        size = add(c2, mid)
-    layers.append(max(2.0 * images * net.fc_n * net.fc_k / (peaks["bf16_tflops"] * 1e12),
-                      (2 * images * (net.fc_n + net.fc_k) + net.fc_n * net.fc_k / 4) / (peaks["hbm_gbs"] * 1e9)))
-    ideal_ms = sum(layers) * 1e3
+    floors = [max(2.0 * m * n * k / (peaks["bf16_tflops"] * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9))
+              for _, _, m, n, k, nbytes in _conv_layers(net, images)]
+    ideal_ms = sum(floors) * 1e3
     return {"bound": "per layer max(tensor, hbm)", "achieved": measured_ms, "peak": ideal_ms, "unit": "ms per pass",
-            "frac": ideal_ms / measured_ms, "traffic": None, "layers": len(layers)}
+            "frac": ideal_ms / measured_ms, "traffic": None, "layers": len(floors)}
 
 
-def run_workload(args):
-    """Secondary workloads, same launch contract: --workload gemm | resnet_qat | resnet_infer (strong scaling)."""
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the tmq_b200 kernels have no CPU fallback")
-    dist, rank, local, world = dist_setup(args.gpus)
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
-    from tmq_b200 import dist as tdist
-    from tmq_b200 import ops, workloads
-    import tmq_b200 as tmq
-    peaks, peak_kind = measured_peaks()
+def _resnet_per_layer(net, x, peaks):
+    """Each layer of the packed pass timed alone on its actual input (CUDA events, 5 launches after 2 warm-ups; the
+    activations of one layer exceed L2 only in the early stages, so late layers read their input from L2, as they do in
+    the real pass).  Reports time, TFLOP/s, share of the measured bf16 peak and of the layer's own floor."""
+    captured = []
+    net(x, trace=lambda name, layer, x_in, res, y: captured.append((name, layer, x_in, res)))
+    shapes = {name: (m, n, k, nbytes) for name, _, m, n, k, nbytes in _conv_layers(net, x.shape[0])}
+    rows = {}
+    for name, layer, x_in, res in captured:
+        if layer is None:
+            continue
+        fn = (lambda: layer.from_images(x_in, defer_relu=True)) if name == "conv1" else (lambda: layer(x_in, residual=res))
+        ms = _time_cuda(fn, 5, warm=2)
+        m, n, k, nbytes = shapes[name]
+        tf = 2.0 * m * n * k / ms / 1e9
+        floor_ms = max(2.0 * m * n * k / (peaks["bf16_tflops"] * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)) * 1e3
+        rows[name] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 3),
+                      "frac_of_layer_floor": round(floor_ms / ms, 3), "M": m, "N": n, "K": k}
+    return rows
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
+
+class _Ctx:
+    """What every workload needs: the process group (or None), rank / world, device, peaks, and the timing helpers."""
+
+    def __init__(self, dist, rank, world, dev):
+        self.dist, self.rank, self.world, self.dev = dist, rank, world, dev
+        self.peaks, self.peak_kind = measured_peaks()
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(step, steps, warmup):
+    def timed(self, step, steps, warmup):
+        """ms per step: warm-ups, barrier, CUDA events around `steps` calls, barrier, max over ranks."""
         for i in range(max(warmup, 3)):
             step(i)
-        barrier()
+        self.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(steps):
             step(i)
         e1.record()
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-        if dist is not None:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        self.barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=self.dev)
+        if self.dist is not None:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item()) / steps
+
+
+def wl_gemm(ctx, steps, warmup, M=8192, K=8192, N=28672, chunks=None):
+    """Prefill linear, output columns sharded over the ranks, all-gather of the column blocks.  `chunks` row chunks
+    pipeline the gather of one chunk under the GEMM of the next (default: 4 when sharded)."""
+    from tmq_b200 import dist as tdist
+    from tmq_b200 import ops
+    dev, world = ctx.dev, ctx.world
+    P = _ternary_packed(ops, N, K, 0)                         # same seed on every rank: the same matrix
+    scale = torch.rand(N, generator=torch.Generator(device=dev).manual_seed(1), device=dev) * 0.09 + 0.01
+    X = torch.randn(M, K, generator=torch.Generator(device=dev).manual_seed(2), device=dev).to(torch.bfloat16)
+    lin = tdist.ColumnShardedLinear(P, N, scale, None, rank=ctx.rank, world_size=world)
+    del P
+    chunks = (4 if world > 1 else 1) if chunks is None else chunks
+    ms = ctx.timed(lambda i: lin(X, blocked=True, chunks=chunks), steps, warmup)
+    ops.check_gemm_status(dev)
+    ms_local = _time_cuda(lambda: lin.local(X), max(3, steps // 2))
+    ms_unchunked = ctx.timed(lambda i: lin(X, blocked=True, chunks=1), max(3, steps // 2), 3) if world > 1 else ms
+    value = 2 * M * N * K / ms / 1e9
+    gather_bytes = M * N * 2 * (world - 1) // max(world, 1)
+    peaks = ctx.peaks
+    return {"metric": "ternary_gemm_bf16_TOPS_equiv", "value": value, "unit": "TOPS-equiv", "n_gpus": world,
+            "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"ternary_linear_M{M}_K{K}_N{N}", "sharding": "output columns, 128-aligned; the GEMM "
+                       "epilogue writes this rank's block into its slot of the gather buffer, NCCL all-gather in place, "
+                       f"{chunks} row chunks pipelined (result left blocked: [chunks, world, M/chunks, N/world])",
+                       "local_gemm_ms": ms_local, "ms_per_step_unchunked": ms_unchunked,
+                       "all_gather_bytes_received_per_gpu": gather_bytes,
+                       "all_gather_floor_ms_at_770GBs": gather_bytes / 770e9 * 1e3,
+                       "l2": "activations + output (604 MB) exceed L2"},
+            "gpu_launches": steps * chunks,
+            "roofline": {"bound": "tensor", "achieved": 2 * M * (N / world) * K / ms_local / 1e9,
+                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": 2 * M * (N / world) * K / ms_local / 1e9 / peaks["bf16_tflops"], "traffic": None,
+                         "peak_kind": ctx.peak_kind, "kernel": "ternary_gemm_kernel<bf16,256>"}}
+
+
+def wl_resnet(ctx, kind, steps, warmup, batch=256, fused_optimizer=False, per_layer=False):
+    """ResNet-18 (101 classes) on synthetic 224 x 224 images, the batch split over the ranks (strong scaling):
+    kind "qat": one QAT step, data parallel; kind "infer": inference from packed weights, no collective."""
+    from tmq_b200 import dist as tdist
+    from tmq_b200 import ops, workloads
+    import tmq_b200 as tmq
+    dev, world, rank = ctx.dev, ctx.world, ctx.rank
+    b0, b1 = tdist.shard_range(batch, rank, world)
+    gen = torch.Generator(device=dev).manual_seed(10 + rank)
+    x = torch.randn(b1 - b0, 3, 224, 224, generator=gen, device=dev)
+    y = torch.randint(0, 101, (b1 - b0,), generator=gen, device=dev)
+    torch.manual_seed(0)
+    extra_cfg, roof = {}, None
+    if kind == "qat":
+        model, ctrl = workloads.build_resnet18(101)
+        model.to(dev).train()
+        for e in range(1, 45):
+            ctrl.step(e)
+        # gradients of the last layers are all-reduced (25 MB buckets) while backward still works on the first ones
+        bucket = tdist.FlatGradBucket(model.parameters(), bucket_bytes=25 << 20) if world > 1 else None
+        if fused_optimizer:      # Adam + clamp as one multi-tensor launch (plus one for the unclamped parameters)
+            opt = workloads.fused_optimizer(model, ctrl, lr=1e-3, bucket=bucket)
+        else:
+            opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+        ms = ctx.timed(lambda i: workloads.qat_step(model, ctrl, opt, x, y, bucket), steps, warmup)
+        metric = "resnet18_qat_images_per_s"
+        sharding = "data parallel, fp32 gradients in one flat buffer, all-reduced in 25 MB buckets from gradient hooks"
+        if fused_optimizer:
+            sharding += "; fused multi-tensor Adam + clamp"
+        if world > 1:
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(3):
+                ctx.dist.all_reduce(bucket.flat)
+            torch.cuda.synchronize()
+            extra_cfg["allreduce_alone_ms"] = (time.perf_counter() - t0) / 3 * 1e3
+            extra_cfg["gradient_bytes"] = bucket.flat.numel() * 4
+        # share of the step spent in this library's kernels (soft-step forward / backward of 21 layers, loss, clamp)
+        w_elems = sum(n.weight.numel() for n in ctrl._registry.values())
+        extra_cfg["quantized_weights"] = w_elems
+    else:
+        model, ctrl = workloads.build_resnet18(101, ctrl=tmq.QuantizationControl())
+        with torch.no_grad():
+            for node in ctrl._registry.values():
+                u = torch.rand(node.weight.shape)
+                node.weight.copy_(torch.where(u < 0.35, -1.0, torch.where(u < 0.65, 0.0, 1.0)))
+        model.to(dev).eval()
+        tmq.compressed_state_dict(model)
+        net = workloads.PackedResNet18(model)
+        ms = ctx.timed(lambda i: net(x), steps, warmup)
+        ops.check_gemm_status(dev)
+        metric, sharding = "resnet18_packed_inference_images_per_s", "batch sharded, no collective"
+        roof = _resnet_layer_roofline(net, b1 - b0, ctx.peaks, ms)
+        if per_layer:
+            roof["per_layer"] = _resnet_per_layer(net, x, ctx.peaks)
+    line = {"metric": metric, "value": batch / (ms * 1e-3), "unit": "images/s", "n_gpus": world, "steps": steps,
+            "warmup": max(warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32" if kind == "qat" else "bf16", "data": "synthetic",
+            "config": dict({"workload": f"resnet18_101cls_batch{batch}_224x224", "sharding": sharding,
+                            "macs_per_batch": 4.643e11 * batch / 256}, **extra_cfg)}
+    if roof is not None:
+        line["roofline"] = roof
+    return line
+
+
+def run_workload(args):
+    """Secondary workloads, same launch contract: --workload gemm | gemv | resnet_qat | resnet_infer | dwconv | ..."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the tmq_b200 kernels have no CPU fallback")
+    dist, rank, local, world = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    from tmq_b200 import ops
+    ctx = _Ctx(dist, rank, world, dev)
+    peaks, peak_kind, timed = ctx.peaks, ctx.peak_kind, ctx.timed
 
     if args.workload == "gemv":
         # decode-like config through the C ABI, distinct matrices so that L2 cannot hold them (profiling helper)
@@ -559,9 +798,10 @@ def run_workload(args):
 
         def sweep(i):
             for wt in wts:
-                for m0 in range(0, Mg, 8):
+                for m0 in range(0, Mg, GEMV_ROWS_PER_PASS):
                     rc = Lb.tmq_ternary_gemv_bf16(X.data_ptr() + m0 * K * 2, wt.data_ptr(), scale.data_ptr(), None,
-                                                  Y.data_ptr() + m0 * N * 2, min(8, Mg - m0), N, K, N, 0, status.data_ptr(), st)
+                                                  Y.data_ptr() + m0 * N * 2, min(GEMV_ROWS_PER_PASS, Mg - m0), N, K, N, 0,
+                                                  status.data_ptr(), st)
                     assert rc == 0
         ms = timed(sweep, args.steps, args.warmup) / NM
         nbytes = N * K // 4 + 2 * Mg * K + 2 * Mg * N + 4 * N
@@ -612,68 +852,11 @@ def run_workload(args):
                              "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"], "traffic": None, "peak_source": peak_kind,
                              "algorithmic_bytes_per_launch": nbytes}}
     elif args.workload == "gemm":
-        M, K, N = args.gemm_m, args.gemm_k, args.gemm_n
-        P = _ternary_packed(ops, N, K, 0)                         # same seed on every rank: the same matrix
-        scale = torch.rand(N, generator=torch.Generator(device=dev).manual_seed(1), device=dev) * 0.09 + 0.01
-        X = torch.randn(M, K, generator=torch.Generator(device=dev).manual_seed(2), device=dev).to(torch.bfloat16)
-        lin = tdist.ColumnShardedLinear(P, N, scale, None, rank=rank, world_size=world)
-        del P
-        ms = timed(lambda i: lin(X, blocked=True), args.steps, args.warmup)
-        ops.check_gemm_status(dev)
-        ms_local = _time_cuda(lambda: lin.local(X), max(3, args.steps // 2))
-        value = 2 * M * N * K / ms / 1e9
-        line = {"metric": "ternary_gemm_bf16_TOPS_equiv", "value": value, "unit": "TOPS-equiv", "n_gpus": world,
-                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": f"ternary_linear_M{M}_K{K}_N{N}", "sharding": "output columns, 128-aligned, "
-                           "one NCCL all-gather of the column blocks (left blocked: [world, M, N/world])", "local_gemm_ms": ms_local,
-                           "l2": "activations + output (604 MB) exceed L2"},
-                "gpu_launches": args.steps,
-                "roofline": {"bound": "tensor", "achieved": 2 * M * (N / world) * K / ms_local / 1e9,
-                             "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                             "frac": 2 * M * (N / world) * K / ms_local / 1e9 / peaks["bf16_tflops"], "traffic": None,
-                             "peak_kind": peak_kind, "kernel": "ternary_gemm_kernel<bf16,256>"}}
+        line = wl_gemm(ctx, args.steps, args.warmup, args.gemm_m, args.gemm_k, args.gemm_n,
+                       chunks=args.gemm_chunks if args.gemm_chunks > 0 else None)
     elif args.workload in ("resnet_qat", "resnet_infer"):
-        batch = args.batch
-        b0, b1 = tdist.shard_range(batch, rank, world)
-        gen = torch.Generator(device=dev).manual_seed(10 + rank)
-        x = torch.randn(b1 - b0, 3, 224, 224, generator=gen, device=dev)
-        y = torch.randint(0, 101, (b1 - b0,), generator=gen, device=dev)
-        torch.manual_seed(0)
-        if args.workload == "resnet_qat":
-            model, ctrl = workloads.build_resnet18(101)
-            model.to(dev).train()
-            for e in range(1, 45):
-                ctrl.step(e)
-            bucket = tdist.FlatGradBucket(model.parameters()) if world > 1 else None
-            if args.fused_optimizer:      # Adam + clamp as one multi-tensor launch (plus one for the unclamped parameters)
-                opt = workloads.fused_optimizer(model, ctrl, lr=1e-3, bucket=bucket)
-            else:
-                opt = torch.optim.Adam(model.parameters(), lr=1e-3)
-            ms = timed(lambda i: workloads.qat_step(model, ctrl, opt, x, y, bucket), args.steps, args.warmup)
-            metric, sharding = "resnet18_qat_images_per_s", "data parallel, one flat fp32 gradient all-reduce per step"
-            if args.fused_optimizer:
-                sharding += "; fused multi-tensor Adam + clamp"
-        else:
-            model, ctrl = workloads.build_resnet18(101, ctrl=tmq.QuantizationControl())
-            with torch.no_grad():
-                for node in ctrl._registry.values():
-                    u = torch.rand(node.weight.shape)
-                    node.weight.copy_(torch.where(u < 0.35, -1.0, torch.where(u < 0.65, 0.0, 1.0)))
-            model.to(dev).eval()
-            tmq.compressed_state_dict(model)
-            net = workloads.PackedResNet18(model)
-            ms = timed(lambda i: net(x), args.steps, args.warmup)
-            ops.check_gemm_status(dev)
-            metric, sharding = "resnet18_packed_inference_images_per_s", "batch sharded, no collective"
-            infer_roofline = _resnet_layer_roofline(net, b1 - b0, peaks, ms)
-        line = {"metric": metric, "value": batch / (ms * 1e-3), "unit": "images/s", "n_gpus": world, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "f32" if args.workload == "resnet_qat" else "bf16", "data": "synthetic",
-                "config": {"workload": f"resnet18_101cls_batch{batch}_224x224", "sharding": sharding,
-                           "macs_per_batch": 4.643e11 * batch / 256}}
-        if args.workload == "resnet_infer":
-            line["roofline"] = infer_roofline
+        line = wl_resnet(ctx, "qat" if args.workload == "resnet_qat" else "infer", args.steps, args.warmup, args.batch,
+                         args.fused_optimizer, per_layer=args.per_layer)
     else:
         raise SystemExit(f"unknown workload {args.workload}")
     if rank == 0:
@@ -698,6 +881,8 @@ def main():
     ap.add_argument("--gemm-n", type=int, default=28672)
     ap.add_argument("--batch", type=int, default=256, help="images per step of the ResNet workloads")
     ap.add_argument("--fused-optimizer", action="store_true", help="resnet_qat: multi-tensor Adam with the clamp fused in")
+    ap.add_argument("--gemm-chunks", type=int, default=0, help="row chunks of the column-sharded GEMM (0: default)")
+    ap.add_argument("--per-layer", action="store_true", help="resnet_infer: time every layer alone as well")
     ap.add_argument("--gemv-rows", type=int, default=1)
     ap.add_argument("--gemv-matrices", type=int, default=32)
     args = ap.parse_args()

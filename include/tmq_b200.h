@@ -107,7 +107,6 @@ int tmq_mt_qloss(const void *d_plan, int ntensors, int nchunks, double sharpness
  * else to the per-tensor pointers stored in the plan. */
 int tmq_mt_qloss_bwd(const void *d_plan, int ntensors, int nchunks, double sharpness, double strength,
                      const float *d_upstream, float *out_base, void *stream);
-/* w_l = clamp(w_l, lo, hi) in place */
 /* Fused optimizer of the QAT step: torch.optim.Adam's update (single-tensor sequence, fp32, one rounding per operation)
  * of every tensor of a plan in one launch, followed by clamp(w, lo, hi) when `clamp` is set - the optimizer step and
  * QuantizationControl.clamp (tmq/tmq.py:263-272) read and write the weights once between them.  In THIS plan a tensor's
@@ -115,6 +114,7 @@ int tmq_mt_qloss_bwd(const void *d_plan, int ntensors, int nchunks, double sharp
  * exp_avg_sq); `step` is the 1-based step count of the bias corrections. */
 int tmq_mt_adam_clamp(const void *d_plan, int ntensors, int nchunks, float *m_base, float *v_base, double lr, double beta1,
                       double beta2, double eps, long long step, int clamp, float lo, float hi, void *stream);
+/* w_l = clamp(w_l, lo, hi) in place */
 int tmq_mt_clamp(const void *d_plan, int ntensors, int nchunks, float lo, float hi, void *stream);
 
 /* Device self-check of the constant-divisor fast path used inside the kernels above: counts, over every finite
@@ -128,6 +128,12 @@ int tmq_selftest_const_div(double digamma, unsigned long long *mismatches, void 
  * uint64, zeroed by the caller. */
 int tmq_selftest_div(unsigned per_b, unsigned long long b_begin, unsigned long long b_count,
                      unsigned long long *mismatches, void *stream);
+
+/* Self-check of the bounded device-side waits every tensor-core kernel uses: one thread waits, with a budget of
+ * budget_cycles SM clocks (<= 4e9), on a barrier that nothing completes.  The kernel returns normally; afterwards
+ * *status (device int, zero before the call) holds TMQ_ERR_TIMEOUT and *waited_cycles (device int64, may be NULL)
+ * the clocks spent waiting.  Nothing faults or hangs: this is how the time-out path is tested. */
+int tmq_selftest_wait_timeout(long long budget_cycles, int *status, long long *waited_cycles, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Hot path 2a: bit-exact 2-bit packing.  W is [N][K] row-major (Linear [out][in]; a conv kernel
@@ -152,19 +158,26 @@ int tmq_unpack2b_f32(const uint32_t *P, float *W, int64_t N, int64_t K, void *st
  * bias are per output channel and fused (pass NULL for none).
  *
  * Weights are consumed in a PREPACKED layout derived once from the reference layout P[K][ceil(N/16)]:
- * Wt[N][Kp/16] words, Kp = K rounded up to 64, 16 consecutive k of one output channel per word, bit order per
+ * Wt[N][row stride] words, Kp = K rounded up to 64, 16 consecutive k of one output channel per word, bit order per
  * activation type (fmt 0: bf16 activations, fmt 1: int8 activations).  tmq_prepack_words gives the word count.
+ *
+ * Status word: `status` is a device int the caller zeroes once.  A kernel whose bounded device-side wait runs out
+ * stores TMQ_ERR_TIMEOUT there and returns; the word is STICKY: while it is non-zero every later GEMM / GEMV /
+ * convolution launch that is given the same word returns at once without touching its output, and the C call still
+ * returns TMQ_OK (it only enqueues).  Callers must read the word at a point where they synchronise anyway (at least
+ * before they trust a batch of results), treat non-zero as a failed batch, and re-zero it before they continue.
  * ------------------------------------------------------------------------------------------------ */
 size_t tmq_prepack_row_words(int64_t K, int fmt); /* row stride in 32-bit words (valid words + bank padding) */
 size_t tmq_prepack_words(int64_t N, int64_t K, int fmt); /* N * row stride */
-/* fmt 2 / 3: the same words as fmt 0 / 1 stored tile-contiguously, Wt[tile][k-block][128 rows][words], rows padded
- * to whole 128-channel tiles; this is what the skinny tensor-core kernel (tmq_ternary_gemv_tc_*) streams. */
-size_t tmq_prepack_tiled_words(int64_t N, int64_t K, int fmt);
+/* Enqueues the conversion followed by an empty kernel, so that Wt is complete and visible before ANY later launch on
+ * the stream starts - including the skinny kernels below, which read Wt ahead of their wait on the stream's previous
+ * kernel (see tmq_ternary_gemv_bf16). */
 int tmq_prepack(const uint32_t *P, uint32_t *Wt, int64_t N, int64_t K, int fmt, void *stream);
 
-/* X: bf16 [M][K] row-major, K % 8 == 0, 16-byte aligned.  Y: bf16 (out_f32 = 0) or fp32 (out_f32 = 1) [M][ldy].
- * fp32 accumulation.  *status (device int, zeroed by the caller) receives TMQ_ERR_TIMEOUT if a bounded device-side
- * wait ran out; the kernel then skips its work instead of hanging. */
+/* X: bf16 [M][K] row-major, K % 8 == 0, 16-byte aligned.  Y: bf16 (out_f32 = 0) or fp32 (out_f32 = 1) [M][ldy],
+ * element-aligned; ldy >= N lets Y be a column block of a wider matrix (Y = base + n0).  bf16 rows are written as
+ * 16-byte vectors when Y is 16-byte aligned and ldy % 8 == 0, element by element otherwise.  fp32 accumulation.
+ * *status: see "Status word" above. */
 int tmq_ternary_gemm_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int64_t M,
                           int64_t N, int64_t K, int64_t ldy, int out_f32, int *status, void *stream);
 /* X: int8 [M][K], K % 16 == 0.  Y: int32 [M][ldy], exact. */
@@ -178,33 +191,44 @@ int tmq_ternary_gemm_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t
  * launch), so consecutive launches overlap their weight traffic with the predecessor's arithmetic; `status` (device
  * int, zero before the first call, may be NULL: then the non-resident streaming kernel is used) receives
  * TMQ_ERR_TIMEOUT if those copies never complete.
+ * CONTRACT that follows from the early fetch: Wt, scale and bias must be complete in memory before the kernel that
+ * PRECEDES this call in the stream starts, i.e. they must not be written by the immediately preceding launch
+ * (tmq_prepack ends with an empty kernel for exactly this reason; weights written by a caller's own kernel need one
+ * launch or an event between them and this call).  X and Y carry no such restriction.
  * replaces: ternary_mvm_cuda, tmq/tmq_cuda.cu:563-603 (kernel :242-286). */
 int tmq_ternary_gemv_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int64_t M,
                           int64_t N, int64_t K, int64_t ldy, int out_f32, int *status, void *stream);
 int tmq_ternary_gemv_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
                         int *status, void *stream);
 
-/* Skinny form on the tensor cores for 1..32 activation rows: split-K over ~4 CTAs per SM, all of a CTA's packed
- * weight bytes in flight at once (TMA ring), decode in shared memory, tcgen05.mma with N = 16 / 32, deterministic
- * in-kernel reduction of the split partials.  `workspace`: tmq_gemv_workspace_bytes(M, N, K) bytes of device memory,
- * 256-byte aligned, zero-filled once before first use (the kernel re-arms it); calls sharing it must be ordered.
- * `status` as for tmq_ternary_gemm_bf16.  Wt is the TILED prepack (fmt 2 for bf16, fmt 3 for int8 activations).
- * replaces: ternary_mvm_cuda, tmq/tmq_cuda.cu:563-603 (kernel :242-286). */
-size_t tmq_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K);
-int tmq_ternary_gemv_tc_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int64_t M,
-                             int64_t N, int64_t K, int64_t ldy, int out_f32, void *workspace, size_t workspace_bytes,
-                             int *status, void *stream);
-int tmq_ternary_gemv_tc_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
-                           void *workspace, size_t workspace_bytes, int *status, void *stream);
-
 /* Ternary Conv2d as an implicit GEMM (no im2col buffer): X bf16 NHWC [B][H][W][C], C % 64 == 0; Wt = fmt-0 prepack of
  * the packed weight with its K rows reordered to (ky, kx, c); Y bf16 NHWC [B][OH][OW][N] with the output geometry of
  * F.conv2d; scale / bias per output channel (folded BatchNorm, NULL for none), optional residual (bf16, shape of Y,
- * added before the activation), optional ReLU.
+ * added before the activation), optional ReLU.  X 16-byte aligned; Y and residual element-aligned (16-byte aligned
+ * pointers with N % 8 == 0 take the vector stores).
  * replaces: Conv2d.compact_forward, tmq/tmq.py:822-871 (F.unfold + ternary_mmm_cuda + F.fold). */
 int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, const void *residual,
                             void *Y, int B, int H, int W, int C, int N, int ky, int kx, int sy, int sx, int py, int px,
                             int dy, int dx, int relu, int *status, void *stream);
+/* The same convolution with fp32 NHWC output (no output rounding; residual stays bf16), and with int8 activations:
+ * X int8 NHWC, Wt = fmt-1 prepack of the (ky, kx, c)-ordered packed weight, Y int32 NHWC, exact.  The fp32-output form
+ * is also how fp32 activations are convolved exactly: split them into three bf16 terms along the channels
+ * (tmq_nchw_f32_to_nhwc_bf16 / tmq_split_f32_bf16 with terms = 3) and stack three copies of the weights per tap.
+ * replaces: Conv2d.compact_forward, tmq/tmq.py:822-871. */
+int tmq_ternary_conv2d_bf16_f32out(const void *X, const uint32_t *Wt, const float *scale, const float *bias,
+                                   const void *residual, float *Y, int B, int H, int W, int C, int N, int ky, int kx, int sy,
+                                   int sx, int py, int px, int dy, int dx, int relu, int *status, void *stream);
+int tmq_ternary_conv2d_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int B, int H, int W, int C, int N, int ky, int kx,
+                          int sy, int sx, int py, int px, int dy, int dx, int *status, void *stream);
+
+/* Activation layout helpers of the packed inference path (replace the eager tensor glue between compact layers,
+ * tmq/tmq.py:857-863): fp32 rows [M][K] -> bf16 [M][terms*Kp] (terms = 1: rounded; terms = 3: the exact split
+ * x = hi + mid + lo, term t at column t*Kp + k; columns K..Kp-1 zero); fp32 NCHW -> bf16 NHWC [B][H][W][terms*C];
+ * global average pooling of bf16 NHWC [B][P][C] -> bf16 [B][C] (fp32 sum, C even). */
+int tmq_split_f32_bf16(const float *X, void *out, int64_t M, int64_t K, int64_t Kp, int terms, void *stream);
+int tmq_nchw_f32_to_nhwc_bf16(const float *X, void *Y, int B, int C, int H, int W, int terms, void *stream);
+int tmq_avgpool_nhwc_bf16(const void *X, void *Y, int B, int P, int C, void *stream);
+
 /* Patch matrix for layers the implicit path cannot take (channel count not a multiple of 64, e.g. a 3-channel stem):
  * X fp32 NCHW -> A bf16 [B*OH*OW][Kp], K = ky*kx*C in (ky, kx, c) order zero-padded to Kp (% 8 == 0); feed A to
  * tmq_ternary_gemm_bf16.  replaces: F.unfold in Conv2d.compact_forward, tmq/tmq.py:857-858. */

@@ -17,7 +17,8 @@ import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-REFERENCE = os.environ.get("TMQ_REFERENCE_DIR", "/root/reference")
+# the reference checkout: TMQ_REFERENCE_DIR, else a checkout placed beside this repository
+REFERENCE = os.environ.get("TMQ_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _torch_flags():

@@ -1,9 +1,9 @@
 """Generates the committed golden fixtures by RUNNING THE REFERENCE on CPU.
 
-Needs the reference checkout (default /root/reference, override with TMQ_REFERENCE_DIR) and the compiled
-reference extension oracle/_ref/tmq_native.so (python oracle/build_ref.py).  Run from the repository root:
+Needs the reference checkout (its path in the environment variable TMQ_REFERENCE_DIR) and the compiled reference
+extension oracle/_ref/tmq_native.so (python oracle/build_ref.py).  Run from the repository root:
 
-    python tests/golden/make_golden.py
+    TMQ_REFERENCE_DIR=<path to the mtnwrw/tmq checkout> python tests/golden/make_golden.py
 
 Outputs (all small, committed):
   softstep.npz   reference tmq.SoftStep / SoftStepDerivative forward+backward (PyTorch CPU eager) on seeded inputs
@@ -11,6 +11,9 @@ Outputs (all small, committed):
   pack.npz       compactify_ternary / expand_ternary known answers (2-D, 4-D, ragged, int inputs)
   codec.npz      compress_ternary / decompress_ternary streams
   mlp_step.npz   the reference MLP QAT step (logits, loss, grads, post-step weights)
+  resnet_qat_step.npz   the reference ResNet-18 (101 classes) QAT step on CPU, batch 8 of 64 x 64 images: logits, loss
+                 terms, gradients of three layers (parameters are filled from one seeded generator in state_dict order,
+                 so the fixture does not have to carry the 45 MB of initial weights)
 """
 import contextlib
 import io
@@ -22,7 +25,8 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-REFERENCE = os.environ.get("TMQ_REFERENCE_DIR", "/root/reference")
+REFERENCE = os.environ.get("TMQ_REFERENCE_DIR")
+assert REFERENCE and os.path.isdir(REFERENCE), "set TMQ_REFERENCE_DIR to the reference checkout"
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 from oracle import build_ref  # noqa: E402
@@ -191,12 +195,74 @@ def make_mlp_step():
     np.savez_compressed(os.path.join(OUT, "mlp_step.npz"), **out)
 
 
+def seeded_fill(model, seed):
+    """Deterministic parameters and buffers, independent of either implementation's own initialisation: every
+    state_dict entry, in key order, from one generator.  Quantized layers' weights U(-1.2, 1.2) (some outside the clamp
+    range), BatchNorm scale U(0.5, 1.5), everything else small.  tests/test_conv_api_gpu.py repeats this on the GPU side."""
+    g = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for key, t in model.state_dict().items():
+            if not t.is_floating_point() or key.endswith("post_scale"):
+                continue
+            if key.endswith("running_var"):
+                t.copy_(torch.rand(t.shape, generator=g) + 0.5)
+            elif key.endswith("running_mean"):
+                t.copy_(torch.randn(t.shape, generator=g) * 0.1)
+            elif t.dim() >= 2:
+                t.copy_(torch.rand(t.shape, generator=g) * 2.4 - 1.2)
+            elif "bn" in key.split(".")[-2] and key.endswith("weight"):
+                t.copy_(torch.rand(t.shape, generator=g) + 0.5)
+            elif key.endswith("weight") and t.dim() == 1:
+                t.copy_(torch.rand(t.shape, generator=g) + 0.5)
+            else:
+                t.copy_(torch.randn(t.shape, generator=g) * 0.1)
+
+
+RESNET_GRAD_LAYERS = ("conv1.weight", "layer1.0.conv1.weight", "layer2.0.downsample.0.weight", "fc.weight")
+
+
+def make_resnet_qat_step():
+    """BASELINE config 4a at test size: torchvision ResNet-18 (101 classes), every conv / fc layer quantized, the
+    sample's fc set-up (samples/resnet_train.py:344-358), one forward + CE + quantization loss + backward on CPU."""
+    import torchvision
+    torch.manual_seed(0)
+    model = torchvision.models.resnet18(num_classes=101)
+    knots = ref.QuantizationScheduleBuilder.default_schedule(50)
+    ctrl = ref.QuantizationControl(epoch_knots=knots, qpenalty_range=(0.0, 1e-3))
+    with contextlib.redirect_stdout(io.StringIO()):
+        ref.quantize_model(model, ctrl)
+    model.fc.disable_bias()
+    model.fc.implicit_bn()
+    ref.Linear.forward = ref.Linear.forward_wrap
+    seeded_fill(model, 4242)
+    for e in range(1, 45):
+        ctrl.step(e)
+    g = torch.Generator().manual_seed(99)
+    x = torch.randn(8, 3, 64, 64, generator=g)
+    y = torch.randint(0, 101, (8,), generator=g)
+    model.train()
+    logits = model(x)
+    ce = torch.nn.functional.cross_entropy(logits, y)
+    ql = ctrl.quantization_loss()
+    (ce + ql).backward()
+    params = dict(model.named_parameters())
+    out = {"x": x.numpy(), "y": y.numpy(), "digamma": np.float64(ctrl.digamma), "qpenalty": np.float64(ctrl.qpenalty),
+           "logits": logits.detach().numpy(), "ce": ce.detach().numpy(), "qloss": ql.detach().numpy(),
+           "n_registered": np.int64(len(ctrl._registry))}
+    for name in RESNET_GRAD_LAYERS:
+        out["grad/" + name] = params[name].grad.detach().numpy()
+    ctrl.clamp()
+    out["clamped/layer1.0.conv1.weight"] = params["layer1.0.conv1.weight"].detach().numpy()
+    np.savez_compressed(os.path.join(OUT, "resnet_qat_step.npz"), **out)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(1)
     make_softstep()
     make_schedule()
     make_pack_and_codec()
     make_mlp_step()
+    make_resnet_qat_step()
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(OUT, f)))

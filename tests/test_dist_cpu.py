@@ -66,6 +66,18 @@ def _worker(rank, world, port, out_dir):
             for w_, p in zip(want, model.parameters()):
                 w_ += p.grad / world
         ok_grad = all(torch.allclose(g, w_, rtol=1e-6, atol=1e-7) for g, w_ in zip(got, want))
+        # the overlapped form: small buckets, all-reduces launched from gradient hooks during backward; two steps in a
+        # row, so the hook counters must re-arm
+        torch.manual_seed(0)
+        model_b = nn.Sequential(nn.Linear(12, 7), nn.ReLU(), nn.Linear(7, 3))
+        bucket_b = tdist.FlatGradBucket(model_b.parameters(), bucket_bytes=64)
+        ok_grad = ok_grad and len(bucket_b.buckets) >= 2 and bucket_b.buckets[0][1] == bucket_b.flat.numel()
+        for _ in range(2):
+            bucket_b.zero()
+            nn.functional.mse_loss(model_b(x_all[b:e]), y_all[b:e]).backward()
+            bucket_b.allreduce_mean()
+            ok_grad = ok_grad and all(torch.allclose(p.grad, w_, rtol=1e-6, atol=1e-7)
+                                      for p, w_ in zip(model_b.parameters(), want))
         # ---- column-sharded ternary linear (uneven shards: 300 channels over 2 ranks, 128-aligned)
         rng = np.random.default_rng(1)
         N, K, M = 300, 40, 5
@@ -83,10 +95,16 @@ def _worker(rank, world, port, out_dir):
         lin2 = tdist.ColumnShardedLinear(torch.from_numpy(T.pack(W2)), N2, matmul=_cpu_matmul)
         full2 = xs @ torch.from_numpy(W2).T
         ok_cols = ok_cols and torch.allclose(lin2(xs), full2, rtol=1e-6, atol=1e-6)
-        ok_cols = ok_cols and torch.allclose(lin2(xs, chunks=2), full2, rtol=1e-6, atol=1e-6)      # overlapped variant
+        xs6 = torch.randn(6, K, generator=gen)
+        full6 = xs6 @ torch.from_numpy(W2).T
+        ok_cols = ok_cols and torch.allclose(lin2(xs6, chunks=2), full6, rtol=1e-6, atol=1e-6)      # overlapped variant
+        ok_cols = ok_cols and torch.allclose(lin2(xs, chunks=2), full2, rtol=1e-6, atol=1e-6)       # 5 rows: one chunk
         blocks = lin2(xs, blocked=True)
         ok_cols = ok_cols and blocks.shape == (world, M, N2 // world) and torch.allclose(
             blocks.permute(1, 0, 2).reshape(M, N2), full2, rtol=1e-6, atol=1e-6)
+        blocks2 = lin2(xs6, blocked=True, chunks=3)
+        ok_cols = ok_cols and blocks2.shape == (3, world, 2, N2 // world) and torch.allclose(
+            blocks2.permute(0, 2, 1, 3).reshape(6, N2), full6, rtol=1e-6, atol=1e-6)
         # ---- scalar all-reduce
         s = tdist.allreduce_scalar(torch.tensor(float(rank + 1), dtype=torch.float64))
         ok_scalar = s.item() == sum(range(1, world + 1))

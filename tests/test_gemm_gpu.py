@@ -26,21 +26,20 @@ SHAPES = [(1, 128, 64), (8, 128, 64), (32, 256, 128), (33, 200, 192), (64, 128, 
           (129, 128, 64), (256, 256, 1024), (300, 520, 576), (512, 1000, 2304)]
 
 
-PATHS = ["tiles", "gemv", "tc"]
+PATHS = ["tiles", "gemv"]
 
 
 @pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_gemm_i8_exact(ops, M, N, K, path):
-    if (path == "gemv" and M > 40) or (path == "tc" and M > 32):
-        pytest.skip("the streaming kernels are meant for skinny problems")
+    if path == "gemv" and M > 40:
+        pytest.skip("the skinny kernels are meant for skinny problems")
     K = (K + 15) // 16 * 16
     W, P = make_weights(N, K, M * 7 + N)
     rng = np.random.default_rng(K)
     X = rng.integers(-127, 128, (M, K)).astype(np.int8)
     wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_I8)
-    wtt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_I8_TILED)
-    Y = ops.ternary_gemm_i8(torch.from_numpy(X).cuda(), wt, N, path=path, wt_tiled=wtt)
+    Y = ops.ternary_gemm_i8(torch.from_numpy(X).cuda(), wt, N, path=path)
     ops.check_gemm_status()
     assert np.array_equal(Y.cpu().numpy(), T.gemm_i8_fast(X, P, N))
 
@@ -48,8 +47,8 @@ def test_gemm_i8_exact(ops, M, N, K, path):
 @pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_gemm_bf16_tolerance(ops, M, N, K, path):
-    if (path == "gemv" and M > 40) or (path == "tc" and M > 32):
-        pytest.skip("the streaming kernels are meant for skinny problems")
+    if path == "gemv" and M > 40:
+        pytest.skip("the skinny kernels are meant for skinny problems")
     K = (K + 7) // 8 * 8
     W, P = make_weights(N, K, M * 11 + N)
     gen = torch.Generator().manual_seed(K)
@@ -57,17 +56,16 @@ def test_gemm_bf16_tolerance(ops, M, N, K, path):
     scale = (torch.rand(N, generator=gen) * 0.09 + 0.01)
     bias = torch.randn(N, generator=gen)
     wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16)
-    wtt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16_TILED)
     ref_acc = T.gemm_f64_fast(X.float().numpy(), P, N)                       # exact sum of exact products
     ref = ref_acc * scale.double().numpy()[None, :] + bias.double().numpy()[None, :]
-    y32 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.float32, path=path, wt_tiled=wtt)
+    y32 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.float32, path=path)
     ops.check_gemm_status()
     got = y32.cpu().double().numpy()
     rms = np.sqrt((ref ** 2).mean(axis=1, keepdims=True))
     assert np.all(np.abs(got - ref) <= 1e-3 * np.maximum(np.abs(ref), rms)), np.abs(got - ref).max()
     # in practice fp32 accumulation of exact products is far tighter than the 1e-3 bar
     assert np.all(np.abs(got - ref) <= 1e-5 * np.maximum(np.abs(ref), rms))
-    y16 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.bfloat16, path=path, wt_tiled=wtt)
+    y16 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.bfloat16, path=path)
     ops.check_gemm_status()
     want16 = torch.from_numpy(ref).to(torch.bfloat16).float().numpy()
     ulp = np.abs(want16) * 2.0 ** -7                     # one bf16 ulp, plus the fp32 accumulation slack near zero
@@ -123,16 +121,16 @@ def test_gemv_baseline_shape(ops, M):
     X = torch.randn(M, K, generator=gen).to(torch.bfloat16)
     scale = torch.rand(N, generator=gen) * 0.09 + 0.01
     ref = T.gemm_f64_fast(X.float().numpy(), P, N) * scale.double().numpy()[None, :]
-    wt, wtt = ops.prepack(Pd, N, ops.FMT_BF16), ops.prepack(Pd, N, ops.FMT_BF16_TILED)
-    y = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), out_dtype=torch.float32, wt_tiled=wtt)
+    wt = ops.prepack(Pd, N, ops.FMT_BF16)
+    y = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), out_dtype=torch.float32)
     rms = np.sqrt((ref ** 2).mean(axis=1, keepdims=True))
     assert np.all(np.abs(y.cpu().double().numpy() - ref) <= 1e-3 * np.maximum(np.abs(ref), rms))
     assert np.all(np.abs(y.cpu().double().numpy() - ref) <= 1e-5 * np.maximum(np.abs(ref), rms))
     X8 = torch.randint(-127, 128, (M, K), generator=gen, dtype=torch.int8)
-    y8 = ops.ternary_gemm_i8(X8.cuda(), ops.prepack(Pd, N, ops.FMT_I8), N, wt_tiled=ops.prepack(Pd, N, ops.FMT_I8_TILED))
+    y8 = ops.ternary_gemm_i8(X8.cuda(), ops.prepack(Pd, N, ops.FMT_I8), N)
     assert np.array_equal(y8.cpu().numpy(), T.gemm_i8_fast(X8.numpy(), P, N))
     # deterministic: same bits on a second run
-    y2 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), out_dtype=torch.float32, wt_tiled=wtt)
+    y2 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), out_dtype=torch.float32)
     for pth in ("gemv", "tiles"):
         yo = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), out_dtype=torch.float32, path=pth)
         assert np.all(np.abs(yo.cpu().double().numpy() - ref) <= 1e-5 * np.maximum(np.abs(ref), rms)), pth
@@ -208,3 +206,22 @@ def test_full_size_prefill_shape_sampled(ops):
     E[torch.arange(256, device="cuda"), ks] = 1
     out = ops.ternary_gemm_i8(E, wt8, N, path="tiles")
     assert torch.equal(out, W[:, ks].T.to(torch.int32))
+
+
+@pytest.mark.parametrize("n0,width", [(0, 256), (3, 256), (8, 200), (5, 203)])
+@pytest.mark.parametrize("M", [8, 100])
+def test_gemm_bf16_writes_a_column_block_of_a_wider_output(ops, M, n0, width):
+    """Y = base + n0 with ldy = the full width: the 16-byte vector stores are only legal when that address is 16-byte
+    aligned and ldy % 8 == 0; every other combination must take the scalar stores and still give the same bits as the
+    plain call, without touching the columns outside the block."""
+    N, K = 72, 192
+    W, P = make_weights(N, K, 31)
+    gen = torch.Generator().manual_seed(n0 * 7 + width)
+    X = torch.randn(M, K, generator=gen).to(torch.bfloat16).cuda()
+    wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16)
+    plain = ops.ternary_gemm(X, wt, N)
+    wide = torch.full((M, width), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.ternary_gemm(X, wt, N, out=wide[:, n0:n0 + N])
+    ops.check_gemm_status()
+    assert torch.equal(wide[:, n0:n0 + N], plain)
+    assert bool((wide[:, :n0] == 7.0).all()) and bool((wide[:, n0 + N:] == 7.0).all())

@@ -2,8 +2,9 @@
 
 It exists for hosts that cannot allocate device memory and therefore cannot supply the scratch buffer that
 tmq_qloss_sum wants; its scratch is a fixed array inside the library.  The check: on two calls in a row (different
-data, so leftovers of the first call would show in the second) it must agree with tmq_qloss_sum to the tolerance the
-loss tests use (rel 2.5e-7: partial sums of four terms are fp32, everything above that fp64).
+data, so leftovers of the first call would show in the second) it must agree with tmq_qloss_sum AND with the CPU
+oracle's fp64 sum of the bit-exact integrand (oracle.softstep.qloss_sum_f64) to the tolerance the loss tests use
+(rel 2.5e-7: partial sums of four terms are fp32, everything above that fp64).
 
 This file sorts last on purpose: a run that stops at the first failure has then already covered everything else.
 It passes on its own in a fresh process as well as after the other tests.
@@ -33,6 +34,7 @@ def test_rejects_oversized_and_bad_arguments_without_touching_the_gpu():
 
 @pytest.mark.gpu
 def test_matches_the_scratch_taking_entry_point_twice_in_a_row():
+    from oracle.softstep import qloss_sum_f64
     L = _lib()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -56,6 +58,8 @@ def test_matches_the_scratch_taking_entry_point_twice_in_a_row():
         r, g = ref.item(), got.item()
         assert r > 0
         assert abs(g - r) <= 2.5e-7 * abs(r), (n, g, r)
+        want = qloss_sum_f64(w.cpu().numpy(), 5.0, 5e-4)
+        assert abs(g - want) <= 2.5e-7 * abs(want), (n, g, want)
     # empty input: the sum is zero and the call still succeeds
     got = torch.full((), 7.0, dtype=torch.float64, device=dev)
     assert L.tmq_qloss_sum_noalloc(None, 0, 5.0, 5e-4, ctypes.c_void_p(got.data_ptr()), stream) == 0

@@ -41,6 +41,7 @@ _SIGNATURES = {
     "tmq_mt_adam_clamp": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_double, c_double, c_double, c_double,
                                   ctypes.c_longlong, c_int, c_float, c_float, c_void_p]),
     "tmq_mt_clamp": (c_int, [c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
+    "tmq_selftest_wait_timeout": (c_int, [ctypes.c_longlong, c_void_p, c_void_p, c_void_p]),
     "tmq_selftest_div": (c_int, [ctypes.c_uint, ctypes.c_uint64, ctypes.c_uint64, c_void_p, c_void_p]),
     "tmq_selftest_const_div": (c_int, [c_double, c_void_p, c_void_p]),
     "tmq_pack2b_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
@@ -58,7 +59,6 @@ _SIGNATURES = {
     "tmq_rc_decode": (c_int, [c_void_p, c_size_t, c_void_p, c_int64, c_int64]),
     "tmq_prepack_row_words": (c_size_t, [c_int64, c_int]),
     "tmq_prepack_words": (c_size_t, [c_int64, c_int64, c_int]),
-    "tmq_prepack_tiled_words": (c_size_t, [c_int64, c_int64, c_int]),
     "tmq_prepack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "tmq_ternary_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                       c_int64, c_int, c_void_p, c_void_p]),
@@ -66,12 +66,12 @@ _SIGNATURES = {
                                       c_int64, c_int, c_void_p, c_void_p]),
     "tmq_ternary_gemv_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p]),
-    "tmq_gemv_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
-    "tmq_ternary_gemv_tc_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-                                         c_int64, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
-    "tmq_ternary_gemv_tc_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
-                                       c_size_t, c_void_p, c_void_p]),
     "tmq_ternary_conv2d_bf16": (c_int, [c_void_p] * 6 + [c_int] * 14 + [c_void_p, c_void_p]),
+    "tmq_ternary_conv2d_bf16_f32out": (c_int, [c_void_p] * 6 + [c_int] * 14 + [c_void_p, c_void_p]),
+    "tmq_ternary_conv2d_i8": (c_int, [c_void_p] * 3 + [c_int] * 13 + [c_void_p, c_void_p]),
+    "tmq_split_f32_bf16": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "tmq_nchw_f32_to_nhwc_bf16": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "tmq_avgpool_nhwc_bf16": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "tmq_conv_patches_bf16": (c_int, [c_void_p, c_void_p] + [c_int] * 13 + [c_void_p]),
     "tmq_ternary_gemm_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p]),

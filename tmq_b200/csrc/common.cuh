@@ -3,6 +3,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "tmq_b200.h"
 
 namespace tmq {
@@ -40,6 +44,24 @@ inline long long prepack_row_words(long long K, int kind) {
     const long long bytes = prepack_valid_words(K) * 4;
     const long long want = kind ? 64 : 32;
     return (bytes + ((want - bytes % 128) + 128) % 128) / 4;
+}
+
+// Opt-in to more than 48 KB of dynamic shared memory.  The attribute belongs to the (kernel, device) pair, so it is set
+// once per kernel on every device the library is used on; the calling thread's current device is the one that launches.
+template <typename K>
+inline int ensure_dynamic_smem(K kernel, int bytes, bool max_carveout = false) {
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, bool> done;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return cuda_status(cudaGetLastError());
+    const std::pair<const void *, int> key(reinterpret_cast<const void *>(kernel), dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.count(key)) return TMQ_OK;
+    int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (rc == TMQ_OK && max_carveout)
+        rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    if (rc == TMQ_OK) done[key] = true;
+    return rc;
 }
 
 inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }

@@ -19,7 +19,10 @@ __device__ __forceinline__ void epilogue_chunk_bf16(const uint32_t (&v)[16], flo
     __syncwarp();
     const int cg = (lane & 3) * 8;  // channel offset of this lane's 8-channel vector
     const long long n = n_base + cg;
-    const bool vec_ok = ((ldy & 7) == 0) && (n + 8 <= N);
+    // 16-byte vectors only when every row's vector is 16-byte aligned: row stride and both base pointers (a caller may
+    // hand in a column block of a wider output, Y = base + n0 with any n0); anything else takes the scalar stores
+    const bool vec_ok = ((ldy & 7) == 0) && (n + 8 <= N) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(residual) & 15) == 0);
 #pragma unroll
     for (int it = 0; it < 2; it++) {
         const int p = it * 8 + (lane >> 2);

@@ -34,17 +34,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait: gives up after ~2 s of SM clock, or as soon as another CTA has flagged a failure, records
-// TMQ_ERR_TIMEOUT in *status and returns false.  Callers then skip their work and fall through to the teardown.
+// Bounded wait: gives up after `budget` SM clock cycles (default ~2 s), or as soon as another CTA has flagged a failure,
+// records TMQ_ERR_TIMEOUT in *status and returns false.  Callers then skip their work and fall through to the teardown.
 constexpr long long kWaitBudgetCycles = 4000000000ll;
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status,
+                                          long long budget = kWaitBudgetCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t spin = 1;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 0x3FFu) == 0) {
             if (*reinterpret_cast<volatile int *>(status) != 0) return false;
-            if (clock64() - t0 > kWaitBudgetCycles) {
+            if (clock64() - t0 > budget) {
                 atomicCAS(status, 0, TMQ_ERR_TIMEOUT);
                 return false;
             }

@@ -31,16 +31,18 @@ constexpr int kConvThreads = 320;  // warp 0: weight TMA, warp 1: MMA, warps 2-5
 constexpr int kConvLag = 2;        // a gathered stage is published this many k-blocks after it was issued
 
 struct ConvArgs {
-    const __nv_bfloat16 *X;
+    const void *X;                  // bf16 or int8 NHWC
     const float *scale, *bias;
     const __nv_bfloat16 *residual;  // optional [M][N], added before the ReLU (ResNet skip connection)
-    __nv_bfloat16 *Y;
+    void *Y;                        // bf16 / fp32 (out_f32) / int32 NHWC
     int B, H, W, C, OH, OW, N;
     int ky, kx, sy, sx, py, px, dy, dx;
     long long M;  // B * OH * OW
     int relu;
     int *status;
 };
+
+enum { CONV_BF16 = 0, CONV_I8 = 1 };
 
 template <int BN>
 struct ConvSmem {
@@ -50,7 +52,7 @@ struct ConvSmem {
     static constexpr int kStages = BN > 128 ? 6 : 4;
     static constexpr int STAGE_BYTES = 4 * 2048;     // transpose areas of the four epilogue warps
     static constexpr int B_BYTES = BN * 128;
-    static constexpr int RAW_BYTES = 128 * 16;
+    static constexpr int RAW_BYTES = 128 * 32;       // 16 bytes per row and k-block for bf16, 32 for int8 activations
     static constexpr int STAGE_OFF = 0;
     static constexpr int B_OFF = STAGE_OFF + STAGE_BYTES;
     static constexpr int RAW_OFF = B_OFF + kStages * B_BYTES;
@@ -67,10 +69,14 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int BN>
+// KIND: CONV_BF16 (bf16 activations, 64 k per k-block, fp32 accumulation) or CONV_I8 (int8 activations, 128 k per
+// k-block, exact int32 accumulation and int32 output).  A k-block is always 128 bytes of one pixel's K run.
+template <int KIND, bool F32OUT, int BN>
 __global__ void __launch_bounds__(kConvThreads, BN > 128 ? 1 : 2)
 ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs args) {
     using L = ConvSmem<BN>;
+    constexpr int ESZ = KIND == CONV_BF16 ? 2 : 1;        // bytes per activation
+    constexpr int RAW_ROW = KIND == CONV_BF16 ? 16 : 32;  // packed bytes per weight row and k-block
     constexpr int kConvStages = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -84,8 +90,8 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long n0 = (long long)blockIdx.x * 128;
     const long long m0 = (long long)blockIdx.y * BN;
-    const int cpb = args.C / 64;                       // k-blocks per filter tap
-    const int nkb = args.ky * args.kx * cpb;
+    const int ntaps = args.ky * args.kx;
+    const int nkb = (ntaps * args.C * ESZ + 127) / 128;   // C % 64 == 0: only int8 can end on half a k-block
     constexpr uint32_t A_COLS = 32;                                   // one k-block of a weight row: 64 bf16
     constexpr uint32_t TMEM_NEED = BN + kConvStages * A_COLS;         // accumulator, then the ring of decoded weight tiles
     constexpr uint32_t TMEM_COLS = TMEM_NEED <= 256 ? 256 : 512;
@@ -119,14 +125,15 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
                 const int s = kb % kConvStages;
                 const uint32_t ph = (uint32_t)(kb / kConvStages) & 1u;
                 if (!ptx::mbar_wait(empty + s, ph ^ 1u, args.status)) break;
-                ptx::mbar_arrive_expect_tx(full_raw + s, (uint32_t)L::RAW_BYTES);
-                ptx::tma_load_2d(smem + L::RAW_OFF + s * L::RAW_BYTES, &tmap_w, full_raw + s, kb * 4, (int)n0);
+                ptx::mbar_arrive_expect_tx(full_raw + s, (uint32_t)(128 * RAW_ROW));
+                ptx::tma_load_2d(smem + L::RAW_OFF + s * L::RAW_BYTES, &tmap_w, full_raw + s, kb * (RAW_ROW / 4), (int)n0);
             }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0 && healthy) {
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
+            constexpr uint32_t idesc = ((KIND == CONV_BF16 ? 1u : 2u) << 4) | (1u << 7) | (1u << 10) |
+                                       ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; kb++) {
                 const int s = kb % kConvStages;
@@ -138,8 +145,12 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
                 const uint32_t a_tmem = tmem_base + BN + (uint32_t)s * A_COLS;
                 const uint64_t b_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES));
 #pragma unroll
-                for (int k4 = 0; k4 < 4; k4++)
-                    ptx::umma_f16_ts(tmem_base, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                for (int k4 = 0; k4 < 4; k4++) {     // 32 bytes of K per instruction
+                    if (KIND == CONV_BF16)
+                        ptx::umma_f16_ts(tmem_base, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                    else
+                        ptx::umma_i8_ts(tmem_base, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                }
                 ptx::umma_commit(empty + s);
             }
             if (ok) ptx::umma_commit(acc_full);
@@ -155,15 +166,29 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
             const uint32_t ph = (uint32_t)(kb / kConvStages) & 1u;
             ok = ptx::mbar_wait(full_raw + s, ph, args.status);
             if (!ok) break;
-            const uint4 p = *reinterpret_cast<const uint4 *>(smem + L::RAW_OFF + s * L::RAW_BYTES + row * 16);
-            const uint32_t words[4] = {p.x, p.y, p.z, p.w};
-            uint32_t cols[32];                        // the row's 64 bf16 of this k-block, K ascending
+            const uint8_t *raw = smem + L::RAW_OFF + s * L::RAW_BYTES + row * RAW_ROW;
+            uint32_t cols[32];                        // the row's 128 operand bytes of this k-block, K ascending
+            if (KIND == CONV_BF16) {
+                const uint4 p = *reinterpret_cast<const uint4 *>(raw);
+                const uint32_t words[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
-            for (int wi = 0; wi < 4; wi++) {
-                uint32_t r[8];
-                decode_word_bf16(words[wi], r);
+                for (int wi = 0; wi < 4; wi++) {
+                    uint32_t r[8];
+                    decode_word_bf16(words[wi], r);
 #pragma unroll
-                for (int j = 0; j < 8; j++) cols[8 * wi + j] = r[j];
+                    for (int j = 0; j < 8; j++) cols[8 * wi + j] = r[j];
+                }
+            } else {
+                const uint4 p0 = *reinterpret_cast<const uint4 *>(raw);
+                const uint4 p1 = *reinterpret_cast<const uint4 *>(raw + 16);
+                const uint32_t words[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                for (int wi = 0; wi < 8; wi++) {
+                    uint32_t r[4];
+                    decode_word_i8(words[wi], r);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) cols[4 * wi + j] = r[j];
+                }
             }
             ptx::tmem_st_x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + BN + (uint32_t)s * A_COLS, cols);
             ptx::tmem_st_wait();
@@ -175,8 +200,9 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
         ptx::tc_fence_after_sync();
         const int quarter = warp & 3;
         const long long n = n0 + quarter * 32 + lane;
-        float sc = 0.5f, bi = 0.0f;                   // operands carried +-2.0
-        if (ok && n < args.N) {
+        const bool n_ok = n < args.N;
+        float sc = KIND == CONV_BF16 ? 0.5f : 1.0f, bi = 0.0f;   // bf16 operands are carried as +-2.0
+        if (ok && n_ok) {
             if (args.scale) sc *= args.scale[n];
             if (args.bias) bi = args.bias[n];
         }
@@ -188,8 +214,25 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
                 uint32_t v[16];
                 ptx::tmem_ld_x16(lane_addr + (uint32_t)c, v);
                 ptx::tmem_ld_wait();
-                epilogue_chunk_bf16(v, sc, bi, stage, args.Y, args.residual, m0 + c, args.M, args.N, n0 + quarter * 32,
-                                    args.N, args.relu, lane);
+                if (KIND == CONV_BF16 && !F32OUT) {
+                    epilogue_chunk_bf16(v, sc, bi, stage, reinterpret_cast<__nv_bfloat16 *>(args.Y), args.residual, m0 + c,
+                                        args.M, args.N, n0 + quarter * 32, args.N, args.relu, lane);
+                } else if (n_ok) {
+                    // 4-byte outputs: lane = channel, so a store instruction covers 32 consecutive channels of one pixel
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const long long m = m0 + c + j;
+                        if (m < args.M) {
+                            if (KIND == CONV_I8) {
+                                reinterpret_cast<int *>(args.Y)[m * args.N + n] = (int)v[j];
+                            } else {
+                                float f = fmaf(__uint_as_float(v[j]), sc, bi);
+                                if (args.residual) f += __bfloat162float(args.residual[m * args.N + n]);
+                                reinterpret_cast<float *>(args.Y)[m * args.N + n] = args.relu ? fmaxf(f, 0.0f) : f;
+                            }
+                        }
+                    }
+                }
             }
         }
     } else {
@@ -233,16 +276,20 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
             const uint32_t ph = (uint32_t)(kb / kConvStages) & 1u;
             ok = ptx::mbar_wait(empty + s, ph ^ 1u, args.status);
             if (!ok) break;
-            const int tap = kb / cpb, c0 = (kb % cpb) * 64;
+            // this thread's 16-byte chunk of the k-block: which filter tap and which channels (with 64-channel int8
+            // layers a k-block spans two taps, so the tap is a per-chunk matter; past the last tap: zeros)
+            const int e0 = (kb * 128 + chunk * 16) / ESZ;
+            const int tap = e0 / args.C, c0 = e0 - tap * args.C;
+            const bool tap_ok = tap < ntaps;
             const int fy = (tap / args.kx) * args.dy, fx = (tap % args.kx) * args.dx;
             const uint32_t bbase = ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES);
-            const int delta = (fy * args.W + fx) * args.C + c0 + chunk * 8;   // the tap's distance from tap (0, 0)
+            const int delta = (fy * args.W + fx) * args.C + c0;   // the chunk's distance from tap (0, 0), channel 0
 #pragma unroll
             for (int i = 0; i < RPT; i++) {
                 const int r = rg + 16 * i;
                 const int iy = (int)((unsigned)ryx[i] >> 16) - 32768 + fy, ix = (ryx[i] & 0xFFFF) - 32768 + fx;
-                const bool inb = roff[i] != -1 && (unsigned)iy < (unsigned)args.H && (unsigned)ix < (unsigned)args.W;
-                const __nv_bfloat16 *src = inb ? args.X + (roff[i] + delta) : args.X;
+                const bool inb = tap_ok && roff[i] != -1 && (unsigned)iy < (unsigned)args.H && (unsigned)ix < (unsigned)args.W;
+                const char *src = reinterpret_cast<const char *>(args.X) + (inb ? (long long)(roff[i] + delta) * ESZ : 0ll);
                 // 0 source bytes = zero fill (padding, rows past the end)
                 cp_async_16(bbase + r * 128 + ((chunk ^ (r & 7)) << 4), src, inb ? 16u : 0u);
             }
@@ -283,24 +330,21 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
     }
 }
 
-template <int BN>
+template <int KIND, bool F32OUT, int BN>
 static int launch_conv(const uint32_t *Wt, const ConvArgs &a, long long K, cudaStream_t st) {
     using L = ConvSmem<BN>;
-    const long long KW = prepack_valid_words(K), KS = prepack_row_words(K, 0);
+    const long long KW = prepack_valid_words(K), KS = prepack_row_words(K, KIND);
     CUtensorMap mw;
-    if (!make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KS * 4, 4, 128,
-                     CU_TENSOR_MAP_SWIZZLE_NONE))
+    // box: one k-block of 128 rows; words beyond KW (an int8 k-block that ends past K) are filled with zeros
+    if (!make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KS * 4,
+                     KIND == CONV_BF16 ? 4 : 8, 128, CU_TENSOR_MAP_SWIZZLE_NONE))
         return TMQ_ERR_LAUNCH;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(ternary_conv_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    });
-    if (attr_err != cudaSuccess) return cuda_status(attr_err);
+    const int attr_rc = ensure_dynamic_smem(ternary_conv_kernel<KIND, F32OUT, BN>, L::TOTAL);
+    if (attr_rc != TMQ_OK) return attr_rc;
     const long long gy = (a.M + BN - 1) / BN;
     if (gy > 65535) return TMQ_ERR_UNSUPPORTED;
     dim3 grid((unsigned)((a.N + 127) / 128), (unsigned)gy);
-    ternary_conv_kernel<BN><<<grid, kConvThreads, L::TOTAL, st>>>(mw, a);
+    ternary_conv_kernel<KIND, F32OUT, BN><<<grid, kConvThreads, L::TOTAL, st>>>(mw, a);
     return launch_status();
 }
 
@@ -633,12 +677,8 @@ extern "C" int tmq_ternary_conv2d_stem_bf16(const float *X, const uint32_t *Wt, 
     if (!make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)N, (uint64_t)KS * 4, 4, 128,
                      CU_TENSOR_MAP_SWIZZLE_NONE))
         return TMQ_ERR_LAUNCH;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(ternary_stem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, StemSmem::TOTAL);
-    });
-    if (attr_err != cudaSuccess) return cuda_status(attr_err);
+    const int attr_rc = ensure_dynamic_smem(ternary_stem_kernel, StemSmem::TOTAL);
+    if (attr_rc != TMQ_OK) return attr_rc;
     dim3 grid((unsigned)(B * OH), (unsigned)((N + 127) / 128));
     ternary_stem_kernel<<<grid, kConvThreads, StemSmem::TOTAL, (cudaStream_t)stream>>>(mw, a);
     return launch_status();
@@ -689,9 +729,9 @@ extern "C" int tmq_maxpool2d_nhwc_bf16(const void *X, void *Y, int B, int H, int
     return launch_status();
 }
 
-extern "C" int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias,
-                                       const void *residual, void *Y, int B, int H, int W, int C, int N, int ky, int kx,
-                                       int sy, int sx, int py, int px, int dy, int dx, int relu, int *status, void *stream) {
+static int conv_common(const void *X, const uint32_t *Wt, const float *scale, const float *bias, const void *residual,
+                       void *Y, int B, int H, int W, int C, int N, int ky, int kx, int sy, int sx, int py, int px, int dy,
+                       int dx, int relu, int out_f32, int *status, int kind, cudaStream_t st) {
     if (!X || !Wt || !Y || !status) return TMQ_ERR_ARG;
     if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || N <= 0 || ky <= 0 || kx <= 0 || sy <= 0 || sx <= 0 || py < 0 || px < 0 ||
         dy <= 0 || dx <= 0)
@@ -701,12 +741,14 @@ extern "C" int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const 
     if ((long long)B * H * W * C > 0x7FFFFFFFll || H > 30000 || W > 30000 || py > 2000 || px > 2000) return TMQ_ERR_UNSUPPORTED;
     const int OH = (H + 2 * py - dy * (ky - 1) - 1) / sy + 1, OW = (W + 2 * px - dx * (kx - 1) - 1) / sx + 1;
     if (OH <= 0 || OW <= 0) return TMQ_ERR_ARG;
-    if (!aligned(X, 16) || !aligned(Wt, 16) || !aligned(Y, 2) || !aligned(status, 4)) return TMQ_ERR_ALIGN;
+    const size_t out_align = (kind == CONV_I8 || out_f32) ? 4 : 2;
+    if (!aligned(X, 16) || !aligned(Wt, 16) || !aligned(Y, out_align) || !aligned(residual, 2) || !aligned(status, 4))
+        return TMQ_ERR_ALIGN;
     ConvArgs a;
-    a.X = reinterpret_cast<const __nv_bfloat16 *>(X);
+    a.X = X;
     a.scale = scale; a.bias = bias;
     a.residual = reinterpret_cast<const __nv_bfloat16 *>(residual);
-    a.Y = reinterpret_cast<__nv_bfloat16 *>(Y);
+    a.Y = Y;
     a.B = B; a.H = H; a.W = W; a.C = C; a.OH = OH; a.OW = OW; a.N = N;
     a.ky = ky; a.kx = kx; a.sy = sy; a.sx = sx; a.py = py; a.px = px; a.dy = dy; a.dx = dx;
     a.M = (long long)B * OH * OW;
@@ -715,5 +757,29 @@ extern "C" int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const 
     const long long K = (long long)ky * kx * C;
     // 128-pixel tiles, two CTAs per SM: measured 69 k images/s on packed ResNet-18 against 55 k with one 256-pixel CTA per
     // SM wherever that filled the GPU (the second CTA hides set-up, pipeline fill and epilogue of the first)
-    return launch_conv<128>(Wt, a, K, (cudaStream_t)stream);
+    if (kind == CONV_I8) return launch_conv<CONV_I8, false, 128>(Wt, a, K, st);
+    if (out_f32) return launch_conv<CONV_BF16, true, 128>(Wt, a, K, st);
+    return launch_conv<CONV_BF16, false, 128>(Wt, a, K, st);
+}
+
+extern "C" int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias,
+                                       const void *residual, void *Y, int B, int H, int W, int C, int N, int ky, int kx,
+                                       int sy, int sx, int py, int px, int dy, int dx, int relu, int *status, void *stream) {
+    return conv_common(X, Wt, scale, bias, residual, Y, B, H, W, C, N, ky, kx, sy, sx, py, px, dy, dx, relu, 0, status,
+                       CONV_BF16, (cudaStream_t)stream);
+}
+
+extern "C" int tmq_ternary_conv2d_bf16_f32out(const void *X, const uint32_t *Wt, const float *scale, const float *bias,
+                                              const void *residual, float *Y, int B, int H, int W, int C, int N, int ky,
+                                              int kx, int sy, int sx, int py, int px, int dy, int dx, int relu, int *status,
+                                              void *stream) {
+    return conv_common(X, Wt, scale, bias, residual, Y, B, H, W, C, N, ky, kx, sy, sx, py, px, dy, dx, relu, 1, status,
+                       CONV_BF16, (cudaStream_t)stream);
+}
+
+extern "C" int tmq_ternary_conv2d_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int B, int H, int W, int C, int N,
+                                     int ky, int kx, int sy, int sx, int py, int px, int dy, int dx, int *status,
+                                     void *stream) {
+    return conv_common(X, Wt, nullptr, nullptr, nullptr, Y, B, H, W, C, N, ky, kx, sy, sx, py, px, dy, dx, 0, 0, status,
+                       CONV_I8, (cudaStream_t)stream);
 }

@@ -343,9 +343,9 @@ __device__ __forceinline__ uint32_t ref_code(const uint32_t *__restrict__ P, lon
     return (P[k * Q + (n >> 4)] >> (2 * (15 - (int)(n & 15)))) & 3u;
 }
 
-// fmt bit 0: 0 = bf16-ready word, 1 = int8-ready word.  fmt bit 1: 0 = row-major Wt[N][KW], 1 = tile-contiguous
-// Wt[tile][k-block][128 rows][words per row and k-block] (rows beyond N are zero), so that the raw tile of one
-// (128-channel tile, k-block) unit is a single contiguous 2 KB / 4 KB run.
+// fmt 0 = bf16-ready words, 1 = int8-ready words; row-major Wt[N][KS].  This kernel never executes
+// griddepcontrol.launch_dependents: a skinny kernel launched right behind it with programmatic stream serialisation
+// (which fetches Wt before its griddepcontrol.wait) therefore cannot start before every block of this grid has exited.
 __global__ void __launch_bounds__(256) prepack_kernel(const uint32_t *__restrict__ P, uint32_t *__restrict__ Wt,
                                                        long long N, long long K, long long KW, long long KS,
                                                        long long rows_out, int fmt) {
@@ -373,12 +373,24 @@ __global__ void __launch_bounds__(256) prepack_kernel(const uint32_t *__restrict
             }
         }
     }
-    if (fmt & 2) {
-        const int wpr = kind == KIND_BF16 ? 4 : 8;  // words per row and k-block
-        const long long tile = n >> 7, row = n & 127, kb = kw / wpr, wi = kw % wpr, nkb = KW / wpr;
-        Wt[((tile * nkb + kb) * 128 + row) * wpr + wi] = word;
-    } else {
-        Wt[n * KS + kw] = word;
+    Wt[n * KS + kw] = word;
+}
+
+// Ends tmq_prepack's work in the stream with an ordinary kernel boundary.  The skinny kernels read Wt ahead of their
+// griddepcontrol.wait; a plain launch between the writer of Wt and them guarantees the writer has completed and its
+// stores are visible before any such early read can be issued.
+__global__ void prepack_fence_kernel() {}
+
+// Test helper for the bounded waits: one thread waits on an mbarrier nobody ever completes, with the given budget,
+// and the kernel returns normally once the wait has given up (TMQ_ERR_TIMEOUT lands in *status).
+__global__ void wait_selftest_kernel(int *status, long long budget, long long *waited_cycles) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        ptx::fence_mbar_init();
+        const long long t0 = clock64();
+        const bool ok = ptx::mbar_wait(&bar, 0u, status, budget);
+        if (waited_cycles) *waited_cycles = ok ? -1 : clock64() - t0;
     }
 }
 
@@ -398,12 +410,8 @@ static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cud
     const bool okw = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KS * 4,
                                  KT::RAW_ROW / 4, kTileN, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!okx || !okw) return TMQ_ERR_LAUNCH;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(ternary_gemm_kernel<KIND, BN, TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    });
-    if (attr_err != cudaSuccess) return cuda_status(attr_err);
+    const int attr_rc = ensure_dynamic_smem(ternary_gemm_kernel<KIND, BN, TA>, L::TOTAL);
+    if (attr_rc != TMQ_OK) return attr_rc;
     const long long ntiles = ((a.N + kTileN - 1) / kTileN) * ((a.M + BN - 1) / BN);
     const unsigned grid = (unsigned)(ntiles < kNumSMs ? ntiles : kNumSMs);
     ternary_gemm_kernel<KIND, BN, TA><<<grid, kGemmThreads, L::TOTAL, st>>>(mx, mw, a);
@@ -448,24 +456,25 @@ extern "C" size_t tmq_prepack_words(int64_t N, int64_t K, int fmt) {
     return (size_t)N * tmq_prepack_row_words(K, fmt);
 }
 
-extern "C" size_t tmq_prepack_tiled_words(int64_t N, int64_t K, int fmt) {
-    if (N <= 0 || K <= 0) return 0;
-    const long long tiles = (N + 127) / 128;
-    const long long kw = (fmt & 1) ? ((K + 127) / 128) * 8 : ((K + 63) / 64) * 4;
-    return (size_t)tiles * 128 * (size_t)kw;
-}
-
 extern "C" int tmq_prepack(const uint32_t *P, uint32_t *Wt, int64_t N, int64_t K, int fmt, void *stream) {
-    if (!P || !Wt || N <= 0 || K <= 0 || fmt < 0 || fmt > 3) return TMQ_ERR_ARG;
+    if (!P || !Wt || N <= 0 || K <= 0 || fmt < 0 || fmt > 1) return TMQ_ERR_ARG;
     if (!aligned(Wt, 16)) return TMQ_ERR_ALIGN;
-    const bool tiled = (fmt & 2) != 0;
-    const long long KW = (tiled && (fmt & 1)) ? ((K + 127) / 128) * 8 : ((K + 63) / 64) * 4;
-    const long long rows_out = tiled ? ((N + 127) / 128) * 128 : N;
-    const long long KS = tiled ? KW : prepack_row_words(K, fmt & 1);
-    const long long total = rows_out * KS;
+    const long long KW = prepack_valid_words(K);
+    const long long KS = prepack_row_words(K, fmt & 1);
+    const long long total = N * KS;
     const long long blocks = (total + 255) / 256;
     if (blocks > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
-    prepack_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(P, Wt, N, K, KW, KS, rows_out, fmt);
+    prepack_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(P, Wt, N, K, KW, KS, N, fmt);
+    int rc = launch_status();
+    if (rc != TMQ_OK) return rc;
+    prepack_fence_kernel<<<1, 32, 0, (cudaStream_t)stream>>>();
+    return launch_status();
+}
+
+extern "C" int tmq_selftest_wait_timeout(long long budget_cycles, int *status, long long *waited_cycles, void *stream) {
+    if (!status || budget_cycles <= 0 || budget_cycles > 4000000000ll) return TMQ_ERR_ARG;
+    if (!aligned(status, 4) || !aligned(waited_cycles, 8)) return TMQ_ERR_ALIGN;
+    wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, budget_cycles, waited_cycles);
     return launch_status();
 }
 

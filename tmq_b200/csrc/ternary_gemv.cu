@@ -624,20 +624,6 @@ __global__ void __launch_bounds__(kResWarps * 32, 2) ternary_gemv_resident_dp4a_
     }
 }
 
-template <typename Kernel>
-static int resident_attributes(Kernel kernel, int slot) {
-    static std::mutex mu;
-    static bool done[8][64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TMQ_ERR_LAUNCH;
-    std::lock_guard<std::mutex> lock(mu);
-    if (done[slot][dev]) return TMQ_OK;
-    int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kResSmemMax));
-    if (rc == TMQ_OK) rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    if (rc == TMQ_OK) done[slot][dev] = true;
-    return rc;
-}
-
 // Returns TMQ_ERR_UNSUPPORTED when the CTA's rows do not fit the shared-memory budget (the caller then streams).
 template <int KIND>
 static int launch_gemv_resident(ResArgs a, cudaStream_t st) {
@@ -664,14 +650,14 @@ static int launch_gemv_resident(ResArgs a, cudaStream_t st) {
     cfg.numAttrs = 1;
     int rc;
     if (KIND == 1 && a.M == 1) {
-        if ((rc = resident_attributes(ternary_gemv_resident_dp4a_kernel<1>, 2)) != TMQ_OK) return rc;
+        if ((rc = ensure_dynamic_smem(ternary_gemv_resident_dp4a_kernel<1>, kResSmemMax, true)) != TMQ_OK) return rc;
         return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_resident_dp4a_kernel<1>, a));
     }
     if (KIND == 1 && a.M == 2) {
-        if ((rc = resident_attributes(ternary_gemv_resident_dp4a_kernel<2>, 3)) != TMQ_OK) return rc;
+        if ((rc = ensure_dynamic_smem(ternary_gemv_resident_dp4a_kernel<2>, kResSmemMax, true)) != TMQ_OK) return rc;
         return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_resident_dp4a_kernel<2>, a));
     }
-    if ((rc = resident_attributes(ternary_gemv_resident_kernel<KIND>, KIND)) != TMQ_OK) return rc;
+    if ((rc = ensure_dynamic_smem(ternary_gemv_resident_kernel<KIND>, kResSmemMax, true)) != TMQ_OK) return rc;
     return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_resident_kernel<KIND>, a));
 }
 

@@ -31,12 +31,18 @@ def shard_range(n, rank, world_size, align=1):
 
 
 class FlatGradBucket:
-    """All gradients of a model in one flat fp32 buffer, so a data-parallel step needs a single all-reduce.
+    """All gradients of a model in one flat fp32 buffer, so a data-parallel step needs no per-tensor collectives.
 
     After construction every parameter's .grad is a view into `self.flat`; backward accumulates straight into it.
-    `zero()` replaces optimizer.zero_grad(set_to_none=True), which would detach the views."""
+    `zero()` replaces optimizer.zero_grad(set_to_none=True), which would detach the views.
 
-    def __init__(self, params):
+    bucket_bytes=None: ONE all-reduce over the whole buffer in allreduce_mean().  With a size, the buffer is cut into
+    contiguous buckets walking the parameters from the last to the first (the order backward produces gradients in);
+    a bucket's all-reduce is launched asynchronously from a post-accumulate hook the moment its last gradient has
+    landed, so the collectives of the late layers run under the backward pass of the early ones and
+    allreduce_mean() only waits."""
+
+    def __init__(self, params, bucket_bytes=None):
         self.params = [p for p in params if p.requires_grad]
         if not self.params:
             raise ValueError("FlatGradBucket: no trainable parameters")
@@ -50,27 +56,62 @@ class FlatGradBucket:
         self.flat = torch.zeros(total, dtype=torch.float32, device=dev)
         for p, off in zip(self.params, self.offsets):
             p.grad = self.flat[off:off + p.numel()].view_as(p)
+        self.buckets = []                                # (begin, end) element ranges of self.flat, last layers first
+        self._works, self._left, self._hooks = [], [], []
+        if bucket_bytes is not None:
+            end, count, owner = total, 0, {}
+            for i in range(len(self.params) - 1, -1, -1):
+                owner[i] = len(self.buckets)
+                count += 1
+                if (end - self.offsets[i]) * 4 >= bucket_bytes or i == 0:
+                    self.buckets.append((self.offsets[i], end))
+                    self._left.append(count)
+                    end, count = self.offsets[i], 0
+            self._sizes = list(self._left)
+            self._works = [None] * len(self.buckets)
+            for i, p in enumerate(self.params):
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(owner[i])))
+
+    def _make_hook(self, b):
+        def hook(_param):
+            self._left[b] -= 1
+            if self._left[b] == 0 and world()[1] > 1:
+                lo, hi = self.buckets[b]
+                self._works[b] = dist.all_reduce(self.flat[lo:hi], op=dist.ReduceOp.SUM, async_op=True)
+        return hook
 
     def zero(self):
         self.flat.zero_()
 
     def allreduce_mean(self, group=None):
-        """Average the gradients over the ranks in place (sum all-reduce, then one scale)."""
+        """Average the gradients over the ranks in place (sum all-reduce(s), then one scale)."""
         _, n = world()
         if n == 1:
+            if self.buckets:
+                self._left = list(self._sizes)
             return None
-        work = dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group)
+        if not self.buckets:
+            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group)
+        else:
+            for b, (lo, hi) in enumerate(self.buckets):
+                if self._works[b] is None:           # a parameter took no part in this backward: reduce its bucket now
+                    self._works[b] = dist.all_reduce(self.flat[lo:hi], op=dist.ReduceOp.SUM, group=group, async_op=True)
+            for b in range(len(self.buckets)):
+                self._works[b].wait()
+                self._works[b] = None
+            self._left = list(self._sizes)
         self.flat.mul_(1.0 / n)
-        return work
+        return None
 
 
 class ColumnShardedLinear:
     """y = x @ T^T for a ternary weight whose output channels are split over the ranks.
 
-    `packed` is the reference-layout packed weight [K, ceil(N/16)] of the FULL matrix (every rank may hold it, or
-    only its own slice via `from_shard`); shard boundaries are multiples of 128 channels (the GEMM's tile height,
-    and a multiple of the 16-channel packing word).  `matmul(x, packed_shard, n_shard)` is the local product; the
-    default runs the CUDA GEMM."""
+    `packed` is the reference-layout packed weight [K, ceil(N/16)] of the FULL matrix; shard boundaries are multiples
+    of 128 channels (the GEMM's tile height, and a multiple of the 16-channel packing word).
+    `matmul(x, packed_shard, n_shard, scale, bias)` is the local product; the default runs the CUDA GEMM, whose epilogue
+    writes this rank's column block straight into its slot of the gather buffer, so the all-gather runs in place and no
+    block is copied before or after the collective."""
 
     ALIGN = 128
 
@@ -89,53 +130,55 @@ class ColumnShardedLinear:
         self._matmul = matmul
         self._wt = None
 
-    def local(self, x):
-        """Column block [M, n1 - n0] of this rank."""
+    def _out_dtype(self, x):
+        return x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.bfloat16
+
+    def local(self, x, out=None):
+        """Column block [M, n1 - n0] of this rank, written into `out` (rows may be wider than the block) when given."""
         n = self.n1 - self.n0
         if self._matmul is not None:
-            return self._matmul(x, self.packed_shard, n, self.scale, self.bias)
+            y = self._matmul(x, self.packed_shard, n, self.scale, self.bias)
+            if out is None:
+                return y
+            out[:, :n].copy_(y)
+            return out[:, :n]
         from . import ops
         if self._wt is None:
             self._wt = ops.prepack(self.packed_shard, n, ops.FMT_BF16)
-        return ops.ternary_gemm(x, self._wt, n, self.scale, self.bias, out_dtype=x.dtype
-                                if x.dtype in (torch.bfloat16, torch.float32) else torch.bfloat16)
+        return ops.ternary_gemm(x, self._wt, n, self.scale, self.bias, out_dtype=self._out_dtype(x),
+                                out=None if out is None else out[:, :n])
 
     def __call__(self, x, group=None, chunks=1, blocked=False):
-        """Full output on every rank.  chunks > 1 splits the rows so that the all-gather of one chunk overlaps the
-        GEMM of the next (equal shards only).  blocked=True returns the column blocks as [world, M, n_shard] without
-        the final interleaving copy (a consumer that walks K in blocks can use them as they are)."""
+        """Full output on every rank.  chunks > 1 splits the rows so that the all-gather of one chunk runs under the
+        GEMM of the next.  blocked=True returns the column blocks as they arrive, [chunks, world, M / chunks, widest]
+        (chunks == 1: [world, M, widest]), without the final interleaving copy - a consumer that walks K in blocks
+        can use them as they are; otherwise the result is the row-major [M, N] matrix."""
         if self.world == 1:
             y = self.local(x)
             return y.unsqueeze(0) if blocked else y
         widths = [b[1] - b[0] for b in self.bounds]
         widest = max(widths)
-        equal = all(wd == widest for wd in widths)
         m = x.shape[0]
-        if chunks > 1 and equal and m >= chunks:
-            first = self.local(x[:1])
-            gathered = torch.empty((self.world, m, widest), dtype=first.dtype, device=first.device)
-            edges = [m * i // chunks for i in range(chunks + 1)]
-            works = []
-            for i in range(chunks):
-                r0, r1 = edges[i], edges[i + 1]
-                y_c = self.local(x[r0:r1]).contiguous()
-                stage = torch.empty((self.world * (r1 - r0), widest), dtype=y_c.dtype, device=y_c.device)
-                works.append((dist.all_gather_into_tensor(stage, y_c, group=group, async_op=True), stage, r0, r1))
-            for work, stage, r0, r1 in works:
-                work.wait()
-                gathered[:, r0:r1, :].copy_(stage.view(self.world, r1 - r0, widest))
-            return gathered if blocked else gathered.permute(1, 0, 2).reshape(m, self.n_total)
-        send = self.local(x).contiguous()
-        if send.shape[1] != widest:      # collectives want equal shapes: the ragged last shard is padded for the trip
-            send = torch.nn.functional.pad(send, (0, widest - send.shape[1]))
-        stacked = torch.empty((self.world * send.shape[0], widest), dtype=send.dtype, device=send.device)
-        dist.all_gather_into_tensor(stacked, send, group=group)      # rank blocks concatenated along dim 0
-        gathered = stacked.view(self.world, send.shape[0], widest)
-        if blocked and equal:
-            return gathered
-        if equal:
-            return gathered.permute(1, 0, 2).reshape(send.shape[0], self.n_total)
-        return torch.cat([gathered[r, :, :wd] for r, wd in enumerate(widths)], dim=1)
+        if chunks < 1 or m % chunks != 0:
+            chunks = 1
+        rows = m // chunks
+        buf = torch.empty((chunks, self.world, rows, widest), dtype=self._out_dtype(x), device=x.device)
+        works = []
+        for c in range(chunks):
+            mine = buf[c, self.rank]                                         # this rank's slot of the gather buffer
+            self.local(x[c * rows:(c + 1) * rows], out=mine)
+            if widths[self.rank] != widest:
+                mine[:, widths[self.rank]:].zero_()                          # ragged last shard: defined padding
+            works.append(dist.all_gather_into_tensor(buf[c].view(self.world * rows, widest), mine, group=group,
+                                                     async_op=True))         # in place: input is a slice of the output
+        for w_ in works:
+            w_.wait()
+        if blocked:
+            return buf if chunks > 1 else buf[0]
+        if all(wd == widest for wd in widths):
+            return buf.permute(0, 2, 1, 3).reshape(m, self.n_total)
+        full = buf.permute(0, 2, 1, 3).reshape(m, self.world, widest)
+        return torch.cat([full[:, r, :wd] for r, wd in enumerate(widths)], dim=1)
 
 
 def allreduce_scalar(t, group=None):

@@ -36,12 +36,15 @@ def _require_cuda_f32(t, name):
 
 
 def reduce_scratch(device):
-    """Per-device scratch of the two-stage reductions (zeroed once; the kernels leave it zeroed)."""
+    """Scratch of the two-stage reductions for the CURRENT stream of `device` (zeroed once; the kernels leave it
+    zeroed).  Calls that share a scratch buffer must be ordered on one stream, so every stream gets its own: a
+    reduction on a side stream can then never meet one on the caller's stream in the same partial sums."""
     device = torch.device(device)
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, torch.cuda.current_stream(index).cuda_stream)
     buf = _scratch.get(key)
     if buf is None:
-        buf = torch.zeros(lib().tmq_reduce_scratch_bytes(), dtype=torch.uint8, device=device)
+        buf = torch.zeros(lib().tmq_reduce_scratch_bytes(), dtype=torch.uint8, device=torch.device("cuda", index))
         _scratch[key] = buf
     return buf
 
@@ -424,9 +427,8 @@ def expand_ternary(packed, orig_shape, entropy_decode=False):
 # ------------------------------------------------------------------------------------------------ ternary GEMM
 
 FMT_BF16, FMT_I8 = 0, 1
-FMT_BF16_TILED, FMT_I8_TILED = 2, 3     # tile-contiguous storage for the skinny tensor-core kernel
-GEMV_MAX_ROWS = 32        # up to here the split-K streaming kernel is used instead of the tiled one
 _status = {}
+_watch = {}
 
 
 def gemm_status_word(device):
@@ -440,27 +442,57 @@ def gemm_status_word(device):
     return buf
 
 
+def _raise_status(device, code):
+    gemm_status_word(device).zero_()           # re-arm: the word is sticky, every launch skips while it is non-zero
+    raise _lib.TmqError(f"ternary GEMM kernel reported status {code}: {lib().tmq_status_string(code).decode()}; "
+                        "results produced on this device since the previous check are invalid")
+
+
 def check_gemm_status(device="cuda"):
-    """Synchronising check: raises if any GEMM launch on this device gave up on a device-side wait."""
+    """Synchronising check: raises if any GEMM / GEMV / convolution launch on this device gave up on a device-side
+    wait, and re-arms the status word."""
     code = int(gemm_status_word(device).item())
     if code != 0:
-        gemm_status_word(device).zero_()
-        raise _lib.TmqError(f"ternary GEMM kernel reported status {code}: "
-                            f"{lib().tmq_status_string(code).decode()}")
+        _raise_status(device, code)
 
 
-_gemv_ws = {}
+class _StatusWatch:
+    """Non-blocking watch over a device's status word.  A kernel that gives up on a bounded wait makes every later
+    launch skip its work (the word is sticky) while the C calls keep returning TMQ_OK, so somebody has to look: every
+    `EVERY` launches the word is copied to pinned host memory behind the work already queued, and the next operator
+    call that finds the copy finished raises if it is non-zero.  No synchronisation is added; a failure surfaces
+    within about 2 * EVERY operator calls instead of never."""
+
+    EVERY = 32
+
+    def __init__(self, device):
+        self.device = device
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+        self.launches = 0
+
+    def note_launch(self):
+        if self.pending and self.event.query():
+            self.pending = False
+            code = int(self.host[0])
+            if code != 0:
+                _raise_status(self.device, code)
+        self.launches += 1
+        if not self.pending and self.launches % self.EVERY == 1 and not torch.cuda.is_current_stream_capturing():
+            self.host.copy_(gemm_status_word(self.device), non_blocking=True)
+            self.event.record()
+            self.pending = True
 
 
-def gemv_workspace(device, nbytes):
-    """Per-device workspace of the split-K GEMV kernel (zeroed when created; the kernel re-arms it)."""
+def _launched(device):
+    """Book-keeping after a tensor-core launch on `device` (see _StatusWatch)."""
     device = torch.device(device)
     key = device.index if device.index is not None else torch.cuda.current_device()
-    buf = _gemv_ws.get(key)
-    if buf is None or buf.numel() < nbytes:
-        buf = torch.zeros(int(nbytes), dtype=torch.uint8, device=device)
-        _gemv_ws[key] = buf
-    return buf
+    w = _watch.get(key)
+    if w is None:
+        w = _watch[key] = _StatusWatch(torch.device("cuda", key))
+    w.note_launch()
 
 
 def prepack_row_words(k, fmt):
@@ -479,19 +511,17 @@ def prepack(packed, columns, fmt=FMT_BF16):
     Q = (N + 15) // 16
     p = packed.contiguous().view(-1, Q)
     K = p.shape[0]
-    if fmt in (FMT_BF16_TILED, FMT_I8_TILED):
-        out = torch.empty(lib().tmq_prepack_tiled_words(N, K, int(fmt)), dtype=torch.int32, device=p.device)
-    else:
-        out = torch.empty((N, lib().tmq_prepack_row_words(K, int(fmt))), dtype=torch.int32, device=p.device)
+    if fmt not in (FMT_BF16, FMT_I8):
+        raise ValueError("prepack: fmt must be FMT_BF16 or FMT_I8")
+    out = torch.empty((N, lib().tmq_prepack_row_words(K, int(fmt))), dtype=torch.int32, device=p.device)
     with torch.cuda.device(p.device):
         check(lib().tmq_prepack(_ptr(p), _ptr(out), N, K, int(fmt), _stream(p)), "prepack")
     return out
 
 
-def _pick_path(path, M, have_tiled):
+def _pick_path(path, M):
     """auto: up to 16 rows go through the skinny kernel in passes of 8 (measured faster than one 32-row tensor-core
-    tile there), anything taller through the tiled tensor-core kernel.  "tc" (persistent stream-K skinny kernel on
-    tile-contiguous weights) is never chosen automatically: it measures slower than both."""
+    tile there), anything taller through the tiled tensor-core kernel."""
     if path != "auto":
         return path
     if M <= 16:
@@ -499,20 +529,17 @@ def _pick_path(path, M, have_tiled):
     return "tiles"
 
 
-def _check_weights(name, wt, N, K, wt_tiled, fmt_tiled):
-    if wt is not None and (wt.dtype != torch.int32 or wt.dim() != 2 or wt.shape[0] != N or not wt.is_contiguous()
-                           or wt.shape[1] != lib().tmq_prepack_row_words(K, fmt_tiled & 1)):
+def _check_weights(name, wt, N, K, fmt):
+    if wt is None or wt.dtype != torch.int32 or wt.dim() != 2 or wt.shape[0] != N or not wt.is_contiguous() \
+            or wt.shape[1] != lib().tmq_prepack_row_words(K, fmt):
         raise RuntimeError(f"{name}: prepacked weights do not match the problem shape")
-    if wt_tiled is not None and (wt_tiled.dtype != torch.int32
-                                 or wt_tiled.numel() != lib().tmq_prepack_tiled_words(N, K, fmt_tiled)):
-        raise RuntimeError(f"{name}: tiled prepacked weights do not match the problem shape")
 
 
-def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16, path="auto", wt_tiled=None):
+def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16, path="auto", out=None):
     """Y = scale * (x @ T^T) + bias with x bf16 [M, K]; fp32 accumulation; Y is bf16 or fp32 [M, N].
-    wt: prepack(..., FMT_BF16); wt_tiled: prepack(..., FMT_BF16_TILED), needed by the skinny tensor-core kernel.
-    path: "auto", or pin "tiles" (tiled tcgen05 GEMM), "tc" (persistent split-K tcgen05 kernel, M <= 32, tiled
-    weights) or "gemv" (warp-level MMA streaming kernel, 8 rows per pass)."""
+    wt: prepack(..., FMT_BF16).  path: "auto", or pin "tiles" (tiled tcgen05 GEMM) or "gemv" (warp-level MMA skinny
+    kernel, 8 rows per pass).  out: optional preallocated [M, >= N] tensor of the output dtype whose rows may be
+    strided (a column block of a wider matrix); it is written in place and returned."""
     if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 2:
         raise RuntimeError("ternary_gemm: expected a 2-D CUDA bf16 activation tensor")
     if out_dtype not in (torch.bfloat16, torch.float32):
@@ -520,75 +547,64 @@ def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16
     x = x.contiguous()
     M, K = x.shape
     N = int(columns)
-    _check_weights("ternary_gemm", wt, N, K, wt_tiled, FMT_BF16_TILED)
-    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _check_weights("ternary_gemm", wt, N, K, FMT_BF16)
+    if out is None:
+        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    else:
+        if out.dtype != out_dtype or out.device != x.device or out.dim() != 2 or tuple(out.shape) != (M, N) \
+                or out.stride(1) != 1 or out.stride(0) < N:
+            raise RuntimeError("ternary_gemm: `out` must be an [M, N] tensor of the output dtype with unit column stride")
+        y = out
+    ldy = y.stride(0) if M > 1 else max(N, y.stride(0))
     if M == 0:
         return y
     sc = None if scale is None else scale.to(device=x.device, dtype=torch.float32).contiguous()
     bi = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
     psc, pbi = (_ptr(sc) if sc is not None else None), (_ptr(bi) if bi is not None else None)
     f32 = 1 if out_dtype == torch.float32 else 0
-    path = _pick_path(path, M, wt_tiled is not None)
-    if path != "tc" and wt is None:
-        raise RuntimeError("ternary_gemm: this path needs the row-major prepacked weights")
+    path = _pick_path(path, M)
+    st = gemm_status_word(x.device)
     with torch.cuda.device(x.device):
-        if path == "tc":
-            if wt_tiled is None or M > GEMV_MAX_ROWS:
-                raise RuntimeError("ternary_gemm: the skinny tensor-core path needs tiled weights and M <= 32")
-            ws = gemv_workspace(x.device, lib().tmq_gemv_workspace_bytes(M, N, K))
-            st = gemm_status_word(x.device)
-            check(lib().tmq_ternary_gemv_tc_bf16(_ptr(x), _ptr(wt_tiled), psc, pbi, _ptr(y), M, N, K, N, f32, _ptr(ws),
-                                                 ws.numel(), _ptr(st), _stream(x)), "ternary_gemv_tc")
-        elif path == "gemv":
+        if path == "gemv":
             esz = y.element_size()
-            st = gemm_status_word(x.device)
             for m0 in range(0, M, 8):
                 check(lib().tmq_ternary_gemv_bf16(ctypes.c_void_p(x.data_ptr() + m0 * K * 2), _ptr(wt), psc, pbi,
-                                                  ctypes.c_void_p(y.data_ptr() + m0 * N * esz), min(8, M - m0), N, K, N,
-                                                  f32, _ptr(st), _stream(x)), "ternary_gemv")
+                                                  ctypes.c_void_p(y.data_ptr() + m0 * ldy * esz), min(8, M - m0), N, K,
+                                                  ldy, f32, _ptr(st), _stream(x)), "ternary_gemv")
         elif path == "tiles":
-            st = gemm_status_word(x.device)
-            check(lib().tmq_ternary_gemm_bf16(_ptr(x), _ptr(wt), psc, pbi, _ptr(y), M, N, K, N, f32, _ptr(st),
+            check(lib().tmq_ternary_gemm_bf16(_ptr(x), _ptr(wt), psc, pbi, _ptr(y), M, N, K, ldy, f32, _ptr(st),
                                               _stream(x)), "ternary_gemm")
         else:
             raise ValueError(f"ternary_gemm: unknown path {path!r}")
+    _launched(x.device)
     return y
 
 
-def ternary_gemm_i8(x, wt, columns, path="auto", wt_tiled=None):
-    """Exact int32 Y = x @ T^T with x int8 [M, K]; wt: prepack(..., FMT_I8), wt_tiled: prepack(..., FMT_I8_TILED)."""
+def ternary_gemm_i8(x, wt, columns, path="auto"):
+    """Exact int32 Y = x @ T^T with x int8 [M, K]; wt: prepack(..., FMT_I8)."""
     if x.dtype != torch.int8 or x.device.type != "cuda" or x.dim() != 2:
         raise RuntimeError("ternary_gemm_i8: expected a 2-D CUDA int8 activation tensor")
     x = x.contiguous()
     M, K = x.shape
     N = int(columns)
-    _check_weights("ternary_gemm_i8", wt, N, K, wt_tiled, FMT_I8_TILED)
+    _check_weights("ternary_gemm_i8", wt, N, K, FMT_I8)
     y = torch.empty((M, N), dtype=torch.int32, device=x.device)
     if M == 0:
         return y
-    path = _pick_path(path, M, wt_tiled is not None)
-    if path != "tc" and wt is None:
-        raise RuntimeError("ternary_gemm_i8: this path needs the row-major prepacked weights")
+    path = _pick_path(path, M)
+    st = gemm_status_word(x.device)
     with torch.cuda.device(x.device):
-        if path == "tc":
-            if wt_tiled is None or M > GEMV_MAX_ROWS:
-                raise RuntimeError("ternary_gemm_i8: the skinny tensor-core path needs tiled weights and M <= 32")
-            ws = gemv_workspace(x.device, lib().tmq_gemv_workspace_bytes(M, N, K))
-            st = gemm_status_word(x.device)
-            check(lib().tmq_ternary_gemv_tc_i8(_ptr(x), _ptr(wt_tiled), _ptr(y), M, N, K, N, _ptr(ws), ws.numel(),
-                                               _ptr(st), _stream(x)), "ternary_gemv_tc_i8")
-        elif path == "gemv":
-            st = gemm_status_word(x.device)
+        if path == "gemv":
             for m0 in range(0, M, 8):
                 check(lib().tmq_ternary_gemv_i8(ctypes.c_void_p(x.data_ptr() + m0 * K), _ptr(wt),
                                                 ctypes.c_void_p(y.data_ptr() + m0 * N * 4), min(8, M - m0), N, K, N,
                                                 _ptr(st), _stream(x)), "ternary_gemv_i8")
         elif path == "tiles":
-            st = gemm_status_word(x.device)
             check(lib().tmq_ternary_gemm_i8(_ptr(x), _ptr(wt), _ptr(y), M, N, K, N, _ptr(st), _stream(x)),
                   "ternary_gemm_i8")
         else:
             raise ValueError(f"ternary_gemm_i8: unknown path {path!r}")
+    _launched(x.device)
     return y
 
 
@@ -614,34 +630,104 @@ def conv_patches(x, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1)):
 
 
 def ternary_conv2d_nhwc(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1), scale=None, bias=None,
-                        relu=False, residual=None):
-    """Implicit-GEMM convolution: x bf16 NHWC [B, H, W, C] (C % 64 == 0), wt = prepack(FMT_BF16) of the packed weight
-    with rows in (ky, kx, c) order -> bf16 NHWC [B, OH, OW, N]."""
-    if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 4 or not x.is_contiguous():
-        raise RuntimeError("ternary_conv2d_nhwc: expected a contiguous 4-D CUDA bf16 NHWC tensor")
+                        relu=False, residual=None, out_dtype=None):
+    """Implicit-GEMM convolution on NHWC activations [B, H, W, C] (C % 64 == 0) -> NHWC [B, OH, OW, N].
+    bf16 x: wt = prepack(FMT_BF16) of the packed weight with rows in (ky, kx, c) order; output bf16 (default) or fp32
+    (out_dtype=torch.float32: no output rounding).  int8 x: wt = prepack(FMT_I8) of the same rows; exact int32 output,
+    no scale / bias / residual / ReLU."""
+    if x.device.type != "cuda" or x.dim() != 4 or not x.is_contiguous() or x.dtype not in (torch.bfloat16, torch.int8):
+        raise RuntimeError("ternary_conv2d_nhwc: expected a contiguous 4-D CUDA bf16 or int8 NHWC tensor")
+    i8 = x.dtype == torch.int8
     b, h, w, c = x.shape
     (ky, kx), (sy, sx), (py, px), (dy, dx) = kernel, stride, padding, dilation
     n = int(columns)
     if c % 64 != 0:
         raise RuntimeError("ternary_conv2d_nhwc: the channel count must be a multiple of 64")
-    if wt.dtype != torch.int32 or wt.shape[0] != n or wt.shape[1] != prepack_row_words(ky * kx * c, FMT_BF16):
+    fmt = FMT_I8 if i8 else FMT_BF16
+    if wt.dtype != torch.int32 or wt.shape[0] != n or wt.shape[1] != prepack_row_words(ky * kx * c, fmt):
         raise RuntimeError("ternary_conv2d_nhwc: prepacked weights do not match the problem shape")
+    if out_dtype is None:
+        out_dtype = torch.int32 if i8 else torch.bfloat16
+    if out_dtype != (torch.int32 if i8 else out_dtype) or out_dtype not in (torch.bfloat16, torch.float32, torch.int32):
+        raise ValueError("ternary_conv2d_nhwc: bf16 activations give bf16 or fp32, int8 activations int32")
+    if i8 and (scale is not None or bias is not None or residual is not None or relu):
+        raise ValueError("ternary_conv2d_nhwc: the int8 form returns the bare int32 sums")
     oh = (h + 2 * py - dy * (ky - 1) - 1) // sy + 1
     ow = (w + 2 * px - dx * (kx - 1) - 1) // sx + 1
-    y = torch.empty((b, oh, ow, n), dtype=torch.bfloat16, device=x.device)
-    sc = None if scale is None else scale.to(device=x.device, dtype=torch.float32).contiguous()
-    bi = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
+    y = torch.empty((b, oh, ow, n), dtype=out_dtype, device=x.device)
+    sc, bi = _opt_f32(scale, x.device), _opt_f32(bias, x.device)
     if residual is not None and (residual.dtype != torch.bfloat16 or tuple(residual.shape) != tuple(y.shape)
                                  or not residual.is_contiguous()):
         raise RuntimeError("ternary_conv2d_nhwc: the residual must be a contiguous bf16 tensor of the output's shape")
     st = gemm_status_word(x.device)
+    geom = (b, h, w, c, n, ky, kx, sy, sx, py, px, dy, dx)
     with torch.cuda.device(x.device):
-        check(lib().tmq_ternary_conv2d_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
-                                            _ptr(bi) if bi is not None else None,
-                                            _ptr(residual) if residual is not None else None, _ptr(y), b, h, w, c, n, ky,
-                                            kx, sy, sx,
-                                            py, px, dy, dx, 1 if relu else 0, _ptr(st), _stream(x)),
-              "ternary_conv2d_nhwc")
+        if i8:
+            check(lib().tmq_ternary_conv2d_i8(_ptr(x), _ptr(wt), _ptr(y), *geom, _ptr(st), _stream(x)), "ternary_conv2d_i8")
+        else:
+            fn = lib().tmq_ternary_conv2d_bf16_f32out if out_dtype == torch.float32 else lib().tmq_ternary_conv2d_bf16
+            check(fn(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None, _ptr(bi) if bi is not None else None,
+                     _ptr(residual) if residual is not None else None, _ptr(y), *geom, 1 if relu else 0, _ptr(st),
+                     _stream(x)), "ternary_conv2d_nhwc")
+    _launched(x.device)
+    return y
+
+
+def conv_rows_kkc(packed, cin, ky, kx, terms=1, pad_to=8):
+    """Packed convolution weights (reference layout: rows in (c, ky, kx) order, [cin * ky * kx, ceil(N/16)] or the 4-D form)
+    -> the row order the implicit GEMM walks, (ky, kx, c), channel runs contiguous as in NHWC.  terms = 3 repeats each
+    tap's channel block three times (for activations split into three bf16 terms along the channels); the row count is
+    padded with zero rows to a multiple of `pad_to`."""
+    rows = packed.contiguous().view(-1, packed.shape[-1])
+    taps = int(ky) * int(kx)
+    if rows.shape[0] != int(cin) * taps:
+        raise RuntimeError("conv_rows_kkc: packed weights do not match the kernel geometry")
+    r = rows.view(int(cin), taps, -1).transpose(0, 1)                  # [tap, c, Q]
+    if terms > 1:
+        r = r.unsqueeze(1).expand(taps, terms, int(cin), r.shape[-1])  # [tap, term, c, Q]
+    r = r.reshape(-1, rows.shape[-1])
+    pad = (-r.shape[0]) % int(pad_to)
+    if pad:
+        r = torch.nn.functional.pad(r, (0, 0, 0, pad))
+    return r.contiguous()
+
+
+def split_f32(x2d, terms=3, kp=None):
+    """fp32 [M, K] -> bf16 [M, terms * kp]: terms = 1 rounds, terms = 3 is the exact split x = hi + mid + lo with term t
+    in columns [t * kp, t * kp + K); kp >= K pads every term with zero columns."""
+    if x2d.dtype != torch.float32 or x2d.device.type != "cuda" or x2d.dim() != 2:
+        raise RuntimeError("split_f32: expected a 2-D CUDA float32 tensor")
+    x2d = x2d.contiguous()
+    m, k = x2d.shape
+    kp = k if kp is None else int(kp)
+    out = torch.empty((m, terms * kp), dtype=torch.bfloat16, device=x2d.device)
+    if m:
+        with torch.cuda.device(x2d.device):
+            check(lib().tmq_split_f32_bf16(_ptr(x2d), _ptr(out), m, k, kp, int(terms), _stream(x2d)), "split_f32")
+    return out
+
+
+def nchw_to_nhwc_bf16(x, terms=1):
+    """fp32 NCHW [B, C, H, W] (contiguous) -> bf16 NHWC [B, H, W, terms * C] in one pass (terms as in split_f32)."""
+    if x.dtype != torch.float32 or x.device.type != "cuda" or x.dim() != 4:
+        raise RuntimeError("nchw_to_nhwc_bf16: expected a 4-D CUDA float32 tensor")
+    x = x.contiguous()
+    b, c, h, w = x.shape
+    y = torch.empty((b, h, w, terms * c), dtype=torch.bfloat16, device=x.device)
+    if x.numel():
+        with torch.cuda.device(x.device):
+            check(lib().tmq_nchw_f32_to_nhwc_bf16(_ptr(x), _ptr(y), b, c, h, w, int(terms), _stream(x)), "nchw_to_nhwc_bf16")
+    return y
+
+
+def avgpool_nhwc(x):
+    """Global average pooling of a contiguous bf16 NHWC tensor [B, H, W, C] (C even) -> bf16 [B, C], fp32 sums."""
+    if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 4 or not x.is_contiguous():
+        raise RuntimeError("avgpool_nhwc: expected a contiguous 4-D CUDA bf16 NHWC tensor")
+    b, h, w, c = x.shape
+    y = torch.empty((b, c), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().tmq_avgpool_nhwc_bf16(_ptr(x), _ptr(y), b, h * w, c, _stream(x)), "avgpool_nhwc")
     return y
 
 
@@ -673,6 +759,7 @@ def ternary_conv2d_stem(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), s
     if rc == -6:
         return None
     check(rc, "ternary_conv2d_stem")
+    _launched(x.device)
     return y
 
 
@@ -787,21 +874,26 @@ def ternary_dwconvtrans_cuda(x, weights, kx, ky):
     return y
 
 
-_f32_weights = {}      # (data_ptr, version, shape, columns, k) -> three stacked copies of the weights, prepacked
+_f32_weights = {}      # (id of the weight tensor, columns, k) -> (tensor, version, data_ptr, shape, stacked prepack)
 
 
 def _stacked_prepack(weights, columns, k8):
-    key = (weights.data_ptr(), weights._version, tuple(weights.shape), int(columns), k8, str(weights.device))
+    """Three stacked copies of the packed weights in the kernels' layout, cached per weight TENSOR OBJECT: the entry
+    keeps the tensor alive (so its id cannot be recycled) and is rebuilt when the tensor's version counter, storage or
+    shape changed.  A fresh tensor object (for instance `param.data`, which makes a new one on every access) is a
+    cache miss: slower, never stale."""
+    key = (id(weights), int(columns), k8)
     hit = _f32_weights.get(key)
-    if hit is None:
-        if len(_f32_weights) >= 64:
+    tag = (weights._version, weights.data_ptr(), tuple(weights.shape))
+    if hit is None or hit[0] is not weights or hit[1] != tag:
+        if len(_f32_weights) >= 32:
             _f32_weights.clear()
         p = weights.contiguous().view(-1, weights.shape[-1])
         if k8 > p.shape[0]:
             p = torch.nn.functional.pad(p, (0, 0, 0, k8 - p.shape[0]))
-        hit = prepack(torch.cat([p, p, p], dim=0), columns, FMT_BF16)
+        hit = (weights, tag, prepack(torch.cat([p, p, p], dim=0), columns, FMT_BF16))
         _f32_weights[key] = hit
-    return hit
+    return hit[2]
 
 
 def ternary_gemm_f32(x2d, weights, columns, scale=None, bias=None):
@@ -816,15 +908,9 @@ def ternary_gemm_f32(x2d, weights, columns, scale=None, bias=None):
     rows = weights.numel() // weights.shape[-1]
     if rows != k:
         raise RuntimeError("ternary_gemm_f32: activation width does not match the packed weights")
-    pad = (-k) % 8
-    if pad:
-        x2d = torch.nn.functional.pad(x2d, (0, pad))
-    hi = x2d.to(torch.bfloat16)
-    r1 = x2d - hi.float()
-    mid = r1.to(torch.bfloat16)
-    lo = (r1 - mid.float()).to(torch.bfloat16)
-    return ternary_gemm(torch.cat([hi, mid, lo], dim=1), _stacked_prepack(weights, columns, k + pad), int(columns), scale,
-                        bias, out_dtype=torch.float32)
+    kp = (k + 7) // 8 * 8
+    return ternary_gemm(split_f32(x2d, 3, kp), _stacked_prepack(weights, columns, kp), int(columns), scale, bias,
+                        out_dtype=torch.float32)
 
 
 def ternary_mmm_cuda(x, weights, columns):

@@ -406,23 +406,34 @@ class TMQLayer:
 
     # ---- compact inference helpers -------------------------------------------------------------------------------------
 
-    def _prepacked_weights(self, fmt, k_repeat=1, k_each=None):
-        """Kernel-side layout of the packed weights, built on first use and whenever the packed tensor changes.
-        k_repeat = 3 stacks three copies along K (each zero-padded to k_each rows) for the exact fp32 path."""
-        w = self.weight.data
-        key = (fmt, k_repeat, k_each)
-        tag = (w.data_ptr(), w._version, tuple(w.shape), str(w.device))
+    def _cached_layout(self, key, build):
+        """Kernel-side layout of the packed weights under `key`, built by build() on first use and whenever the packed
+        tensor changes."""
+        # identity of the packed tensor: the Parameter object (kept alive by the cache entry, so its id cannot be
+        # recycled), its in-place version counter (copy_ / load_state_dict bump it; `.data` would always read 0), and
+        # the storage it points at (module.to(...) rebinds .data under the same Parameter)
+        p = self.weight
+        tag = (id(p), p._version, p.data_ptr(), tuple(p.shape), str(p.device))
         hit = self._prepacked.get(key)
+        if hit is not None and hit[0][0] != tag[0]:
+            self._prepacked.clear()               # a different Parameter was bound: every cached layout is stale
+            hit = None
         if hit is None or hit[0] != tag:
-            n_out = self._gemm_columns()
+            hit = (tag, build(), p)
+            self._prepacked[key] = hit
+        return hit[1]
+
+    def _prepacked_weights(self, fmt, k_repeat=1, k_each=None):
+        """GEMM layout of the layer's packed matrix.  k_repeat = 3 stacks three copies along K (each zero-padded to
+        k_each rows) for the exact fp32 path."""
+        def build():
             packed = self._packed_matrix()
             if k_each is not None and k_each > packed.shape[0]:
                 packed = torch.nn.functional.pad(packed, (0, 0, 0, k_each - packed.shape[0]))
             if k_repeat > 1:
                 packed = torch.cat([packed] * k_repeat, dim=0)
-            hit = (tag, ops.prepack(packed, n_out, fmt))
-            self._prepacked[key] = hit
-        return hit[1]
+            return ops.prepack(packed, self._gemm_columns(), fmt)
+        return self._cached_layout((fmt, k_repeat, k_each), build)
 
     def _gemm_columns(self):
         """Output width N of the layer's GEMM."""
@@ -461,15 +472,9 @@ class TMQLayer:
             raise RuntimeError("compact inference: activations must be float32, bfloat16 or int8")
         # fp32 activations: x = hi + mid + lo with three bf16 terms is exact, so is every product with {-1,0,1};
         # the three terms ride along K against three stacked copies of the weights, accumulation is fp32
-        pad = (-k) % 8
-        if pad:
-            x2d = torch.nn.functional.pad(x2d, (0, pad))
-        hi = x2d.to(torch.bfloat16)
-        r1 = x2d - hi.float()
-        mid = r1.to(torch.bfloat16)
-        lo = (r1 - mid.float()).to(torch.bfloat16)
-        x3 = torch.cat([hi, mid, lo], dim=1)
-        return ops.ternary_gemm(x3, self._prepacked_weights(ops.FMT_BF16, k_repeat=3, k_each=x2d.shape[1]), n_out,
+        kp = (k + 7) // 8 * 8
+        x3 = ops.split_f32(x2d, 3, kp)                      # one kernel: [M, 3 * kp] bf16
+        return ops.ternary_gemm(x3, self._prepacked_weights(ops.FMT_BF16, k_repeat=3, k_each=kp), n_out,
                                 scale, bias, out_dtype=torch.float32)
 
     def _load_compact_metadata(self, state_dict, prefix, local_metadata):
@@ -611,8 +616,10 @@ class Conv2d(nn.Module, TMQLayer):
 
     @torch.no_grad()
     def compact_forward(self, x):
-        """Convolution from packed weights as a GEMM over unfolded patches (output geometry of F.conv2d);
-        reference path: unfold + CUDA-core GEMM + fold [tmq/tmq.py:822-871]."""
+        """Convolution from packed weights with the output geometry of F.conv2d.  Channel counts that are a multiple of
+        64 run as an implicit GEMM (bf16, int8 or - exactly - fp32 activations); few-channel layers with bf16
+        activations run the fused stem kernel; depthwise layers their own kernel; the rest falls back to explicit
+        patches.  Reference path: unfold + CUDA-core GEMM + fold [tmq/tmq.py:822-871]."""
         assert not self.training, "Compact inference is not supported in training mode"
         assert self.weight.data.dtype == torch.int32, "Compact inference requires 32-bit integer words"
         _require_cuda(x, "compact_forward")
@@ -634,6 +641,67 @@ class Conv2d(nn.Module, TMQLayer):
             if self.post_scale_imm != 1.0:
                 scale = torch.full((c,), float(self.post_scale_imm), dtype=torch.float32, device=x.device)
             return ops.ternary_dwconv2d(x, self.weight.data, (ky, kx), (sy, sx), (py, px), (dy, dx), scale, self.bias)
+        if c != int(self.original_shape[1]):
+            raise RuntimeError("compact inference: channel count does not match the packed weights")
+        if c % 64 == 0 and x.dtype in (torch.bfloat16, torch.float32, torch.int8):
+            return self._implicit_forward(x, (ky, kx), (sy, sx), (py, px), (dy, dx))
+        if x.dtype == torch.bfloat16 and (dy, dx) == (1, 1):
+            y = self._few_channel_forward(x, (ky, kx), (sy, sx), (py, px))
+            if y is not None:
+                return y
+        return self._patch_forward(x, (ky, kx), (sy, sx), (py, px), (dy, dx))
+
+    def _epilogue_scale(self, n_out, device):
+        if self.post_scale_imm == 1.0:
+            return None
+        return torch.full((n_out,), float(self.post_scale_imm), dtype=torch.float32, device=device)
+
+    def _implicit_forward(self, x, kernel, stride, padding, dilation):
+        """Implicit GEMM on the tensor cores, no patch matrix.  The result is NHWC in memory and returned as the NCHW
+        view of it (torch's channels_last), which the next compact layer takes without a copy.
+        bf16 -> bf16; int8 -> exact int32 sums (no scale / bias); fp32 -> fp32 through the exact three-term split of
+        the activations along the channels (three stacked copies of the weights per filter tap)."""
+        b, c, h, w = x.shape
+        n_out = int(self.original_shape[0])
+        (ky, kx) = kernel
+        terms = 3 if x.dtype == torch.float32 else 1
+        fmt = ops.FMT_I8 if x.dtype == torch.int8 else ops.FMT_BF16
+        wt = self._cached_layout(("conv", fmt, terms), lambda: ops.prepack(
+            ops.conv_rows_kkc(self.weight.data, c, ky, kx, terms, pad_to=1), n_out, fmt))
+        nhwc = x.permute(0, 2, 3, 1)
+        if x.dtype == torch.float32:
+            if nhwc.is_contiguous():                       # channels_last fp32: split the pixel rows in place
+                xin = ops.split_f32(nhwc.reshape(b * h * w, c), 3, c).view(b, h, w, 3 * c)
+            else:
+                xin = ops.nchw_to_nhwc_bf16(x, 3)
+        else:
+            xin = nhwc if nhwc.is_contiguous() else nhwc.contiguous()
+        if x.dtype == torch.int8:
+            y = ops.ternary_conv2d_nhwc(xin, wt, n_out, kernel, stride, padding, dilation)
+        else:
+            y = ops.ternary_conv2d_nhwc(xin, wt, n_out, kernel, stride, padding, dilation,
+                                        self._epilogue_scale(n_out, x.device), self.bias,
+                                        out_dtype=torch.float32 if terms == 3 else torch.bfloat16)
+        return y.permute(0, 3, 1, 2)
+
+    def _few_channel_forward(self, x, kernel, stride, padding):
+        """Layers with few input channels (an image stem) and bf16 activations: the fused kernel that keeps the patches
+        on chip.  None when the geometry is outside that kernel's limits."""
+        b, c, h, w = x.shape
+        n_out = int(self.original_shape[0])
+        (ky, kx) = kernel
+        wt = self._cached_layout(("stem",), lambda: ops.prepack(
+            ops.conv_rows_kkc(self.weight.data, c, ky, kx, 1, pad_to=8), n_out, ops.FMT_BF16))
+        y = ops.ternary_conv2d_stem(x.float(), wt, n_out, kernel, stride, padding,
+                                    self._epilogue_scale(n_out, x.device), self.bias)
+        return None if y is None else y.permute(0, 3, 1, 2)
+
+    def _patch_forward(self, x, kernel, stride, padding, dilation):
+        """Fallback for what the kernels above do not take (channel counts that are no multiple of 64 with fp32 or int8
+        activations, dilated few-channel layers): explicit patches (torch's unfold) through the ternary GEMM, exact for
+        fp32 [the reference's only route, tmq/tmq.py:857-863]."""
+        b, c, h, w = x.shape
+        (ky, kx), (sy, sx), (py, px), (dy, dx) = kernel, stride, padding, dilation
         h_out = (h + 2 * py - dy * (ky - 1) - 1) // sy + 1
         w_out = (w + 2 * px - dx * (kx - 1) - 1) // sx + 1
         if ky == 1 and kx == 1 and py == 0 and px == 0:

@@ -82,19 +82,13 @@ class PackedConv:
         self.stride, self.padding = api._pair(layer.stride), api._pair(layer.padding)
         self.dilation = api._pair(layer.dilation)
         self.relu = relu
+        self.layer = layer
         self.scale, self.bias = _fold_bn(bn, getattr(layer, "bias", None), float(layer.post_scale_imm))
-        packed = layer.weight.data.view(-1, layer.weight.shape[-1])            # rows in (c, ky, kx) order
         # the implicit GEMM walks K as (ky, kx, c): channel runs are contiguous in NHWC
-        k = torch.arange(self.cin * self.ky * self.kx, device=packed.device)
-        c, rem = k // (self.ky * self.kx), k % (self.ky * self.kx)
-        self.perm_from_ckk = torch.argsort(rem * self.cin + c)                 # new row j <- old row perm[j]
-        self.packed_kkc = packed.index_select(0, self.perm_from_ckk).contiguous()
-        self.K = self.packed_kkc.shape[0]
+        self.K = self.cin * self.ky * self.kx
         self.implicit = (self.cin % 64 == 0)
-        kpad = (-self.K) % 8
-        p = torch.nn.functional.pad(self.packed_kkc, (0, 0, 0, kpad)) if kpad else self.packed_kkc
-        self.wt = ops.prepack(p, self.cout, ops.FMT_BF16)
-        self.kpad = kpad
+        self.wt = ops.prepack(ops.conv_rows_kkc(layer.weight.data, self.cin, self.ky, self.kx, 1, pad_to=8), self.cout,
+                              ops.FMT_BF16)
 
     def from_images(self, images, defer_relu=False):
         """Stem route: fp32 NCHW images -> bf16 NHWC feature map, patches built by a kernel (no torch glue).
@@ -140,14 +134,23 @@ class PackedResNet18:
         self.fc_wt = ops.prepack(packed, self.fc_n, ops.FMT_BF16)
 
     @torch.no_grad()
-    def __call__(self, images):
-        x = self.conv1.from_images(images.float(), defer_relu=True)                   # bf16 NHWC
-        x = ops.maxpool2d_nhwc(x, 3, 2, 1, relu=True)                                 # ReLU folded into the pooling
-        for c1, c2, down in self.blocks:
-            identity = x if down is None else down(x)
-            x = c2(c1(x), residual=identity)
-        pooled = x.float().mean(dim=(1, 2)).to(torch.bfloat16).contiguous()          # [B, 512]
-        return ops.ternary_gemm(pooled, self.fc_wt, self.fc_n, self.fc_scale, self.fc_bias, out_dtype=torch.float32)
+    def __call__(self, images, trace=None):
+        """trace(name, layer, input, residual, output), when given, sees every layer's actual operands (layerwise
+        checks); `layer` is the PackedConv, or None for the pooling layers and the classifier."""
+        def seen(name, layer, x_in, res, y):
+            if trace is not None:
+                trace(name, layer, x_in, res, y)
+            return y
+        images = images.float()
+        x = seen("conv1", self.conv1, images, None, self.conv1.from_images(images, defer_relu=True))   # bf16 NHWC
+        x = seen("maxpool", None, x, None, ops.maxpool2d_nhwc(x, 3, 2, 1, relu=True))   # ReLU folded into the pooling
+        for i, (c1, c2, down) in enumerate(self.blocks):
+            identity = x if down is None else seen(f"block{i}.down", down, x, None, down(x))
+            mid = seen(f"block{i}.conv1", c1, x, None, c1(x))
+            x = seen(f"block{i}.conv2", c2, mid, identity, c2(mid, residual=identity))
+        pooled = seen("avgpool", None, x, None, ops.avgpool_nhwc(x))                   # [B, 512] bf16, fp32 sums
+        return seen("fc", None, pooled, None, ops.ternary_gemm(pooled, self.fc_wt, self.fc_n, self.fc_scale,
+                                                               self.fc_bias, out_dtype=torch.float32))
 
 
 def shard_batch(x, rank=None, world_size=None):
