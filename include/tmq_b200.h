@@ -210,6 +210,16 @@ int tmq_ternary_gemv_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t
 int tmq_ternary_conv2d_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, const void *residual,
                             void *Y, int B, int H, int W, int C, int N, int ky, int kx, int sy, int sx, int py, int px,
                             int dy, int dx, int relu, int *status, void *stream);
+/* Unit-stride form with the input tile resident in shared memory for all filter taps ("shifted window"): one 4-D TMA
+ * copy per 64-channel slice brings a tile's input pixels (zero padding = the copy's out-of-bounds fill) and every
+ * tap's MMAs read that one copy through a descriptor shifted by the tap's offset; persistent CTAs, double-buffered
+ * accumulator.  Same operands and results as tmq_ternary_conv2d_bf16 with sy = sx = 1, except the K order of Wt:
+ * (64-channel slice, ky, kx, channel within the slice).  ky * kx <= 9; TMQ_ERR_UNSUPPORTED outside its limits.
+ * replaces: Conv2d.compact_forward for stride-1 layers, tmq/tmq.py:822-871. */
+int tmq_ternary_conv2d_s1_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias, const void *residual,
+                               void *Y, int B, int H, int W, int C, int N, int ky, int kx, int py, int px, int dy, int dx,
+                               int relu, int *status, void *stream);
+
 /* The same convolution with fp32 NHWC output (no output rounding; residual stays bf16), and with int8 activations:
  * X int8 NHWC, Wt = fmt-1 prepack of the (ky, kx, c)-ordered packed weight, Y int32 NHWC, exact.  The fp32-output form
  * is also how fp32 activations are convolved exactly: split them into three bf16 terms along the channels
@@ -223,7 +233,7 @@ int tmq_ternary_conv2d_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int B
 
 /* Activation layout helpers of the packed inference path (replace the eager tensor glue between compact layers,
  * tmq/tmq.py:857-863): fp32 rows [M][K] -> bf16 [M][terms*Kp] (terms = 1: rounded; terms = 3: the exact split
- * x = hi + mid + lo, term t at column t*Kp + k; columns K..Kp-1 zero); fp32 NCHW -> bf16 NHWC [B][H][W][terms*C];
+ * x = lo + mid + hi, smallest term first, term t at column t*Kp + k; columns K..Kp-1 zero); fp32 NCHW -> bf16 NHWC [B][H][W][terms*C];
  * global average pooling of bf16 NHWC [B][P][C] -> bf16 [B][C] (fp32 sum, C even). */
 int tmq_split_f32_bf16(const float *X, void *out, int64_t M, int64_t K, int64_t Kp, int terms, void *stream);
 int tmq_nchw_f32_to_nhwc_bf16(const float *X, void *Y, int B, int C, int H, int W, int terms, void *stream);
@@ -244,6 +254,18 @@ int tmq_conv_patches_bf16(const float *X, void *A, int B, int C, int H, int W, i
 int tmq_ternary_conv2d_stem_bf16(const float *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int B,
                                  int C, int H, int W, int N, int ky, int kx, int sy, int sx, int py, int px, int k_rows,
                                  int relu, int *status, void *stream);
+
+/* The same layer class with the patches read by descriptor instead of being assembled: the input rows an output row
+ * touches are kept in shared memory as bf16 [row][pixel][CP channels], CP = 8 / sx channel slots per pixel (sx = 2: up to
+ * 4 channels, sx = 1: up to 8), which puts the patch rows of neighbouring output pixels 16 bytes apart - the row pitch of
+ * the tensor core's unswizzled operand layout - so every MMA reads its operand straight from that window.  Wt = fmt-0
+ * prepack of the packed weights with K ordered (ky, [kx, CP] zero-padded to a multiple of 16): tmq_stem_rows_k rows
+ * (0 = layer not covered).  Limits: OW <= 128, N <= 128, N % 8 == 0, ky * ceil(kx * CP / 16) <= 16; TMQ_ERR_UNSUPPORTED
+ * beyond (then: tmq_ternary_conv2d_stem_bf16).  replaces: Conv2d.compact_forward for such layers, tmq/tmq.py:822-871. */
+int tmq_stem_rows_k(int C, int ky, int kx, int sx);
+int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y,
+                                      int B, int C, int H, int W, int N, int ky, int kx, int sy, int sx, int py, int px,
+                                      int relu, int *status, void *stream);
 
 /* Max pooling between packed layers: X bf16 NHWC [B][H][W][C] (C % 8 == 0) -> Y [B][OH][OW][C], square window k, stride s,
  * padding p (positions outside the image are ignored), OH = (H + 2p - k) / s + 1; relu != 0 applies max(0, .) as well

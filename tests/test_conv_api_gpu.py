@@ -136,15 +136,16 @@ def test_layout_kernels(ops):
     x[0, :4] = torch.tensor([0.0, -0.0, 1.0, 3.0e38])
     s = ops.split_f32(x.cuda(), 3, 56)
     assert s.shape == (37, 168)
-    hi, mid, lo = s[:, :50].float(), s[:, 56:106].float(), s[:, 112:162].float()
+    lo, mid, hi = s[:, :50].float(), s[:, 56:106].float(), s[:, 112:162].float()
     assert torch.equal(hi + mid + lo, x.cuda())                                   # three bf16 terms rebuild the fp32 value
+    assert torch.equal(hi, x.cuda().to(torch.bfloat16).float())                   # smallest term first, leading term last
     assert float(s[:, 50:56].abs().max()) == 0.0 and float(s[:, 162:].abs().max()) == 0.0
     assert torch.equal(ops.split_f32(x.cuda(), 1), x.cuda().to(torch.bfloat16))
     img = torch.randn(3, 70, 9, 5, generator=gen).cuda()
     assert torch.equal(ops.nchw_to_nhwc_bf16(img), img.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous())
     t3 = ops.nchw_to_nhwc_bf16(img, 3)
     assert t3.shape == (3, 9, 5, 210)
-    assert torch.equal(t3[..., :70].float() + t3[..., 70:140].float() + t3[..., 140:].float(), img.permute(0, 2, 3, 1))
+    assert torch.equal(t3[..., 140:].float() + t3[..., 70:140].float() + t3[..., :70].float(), img.permute(0, 2, 3, 1))
     f = torch.randn(4, 7, 7, 512, generator=gen).to(torch.bfloat16).cuda()
     want = f.double().mean(dim=(1, 2))
     got = ops.avgpool_nhwc(f).double()

@@ -47,6 +47,96 @@ def test_implicit_conv_matches_conv2d(ops, case):
     _conv_case(ops, b, c, h, w, n, k, s, p, d, relu, seed=sum(case[:9]))
 
 
+S1_CASES = [
+    # b, c, h, w, n, (ky, kx), (py, px), (dy, dx), relu, residual
+    (3, 64, 56, 56, 64, (3, 3), (1, 1), (1, 1), True, True),        # two output rows per tile
+    (2, 128, 28, 28, 128, (3, 3), (1, 1), (1, 1), True, False),
+    (2, 256, 14, 14, 256, (3, 3), (1, 1), (1, 1), False, True),     # two channel tiles, two row tiles per image
+    (5, 512, 7, 7, 512, (3, 3), (1, 1), (1, 1), True, True),        # two images side by side in one tile, odd image count
+    (1, 64, 7, 7, 72, (3, 3), (1, 1), (1, 1), False, False),        # a single small image, ragged channel count
+    (2, 64, 13, 9, 200, (3, 3), (0, 0), (1, 1), False, False),      # no padding
+    (2, 64, 11, 150, 64, (3, 3), (1, 1), (1, 1), True, False),      # rows wider than a tile: column pieces
+    (2, 64, 20, 20, 64, (3, 3), (2, 2), (2, 2), False, False),      # dilation 2
+    (3, 128, 9, 12, 64, (1, 1), (0, 0), (1, 1), True, True),        # 1 x 1
+    (2, 64, 10, 17, 96, (3, 1), (1, 0), (1, 1), False, False),      # 3 x 1 kernel, asymmetric padding
+    (2, 64, 12, 12, 64, (2, 2), (1, 0), (1, 1), False, False),      # even kernel: output larger / smaller than the input
+]
+
+
+@pytest.mark.parametrize("case", S1_CASES)
+def test_shifted_window_conv_matches_conv2d(ops, case):
+    b, c, h, w, n, (ky, kx), (py, px), (dy, dx), relu, with_res = case
+    gen = torch.Generator().manual_seed(b * 1000 + c + h * 7 + w + n)
+    x = torch.randn(b, c, h, w, generator=gen).to(torch.bfloat16)
+    wgt = torch.randint(-1, 2, (n, c, ky, kx), generator=gen).float()
+    scale = torch.rand(n, generator=gen) * 0.09 + 0.01
+    bias = torch.randn(n, generator=gen)
+    ref = nn.functional.conv2d(x.double(), wgt.double(), None, 1, (py, px), (dy, dx)) * scale.double().view(1, -1, 1, 1) \
+        + bias.double().view(1, -1, 1, 1)
+    res = None
+    if with_res:
+        res = torch.randn(ref.shape, generator=gen).to(torch.bfloat16)
+        ref = ref + res.double()
+    if relu:
+        ref = torch.relu(ref)
+    packed = ops.compactify_ternary(wgt.cuda())
+    wt = ops.prepack(ops.conv_rows_skkc(packed, c, ky, kx), n, ops.FMT_BF16)
+    y = ops.ternary_conv2d_s1(x.cuda().permute(0, 2, 3, 1).contiguous(), wt, n, (ky, kx), (py, px), (dy, dx), scale.cuda(),
+                              bias.cuda(), relu=relu,
+                              residual=None if res is None else res.cuda().permute(0, 2, 3, 1).contiguous())
+    ops.check_gemm_status()
+    assert y is not None
+    got = y.permute(0, 3, 1, 2).double().cpu()
+    assert got.shape == ref.shape
+    tol = 2.0 ** -7 * ref.abs() + 1e-4 * ref.abs().max()
+    bad = (got - ref).abs() > tol
+    assert not bool(bad.any()), (int(bad.sum()), float((got - ref).abs().max()))
+    # the gather kernel computes the same sums in the same precision: the two agree to the last bf16 bit almost everywhere
+    wt2 = ops.prepack(ops.conv_rows_kkc(packed, c, ky, kx), n, ops.FMT_BF16)
+    y2 = ops.ternary_conv2d_nhwc(x.cuda().permute(0, 2, 3, 1).contiguous(), wt2, n, (ky, kx), (1, 1), (py, px), (dy, dx),
+                                 scale.cuda(), bias.cuda(), relu=relu,
+                                 residual=None if res is None else res.cuda().permute(0, 2, 3, 1).contiguous())
+    assert float((y.float() != y2.float()).float().mean()) < 1e-3
+
+
+STEM_CASES = [
+    # b, c, h, w, n, (ky, kx), (sy, sx), (py, px), relu
+    (2, 3, 224, 224, 64, (7, 7), (2, 2), (3, 3), False),        # the ResNet stem
+    (3, 3, 64, 64, 64, (7, 7), (2, 2), (3, 3), True),
+    (2, 1, 30, 40, 32, (3, 3), (2, 2), (1, 1), False),          # one channel
+    (2, 4, 33, 31, 64, (5, 5), (2, 2), (2, 2), True),           # all four channel slots used, odd sizes
+    (2, 3, 21, 50, 72, (3, 5), (1, 2), (0, 2), False),          # vertical stride 1, ragged channel count
+    (2, 8, 20, 24, 64, (3, 3), (1, 1), (1, 1), True),           # horizontal stride 1: eight channel slots
+    (1, 5, 17, 19, 128, (3, 3), (2, 1), (1, 1), False),
+]
+
+
+@pytest.mark.parametrize("case", STEM_CASES)
+def test_descriptor_patch_stem_matches_conv2d(ops, case):
+    b, c, h, w, n, (ky, kx), (sy, sx), (py, px), relu = case
+    gen = torch.Generator().manual_seed(b + 10 * c + h + w + n)
+    x = torch.randn(b, c, h, w, generator=gen)
+    wgt = torch.randint(-1, 2, (n, c, ky, kx), generator=gen).float()
+    scale = torch.rand(n, generator=gen) * 0.09 + 0.01
+    bias = torch.randn(n, generator=gen)
+    ref = nn.functional.conv2d(x.to(torch.bfloat16).double(), wgt.double(), None, (sy, sx), (py, px)) \
+        * scale.double().view(1, -1, 1, 1) + bias.double().view(1, -1, 1, 1)
+    if relu:
+        ref = torch.relu(ref)
+    packed = ops.compactify_ternary(wgt.cuda())
+    rows = ops.conv_rows_stem(packed, c, ky, kx, sx)
+    assert rows is not None
+    y = ops.ternary_conv2d_stem_rows(x.cuda(), ops.prepack(rows, n, ops.FMT_BF16), n, (ky, kx), (sy, sx), (py, px),
+                                     scale.cuda(), bias.cuda(), relu=relu)
+    ops.check_gemm_status()
+    assert y is not None
+    got = y.permute(0, 3, 1, 2).double().cpu()
+    assert got.shape == ref.shape
+    tol = 2.0 ** -7 * ref.abs() + 1e-4 * ref.abs().max()
+    bad = (got - ref).abs() > tol
+    assert not bool(bad.any()), (int(bad.sum()), float((got - ref).abs().max()))
+
+
 def test_residual_fusion_and_patch_kernel(ops):
     gen = torch.Generator().manual_seed(77)
     # residual + ReLU inside the epilogue equals conv, then add, then ReLU

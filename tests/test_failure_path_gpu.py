@@ -38,12 +38,12 @@ def test_a_wait_that_nothing_completes_gives_up_and_reports(ops):
     torch.cuda.synchronize()
     assert time.perf_counter() - t0 < 1.0                # returned promptly; the context is still usable
     assert int(status.item()) == TIMEOUT
-    assert budget < int(waited.item()) < 50 * budget
-    # a second waiter that finds the word already set leaves early instead of spending its own budget
+    assert budget < int(waited.item()) < 100 * budget   # the clock is read every 1024 polls of the barrier
+    # a second waiter that finds the word already set leaves early instead of spending its own budget (~2 s)
     waited.zero_()
     assert L.tmq_selftest_wait_timeout(4_000_000_000, status.data_ptr(), waited.data_ptr(), _stream()) == 0
     torch.cuda.synchronize()
-    assert 0 < int(waited.item()) < 1_000_000
+    assert 0 < int(waited.item()) < 200_000_000
     # bad arguments are refused on the host
     assert L.tmq_selftest_wait_timeout(0, status.data_ptr(), None, _stream()) == -1
     assert L.tmq_selftest_wait_timeout(1000, None, None, _stream()) == -1

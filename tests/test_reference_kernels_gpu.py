@@ -71,10 +71,12 @@ def test_reference_gemm_pins_the_oracle_and_matches_the_library(ref, ops, M, N, 
     ops.check_gemm_status()
     exact = T.gemm_f64_fast(X.numpy(), P, N)
     rms = np.sqrt((exact ** 2).mean())
-    # both are fp32 accumulations of exact products in different orders
-    assert np.abs(y_ref - exact).max() <= 2e-5 * rms
-    assert np.abs(ours - exact).max() <= 2e-5 * rms
-    assert np.abs(ours - y_ref).max() <= 4e-5 * rms
+    # both are fp32 accumulations of exact products, in different orders; the tensor core's accumulator drops the bits
+    # of a product that lie below its running sum instead of rounding, hence the wider band for the library
+    err_ref, err_ours = np.abs(y_ref - exact).max() / rms, np.abs(ours - exact).max() / rms
+    assert err_ref <= 2e-5, err_ref
+    assert err_ours <= 1e-4, err_ours
+    assert np.abs(ours - y_ref).max() <= 1.2e-4 * rms
     # batched forms of the reference signature: [B, M, K] and [1, B, M, K]
     if M == 64 and K == 256:
         Xb = torch.randn(3, M, K, generator=gen)
@@ -82,7 +84,7 @@ def test_reference_gemm_pins_the_oracle_and_matches_the_library(ref, ops, M, N, 
         ob = ops.ternary_mmm_cuda(Xb.cuda(), Pd, N).cpu().numpy()
         assert yb.shape == ob.shape == (3, M, N)
         assert np.array_equal(yb.reshape(-1, N).view(np.uint32), T.gemm_f32_seq(Xb.numpy().reshape(-1, K), P, N).view(np.uint32))
-        assert np.abs(ob - yb).max() <= 4e-5 * rms
+        assert np.abs(ob - yb).max() <= 1.2e-4 * rms
         y4 = ref.ternary_mmm_cuda(Xb.cuda().unsqueeze(0), Pd, N)
         o4 = ops.ternary_mmm_cuda(Xb.cuda().unsqueeze(0), Pd, N)
         assert tuple(y4.shape) == tuple(o4.shape) == (1, 3, M, N)
@@ -103,7 +105,7 @@ def test_reference_gemv_and_the_library_agree_with_the_exact_result(ref, ops, N,
     exact = T.gemm_f64_fast(x.numpy()[None, :], P, N)[0]
     rms = np.sqrt((exact ** 2).mean())
     assert np.abs(y_ref.cpu().numpy() - exact).max() <= 2e-5 * rms
-    assert np.abs(ours.cpu().numpy() - exact).max() <= 2e-5 * rms
+    assert np.abs(ours.cpu().numpy() - exact).max() <= 1e-4 * rms
     # the other activation ranks of the reference signature keep their shape
     for shape in ((1, K), (1, 1, K), (1, 1, 1, K)):
         a = ref.ternary_mvm_cuda(x.cuda().view(shape), Pd, N)

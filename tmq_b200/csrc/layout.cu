@@ -5,7 +5,10 @@
 //     lo = bf16(x - hi - mid) is EXACT for every finite fp32 x whose low term is not subnormal in bf16 (8 + 8 + 8
 //     significant bits), so a product with a weight in {-1, 0, +1} is exact per term and the tensor core's fp32
 //     accumulation reproduces an fp32 GEMM / convolution.  The three terms ride along K (GEMM: [M][3*Kp]) or along the
-//     channels (convolution: NHWC [B][H][W][3*C]) against three stacked copies of the weights.
+//     channels (convolution: NHWC [B][H][W][3*C]) against three stacked copies of the weights, SMALLEST TERM FIRST
+//     (lo, mid, hi): the tensor core aligns every product to its running fp32 sum and drops the bits below it, so the
+//     tiny terms are added while the sum is still tiny (measured at K = 4096: relative error 6e-5 with the large terms
+//     first, fp32-GEMM level with them last).
 //   * NCHW fp32 -> NHWC bf16 (one or three terms) in one pass, for convolutions fed with torch's default layout.
 //   * global average pooling on NHWC bf16.
 #include <cuda_bf16.h>
@@ -34,9 +37,9 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict
     } else {
         __nv_bfloat16 hi, mid, lo;
         split3(x, hi, mid, lo);
-        o[0] = hi;
+        o[0] = lo;                 // smallest term first: see the note on the accumulation order above
         o[Kp] = mid;
-        o[2 * Kp] = lo;
+        o[2 * Kp] = hi;
     }
 }
 
@@ -68,9 +71,9 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float *__restri
             } else {
                 __nv_bfloat16 hi, mid, lo;
                 split3(x, hi, mid, lo);
-                o[0] = hi;
+                o[0] = lo;
                 o[C] = mid;
-                o[2 * C] = lo;
+                o[2 * C] = hi;
             }
         }
     }

@@ -91,6 +91,7 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
     const long long n0 = (long long)blockIdx.x * 128;
     const long long m0 = (long long)blockIdx.y * BN;
     const int ntaps = args.ky * args.kx;
+    const int cpb = args.C / 64;                           // bf16: k-blocks per filter tap
     const int nkb = (ntaps * args.C * ESZ + 127) / 128;   // C % 64 == 0: only int8 can end on half a k-block
     constexpr uint32_t A_COLS = 32;                                   // one k-block of a weight row: 64 bf16
     constexpr uint32_t TMEM_NEED = BN + kConvStages * A_COLS;         // accumulator, then the ring of decoded weight tiles
@@ -278,9 +279,16 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
             if (!ok) break;
             // this thread's 16-byte chunk of the k-block: which filter tap and which channels (with 64-channel int8
             // layers a k-block spans two taps, so the tap is a per-chunk matter; past the last tap: zeros)
-            const int e0 = (kb * 128 + chunk * 16) / ESZ;
-            const int tap = e0 / args.C, c0 = e0 - tap * args.C;
-            const bool tap_ok = tap < ntaps;
+            int tap, c0;
+            if (KIND == CONV_BF16) {          // 64 channels per k-block: one tap for the whole k-block
+                tap = kb / cpb;
+                c0 = (kb - tap * cpb) * 64 + chunk * 8;
+            } else {
+                const int e0 = kb * 128 + chunk * 16;
+                tap = e0 / args.C;
+                c0 = e0 - tap * args.C;
+            }
+            const bool tap_ok = KIND == CONV_BF16 || tap < ntaps;
             const int fy = (tap / args.kx) * args.dy, fx = (tap % args.kx) * args.dx;
             const uint32_t bbase = ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES);
             const int delta = (fy * args.W + fx) * args.C + c0;   // the chunk's distance from tap (0, 0), channel 0

@@ -1,0 +1,759 @@
+// Stride-1 ternary Conv2d from 2-bit packed weights as a SHIFTED-WINDOW implicit GEMM on tcgen05, and the few-channel
+// stem whose patches are read by descriptor.
+//
+// The gather-based implicit GEMM (ternary_conv.cu) fetches every input pixel once per filter tap.  For unit stride the
+// patch rows of neighbouring output pixels are neighbouring input pixels, so the input never has to be rearranged at all:
+//
+//   * a tile is R output rows x Wt output columns of one image.  ONE 4-D TMA copy brings the (R + halo) x (Wt + halo)
+//     input pixels of a 64-channel slice into shared memory as consecutive 128-byte rows (128-byte swizzle), with the
+//     convolution's zero padding produced by the copy's out-of-bounds fill;
+//   * output position n = r * Wp + j of the tile (Wp = Wt + halo: the positions j >= Wt of each row are computed and
+//     thrown away) reads, for filter tap (fy, fx), the shared-memory row n + fy * Wp + fx.  The B operand of the MMAs of
+//     that tap is therefore the SAME shared-memory tile with its descriptor's start address moved by fy * Wp + fx rows
+//     (the swizzle is a function of the address, so a start in the middle of a 1024-byte swizzle atom reads correctly,
+//     and measured no slower than an aligned one): ky * kx taps reuse one copy, and the load/store units never touch the
+//     activations;
+//   * weights are the 128-row A operand, decoded from TMA-loaded packed words into TENSOR memory exactly as in the tiled
+//     GEMM (ternary_gemm.cu); their K order is (64-channel slice, ky, kx, channel) so that the words of all taps of a slice
+//     are one contiguous run per output channel = one TMA copy per slice;
+//   * persistent CTAs, two per SM (see the note above the kernel), each with one 128-column accumulator and a four-stage
+//     ring of decoded weight k-blocks in its 256 tensor-memory columns; the epilogue (folded BatchNorm scale / bias,
+//     residual, ReLU, NHWC bf16 stores) of one CTA runs under the multiplications of the other;
+//   * small images (Wp * R well below 128 positions) put several sub-tiles - different images - side by side in the 128
+//     accumulator columns, each with its own input copy; the decoded weights serve all of them.
+//
+// Limits: unit stride, C % 64 == 0, ky * kx <= 9, (Wt + halo) <= 128 positions per row piece (wider rows are cut into
+// column pieces).  Everything else (strides, int8, fp32 output) stays with ternary_conv.cu.  All mbarrier waits are bounded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "decode.cuh"
+#include "epilogue.cuh"
+#include "ptx.cuh"
+#include "tma_host.cuh"
+
+namespace tmq {
+
+constexpr int kSwThreads = 320;   // warp 0: TMA, warp 1: MMA, warps 2-5: decode, warps 6-9: epilogue
+constexpr int kSwBN = 128;        // accumulator columns (output positions) per tile
+constexpr int kSwAStages = 4;     // decoded weight k-blocks in tensor memory (32 columns each)
+constexpr int kSwMaxTaps = 9;     // ky * kx
+constexpr int kSwMaxSub = 4;      // sub-tiles per tile
+
+#ifdef TMQ_SW_TRACE
+// development build only: time stamps (ns) of CTA 0's pipeline events, row = k-block / slice / tile counter
+__device__ unsigned long long g_sw_trace[512][8];
+__device__ __forceinline__ unsigned long long sw_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define SW_TRACE(row, col) do { if (blockIdx.x == 0 && (row) < 512) g_sw_trace[(row)][(col)] = sw_now(); } while (0)
+#else
+#define SW_TRACE(row, col) do { } while (0)
+#endif
+
+struct SwArgs {
+    const float *scale, *bias;
+    const __nv_bfloat16 *residual;
+    __nv_bfloat16 *Y;
+    int B, H, W, C, OH, OW, N;            // N = output channels
+    int ky, kx, py, px, dy, dx;
+    int R, Wt, Wp, Rin;                    // tile rows / columns, shared-memory row pitch (positions), input rows per tile
+    int nsub;                              // sub-tiles per tile (1, 2 or 4), each with kSwBN / nsub accumulator columns
+    int col_pieces, row_tiles;             // pieces per output row, tiles per image column piece
+    long long subtiles;                    // B * row_tiles * col_pieces
+    long long tiles_p;                     // ceil(subtiles / nsub)
+    int tiles_n;                           // ceil(N / 128)
+    int region_rows;                       // 128-byte rows reserved per sub-tile region in a stage
+    int in_stages, raw_stages;
+    int relu;
+    int *status;
+};
+
+// dynamic shared memory: [epilogue staging 4 x 2 KB][position -> pixel table 128 ints + tap shifts][regions][raw words][barriers]
+struct SwSmem {
+    int stage_off, lut_off, in_off, raw_off, bar_off, total;
+    int in_stage_bytes, raw_stage_bytes;
+};
+
+__host__ __device__ inline SwSmem sw_smem(int region_rows, int nsub, int in_stages, int ntaps, int raw_stages) {
+    SwSmem s;
+    s.stage_off = 0;
+    s.lut_off = 4 * 2048;
+    s.in_off = s.lut_off + 1024;                                  // 1024-aligned as long as the base is
+    s.in_stage_bytes = ((region_rows * nsub * 128) + 1023) / 1024 * 1024;
+    s.raw_off = s.in_off + in_stages * s.in_stage_bytes;
+    s.raw_stage_bytes = ntaps * 128 * 16;                          // 16 packed bytes per row and k-block
+    s.bar_off = s.raw_off + raw_stages * s.raw_stage_bytes;
+    s.total = s.bar_off + 256 + 1024;
+    return s;
+}
+
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int c, int w, int h, int b) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(ptx::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(ptx::smem_u32(bar)), "r"(c), "r"(w), "r"(h),
+          "r"(b)
+        : "memory");
+}
+
+// decomposition of a sub-tile index into (image, first output row, first output column)
+__device__ __forceinline__ void sw_subtile(const SwArgs &a, long long st, int &b, int &oy0, int &ox0) {
+    const int per_img = a.row_tiles * a.col_pieces;
+    b = (int)(st / per_img);
+    const int rem = (int)(st - (long long)b * per_img);
+    oy0 = (rem / a.col_pieces) * a.R;
+    ox0 = (rem % a.col_pieces) * a.Wt;
+}
+
+// Two CTAs share an SM (256 tensor-memory columns and at most ~110 KB of shared memory each).  A single thread per CTA
+// issues the MMAs and needs several hundred cycles of its own instructions per k-block - more than the tensor core needs
+// for the k-block's four 128 x 128 x 16 MMAs - so one CTA alone cannot keep the tensor core busy; the second CTA's issue
+// thread fills the gaps, and one CTA's epilogue runs under the other's multiplications.  The issue loop is kept small on
+// purpose: unrolled over the filter taps it measured TWICE as slow (the lone issuing warp then misses the instruction
+// cache on every pass).
+__global__ void __launch_bounds__(kSwThreads, 2)
+ternary_conv_sw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const SwArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int ntaps = args.ky * args.kx;
+    const SwSmem L = sw_smem(args.region_rows, args.nsub, args.in_stages, ntaps, args.raw_stages);
+    uint64_t *full_in = reinterpret_cast<uint64_t *>(smem + L.bar_off);       // [in_stages]  input regions landed
+    uint64_t *empty_in = full_in + 4;                                          // [in_stages]  MMAs done reading them
+    uint64_t *full_raw = empty_in + 4;                                         // [raw_stages] packed words landed
+    uint64_t *empty_raw = full_raw + 4;                                        // [raw_stages] 4 decode warps done with them
+    uint64_t *full_a = empty_raw + 4;                                          // [kSwAStages] decoded k-block in tensor memory
+    uint64_t *empty_a = full_a + kSwAStages;                                   // [kSwAStages] MMAs done reading it
+    uint64_t *acc_full = empty_a + kSwAStages;
+    uint64_t *acc_empty = acc_full + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
+    int *lut = reinterpret_cast<int *>(smem + L.lut_off);                      // [128] output pixel of a position, -1 = none
+    int *shtab = lut + 128;                                                    // [ntaps] row shift of a filter tap
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nslices = args.C / 64;
+    const long long ntiles = args.tiles_p * args.tiles_n;
+    const int nsubcols = kSwBN / args.nsub;
+    constexpr uint32_t TMEM_COLS = 256;                                        // 128 accumulator + 4 x 32 weight ring
+    constexpr uint32_t A_BASE = kSwBN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 4; s++) {
+            ptx::mbar_init(full_in + s, 1);
+            ptx::mbar_init(empty_in + s, 1);
+            ptx::mbar_init(full_raw + s, 1);
+            ptx::mbar_init(empty_raw + s, 4);
+        }
+        for (int s = 0; s < kSwAStages; s++) {
+            ptx::mbar_init(full_a + s, 4);     // one arrival per decode warp
+            ptx::mbar_init(empty_a + s, 1);
+        }
+        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_empty, 4);
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_x);
+        ptx::prefetch_tensormap(&tmap_w);
+    }
+    if (threadIdx.x < ntaps) shtab[threadIdx.x] = (threadIdx.x / args.kx) * args.dy * args.Wp + (threadIdx.x % args.kx) * args.dx;
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const bool healthy = (*reinterpret_cast<volatile int *>(args.status) == 0);
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA: input regions and packed words per slice
+        if (lane == 0 && healthy) {
+            int si = 0, sr = 0;
+            uint32_t in_phase = 1, raw_phase = 1;                              // producer side: first pass over a stage is free
+            bool ok = true;
+            const uint32_t in_bytes = (uint32_t)(args.Rin * args.Wp * 128);
+            for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int n0 = (int)(tile % args.tiles_n) * 128;
+                const long long st0 = (tile / args.tiles_n) * args.nsub;
+                int bb[kSwMaxSub], oy[kSwMaxSub], ox[kSwMaxSub];
+                for (int g = 0; g < args.nsub; g++) sw_subtile(args, st0 + g, bb[g], oy[g], ox[g]);   // past the end: zeros
+                for (int sl = 0; sl < nslices; sl++) {
+                    ok = ptx::mbar_wait(empty_in + si, in_phase, args.status);
+                    if (!ok) break;
+                    SW_TRACE(sl, 0);
+                    ptx::mbar_arrive_expect_tx(full_in + si, in_bytes * (uint32_t)args.nsub);
+                    for (int g = 0; g < args.nsub; g++)
+                        tma_load_4d(smem + L.in_off + si * L.in_stage_bytes + g * args.region_rows * 128, &tmap_x, full_in + si,
+                                    sl * 64, ox[g] - args.px, oy[g] - args.py, bb[g]);
+                    ok = ptx::mbar_wait(empty_raw + sr, raw_phase, args.status);
+                    if (!ok) break;
+                    ptx::mbar_arrive_expect_tx(full_raw + sr, (uint32_t)L.raw_stage_bytes);
+                    ptx::tma_load_2d(smem + L.raw_off + sr * L.raw_stage_bytes, &tmap_w, full_raw + sr, sl * ntaps * 4, n0);
+                    if (++si == args.in_stages) { si = 0; in_phase ^= 1u; }
+                    if (++sr == args.raw_stages) { sr = 0; raw_phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (one thread; keep this loop small)
+        if (lane == 0 && healthy) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(nsubcols >> 3) << 17) | ((128u >> 4) << 24);
+            const uint32_t sub_units = (uint32_t)(args.region_rows * 8);       // next sub-tile's region, in 16-byte units
+            int si = 0, sa = 0, ka = 0;
+            uint32_t in_phase = 0, a_phase = 0, acc_phase = 1;
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                ok = ptx::mbar_wait(acc_empty, acc_phase, args.status);        // the epilogue has drained the accumulator
+                if (!ok) break;
+                acc_phase ^= 1u;
+                ptx::tc_fence_after_sync();
+                uint32_t accum = 0u;
+                for (int sl = 0; sl < nslices && ok; sl++) {
+                    ok = ptx::mbar_wait(full_in + si, in_phase, args.status);
+                    if (!ok) break;
+                    SW_TRACE(sl, 1);
+                    const uint64_t in_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L.in_off + si * L.in_stage_bytes));
+#pragma unroll 1
+                    for (int tap = 0; tap < ntaps; tap++, ka++) {
+                        ok = ptx::mbar_wait(full_a + sa, a_phase, args.status);
+                        if (!ok) break;
+                        SW_TRACE(ka, 4);
+                        ptx::tc_fence_after_sync();
+                        const uint32_t a_tmem = tmem_base + A_BASE + (uint32_t)sa * 32u;
+                        uint64_t b_desc = in_desc + (uint32_t)(shtab[tap] * 8);    // the tap's row shift, in 16-byte units
+                        uint32_t d_tmem = tmem_base;
+                        for (int g = 0; g < args.nsub; g++, b_desc += sub_units, d_tmem += (uint32_t)nsubcols) {
+#pragma unroll
+                            for (int k4 = 0; k4 < 4; k4++)
+                                ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (accum | (uint32_t)k4) ? 1u : 0u);
+                        }
+                        accum = 1u;
+                        ptx::umma_commit(empty_a + sa);
+                        SW_TRACE(ka, 5);
+                        sa = (sa + 1) & (kSwAStages - 1);
+                        a_phase ^= (sa == 0) ? 1u : 0u;
+                    }
+                    if (ok) ptx::umma_commit(empty_in + si);                   // every tap of the slice has read the region
+                    if (++si == args.in_stages) { si = 0; in_phase ^= 1u; }
+                }
+                if (ok) ptx::umma_commit(acc_full);
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- decode warps 2..5: one tensor-memory lane quarter each
+        const int row = (warp & 3) * 32 + lane;
+        bool ok = healthy;
+        int sr = 0, sa = 0;
+        uint32_t raw_phase = 0, a_phase = 1;
+        int ka = 0;
+        for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            for (int sl = 0; sl < nslices && ok; sl++) {
+                ok = ptx::mbar_wait(full_raw + sr, raw_phase, args.status);
+                if (!ok) break;
+                const uint8_t *raw = smem + L.raw_off + sr * L.raw_stage_bytes + row * (ntaps * 16);
+#pragma unroll 1
+                for (int tap = 0; tap < ntaps; tap++, ka++) {
+                    ok = ptx::mbar_wait(empty_a + sa, a_phase, args.status);
+                    if (!ok) break;
+                    if (warp == 2 && lane == 0) SW_TRACE(ka, 2);
+                    const uint4 p = *reinterpret_cast<const uint4 *>(raw + tap * 16);
+                    const uint32_t words[4] = {p.x, p.y, p.z, p.w};
+                    uint32_t cols[32];
+#pragma unroll
+                    for (int wi = 0; wi < 4; wi++) {
+                        uint32_t r[8];
+                        decode_word_bf16(words[wi], r);
+#pragma unroll
+                        for (int j = 0; j < 8; j++) cols[8 * wi + j] = r[j];
+                    }
+                    ptx::tmem_st_x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + A_BASE + (uint32_t)sa * 32u, cols);
+                    ptx::tmem_st_wait();
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(full_a + sa);
+                    if (warp == 2 && lane == 0) SW_TRACE(ka, 3);
+                    sa = (sa + 1) & (kSwAStages - 1);
+                    a_phase ^= (sa == 0) ? 1u : 0u;
+                }
+                __syncwarp();
+                if (lane == 0 && ok) ptx::mbar_arrive(empty_raw + sr);         // this warp has read its words of the slice
+                if (++sr == args.raw_stages) { sr = 0; raw_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue warps 6..9
+        // The residual values of the first half of the tile are requested BEFORE the accumulator is waited for, those of
+        // the second half while the first is being written, so their latency hides under work already in flight.
+        const int quarter = warp & 3;
+        float *stage = reinterpret_cast<float *>(smem + L.stage_off) + (warp - 6) * 512;
+        const int et = threadIdx.x - 192;                                      // 0..127
+        bool ok = healthy;
+        uint32_t acc_phase = 0;
+        int ti = 0;
+        for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ti++) {
+            const long long n0 = (tile % args.tiles_n) * 128;
+            const long long st0 = (tile / args.tiles_n) * args.nsub;
+            {   // position -> output pixel index of this tile (one position per epilogue thread)
+                const int g = et / nsubcols, pos = et - g * nsubcols;
+                int b, oy0, ox0;
+                sw_subtile(args, st0 + g, b, oy0, ox0);
+                const int r = pos / args.Wp, j = pos - r * args.Wp;
+                const int oy = oy0 + r, ox = ox0 + j;
+                const bool valid = (st0 + g) < args.subtiles && r < args.R && j < args.Wt && oy < args.OH && ox < args.OW;
+                lut[et] = valid ? ((b * args.OH + oy) * args.OW + ox) : -1;
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");                     // the four epilogue warps: table complete
+            const long long n = n0 + quarter * 32 + lane;
+            float sc = 0.5f, bi = 0.0f;                                        // operands carried +-2.0
+            if (n < args.N) {
+                if (args.scale) sc *= args.scale[n];
+                if (args.bias) bi = args.bias[n];
+            }
+            const int cg = (lane & 3) * 8;
+            const long long nv = n0 + quarter * 32 + cg;                       // first channel of this lane's 8-channel vector
+            const bool vec_ok = ((args.N & 7) == 0) && (nv + 8 <= args.N) && ((reinterpret_cast<uintptr_t>(args.Y) & 15) == 0) &&
+                                ((reinterpret_cast<uintptr_t>(args.residual) & 15) == 0);
+            const bool pre = args.residual != nullptr && vec_ok;
+            uint4 rv[8];                                                       // residual vectors, four chunks ahead
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                rv[q] = make_uint4(0, 0, 0, 0);
+                if (pre) {
+                    const int pix = lut[(q >> 1) * 16 + (q & 1) * 8 + (lane >> 2)];
+                    if (pix >= 0) rv[q] = __ldg(reinterpret_cast<const uint4 *>(args.residual + (long long)pix * args.N + nv));
+                }
+            }
+            ok = ptx::mbar_wait(acc_full, acc_phase, args.status);
+            if (!ok) break;
+            acc_phase ^= 1u;
+            if (warp == 6 && lane == 0) SW_TRACE(ti, 6);
+            ptx::tc_fence_after_sync();
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+            for (int cc = 0; cc < 8; cc++) {
+                uint32_t v[16];
+                ptx::tmem_ld_x16(lane_addr + (uint32_t)(cc * 16), v);
+                ptx::tmem_ld_wait();
+                if (cc == 7) {                                                 // drained: the MMA thread may start the next tile
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(acc_empty);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j++) stage[j * 32 + lane] = fmaf(__uint_as_float(v[j]), sc, bi);
+                __syncwarp();
+#pragma unroll
+                for (int itr = 0; itr < 2; itr++) {
+                    const int p = itr * 8 + (lane >> 2);
+                    const int pix = lut[cc * 16 + p];
+                    const uint4 rcur = rv[(cc & 3) * 2 + itr];
+                    if (cc < 4 && pre) {                                       // request the residual of chunk cc + 4 into the freed slot
+                        const int pix4 = lut[(cc + 4) * 16 + p];
+                        rv[(cc & 3) * 2 + itr] = make_uint4(0, 0, 0, 0);
+                        if (pix4 >= 0)
+                            rv[(cc & 3) * 2 + itr] = __ldg(reinterpret_cast<const uint4 *>(args.residual + (long long)pix4 * args.N + nv));
+                    }
+                    if (pix >= 0 && nv < args.N) {
+                        const float4 lo = *reinterpret_cast<const float4 *>(stage + p * 32 + cg);
+                        const float4 hi = *reinterpret_cast<const float4 *>(stage + p * 32 + cg + 4);
+                        float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                        const long long off = (long long)pix * args.N + nv;
+                        if (vec_ok) {
+                            if (args.residual) {
+                                const __nv_bfloat16 *rb = reinterpret_cast<const __nv_bfloat16 *>(&rcur);
+#pragma unroll
+                                for (int e = 0; e < 8; e++) f[e] += __bfloat162float(rb[e]);
+                            }
+                            __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+                            for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(args.relu ? fmaxf(f[e], 0.0f) : f[e]);
+                            *reinterpret_cast<uint4 *>(args.Y + off) = *reinterpret_cast<const uint4 *>(o);
+                        } else {
+                            for (int e = 0; e < 8 && nv + e < args.N; e++) {
+                                float x = f[e];
+                                if (args.residual) x += __bfloat162float(args.residual[off + e]);
+                                args.Y[off + e] = __float2bfloat16_rn(args.relu ? fmaxf(x, 0.0f) : x);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            if (warp == 6 && lane == 0) SW_TRACE(ti, 7);
+            asm volatile("bar.sync 2, 128;" ::: "memory");                     // everyone is done with the table
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn4)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static bool make_map_nhwc(CUtensorMap *map, const void *base, int B, int H, int W, int C, int box_w, int box_h) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)W * C * 2, (cuuint64_t)H * W * C * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)box_w, (cuuint32_t)box_h, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+
+// ---- few-channel layers (an image stem): patches by descriptor, no operand tile -------------------------------------
+//
+// X fp32 NCHW with C <= CP channels, horizontal stride sx, CP = 8 / sx (sx = 2: up to 4 channels, sx = 1: up to 8).  The
+// input rows an output row needs are converted once to bf16 in shared memory as [row][pixel][CP channels]: a pixel is
+// CP * 2 bytes, so the patch rows of neighbouring OUTPUT pixels start sx * CP * 2 = 16 bytes apart - exactly the row
+// pitch of the tensor core's unswizzled K-major operand layout (8 rows x 16 bytes per core matrix).  The B operand of
+// the MMAs of filter row fy is therefore that shared-memory row itself, read through a descriptor whose core matrices
+// overlap (K-neighbour 16 bytes on, next 8 pixels 128 bytes on): no patch matrix, no operand tile, nothing but the
+// window is ever written.  K runs as (filter row, [kx x CP] padded to a multiple of 16) with zero weights in the padding.
+// Persistent CTAs (two per SM) decode the weights into tensor memory once and then walk (image, output row) tiles:
+// window fill, 'ky * KR' MMAs of N = OW, epilogue (scale / bias / ReLU, NHWC bf16).
+struct StemRowsArgs {
+    const float *X;
+    const float *scale, *bias;
+    __nv_bfloat16 *Y;
+    int B, C, H, W, OH, OW, N;
+    int ky, kx, sy, sx, py, px;
+    int KR;          // MMAs (16 k each) per filter row
+    int KW;          // packed words per weight row
+    int WB;          // bytes of one window row
+    int Npad;        // OW rounded up to 16: the MMA's N
+    long long tiles; // B * OH
+    int relu;
+    int *status;
+};
+
+constexpr int kStemRowsThreads = 320;   // warp 0: TMA, warp 1: MMA, warps 2-5: decode then epilogue, warps 6-9: window
+
+__device__ __forceinline__ uint64_t desc_rows16(uint32_t addr) {
+    // unswizzled K-major: K-adjacent core matrix 16 bytes on (leading byte offset), next 8 rows 128 bytes on (stride)
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(16u >> 4) << 16;
+    d |= (uint64_t)(128u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+
+template <int CP>
+__global__ void __launch_bounds__(kStemRowsThreads, 2)
+ternary_stem_rows_kernel(const __grid_constant__ CUtensorMap tmap_w, const StemRowsArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float *stage_base = reinterpret_cast<float *>(smem);                       // 4 x 2 KB
+    uint8_t *raw = smem + 8192;                                                // 128 rows x KW words
+    uint8_t *win = raw + 128 * 64;                                             // ky rows x WB bytes
+    const int win_bytes = (args.ky * args.WB + 127) / 128 * 128;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(win + win_bytes);
+    uint64_t *full_raw = bars, *full_a = bars + 1, *win_full = bars + 2, *win_empty = bars + 3, *acc_full = bars + 4,
+             *acc_empty = bars + 5;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 6);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t ACC_BASE = 128, TMEM_COLS = 256;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(full_raw, 1);
+        ptx::mbar_init(full_a, 4);
+        ptx::mbar_init(win_full, 4);       // the four window warps
+        ptx::mbar_init(win_empty, 1);
+        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_empty, 4);
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_w);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const bool healthy = (*reinterpret_cast<volatile int *>(args.status) == 0);
+
+    if (warp == 0) {
+        if (lane == 0 && healthy) {
+            ptx::mbar_arrive_expect_tx(full_raw, (uint32_t)(128 * args.KW * 4));
+            ptx::tma_load_2d(raw, &tmap_w, full_raw, 0, 0);
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0 && healthy) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(args.Npad >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = ptx::mbar_wait(full_a, 0u, args.status);
+            const uint64_t win_desc = desc_rows16(ptx::smem_u32(win));
+            const uint32_t row_units = (uint32_t)(args.WB >> 4);               // one window row, in descriptor units
+            int ti = 0;
+            for (long long tile = blockIdx.x; tile < args.tiles && ok; tile += gridDim.x, ti++) {
+                ok = ptx::mbar_wait(acc_empty, ((uint32_t)ti & 1u) ^ 1u, args.status);
+                if (ok) ok = ptx::mbar_wait(win_full, (uint32_t)ti & 1u, args.status);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                uint64_t row_desc = win_desc;
+                uint32_t a_col = tmem_base;
+                for (int r = 0; r < args.ky; r++, row_desc += row_units)
+                    for (int j = 0; j < args.KR; j++, a_col += 8u)
+                        ptx::umma_f16_ts(tmem_base + ACC_BASE, a_col, row_desc + 2u * (uint32_t)j, idesc,
+                                         (r | j) != 0 ? 1u : 0u);
+                ptx::umma_commit(win_empty);
+                ptx::umma_commit(acc_full);
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- weights -> tensor memory once, then epilogues
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        bool ok = healthy;
+        if (ok) ok = ptx::mbar_wait(full_raw, 0u, args.status);
+        if (ok) {
+            for (int w4 = 0; w4 < args.KW; w4 += 4) {
+                const uint4 p = *reinterpret_cast<const uint4 *>(raw + (size_t)row * args.KW * 4 + w4 * 4);
+                const uint32_t words[4] = {p.x, p.y, p.z, p.w};
+                uint32_t cols[32];
+#pragma unroll
+                for (int wi = 0; wi < 4; wi++) {
+                    uint32_t r8[8];
+                    decode_word_bf16(words[wi], r8);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) cols[8 * wi + j] = r8[j];
+                }
+                ptx::tmem_st_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)w4 * 8u, cols);
+            }
+            ptx::tmem_st_wait();
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(full_a);
+        }
+        const long long n = (long long)quarter * 32 + lane;
+        float sc = 0.5f, bi = 0.0f;                   // operands carried +-2.0
+        if (n < args.N) {
+            if (args.scale) sc *= args.scale[n];
+            if (args.bias) bi = args.bias[n];
+        }
+        float *stage = stage_base + (warp - 2) * 512;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + ACC_BASE;
+        int ti = 0;
+        for (long long tile = blockIdx.x; tile < args.tiles && ok; tile += gridDim.x, ti++) {
+            ok = ptx::mbar_wait(acc_full, (uint32_t)ti & 1u, args.status);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const long long m_base = tile * args.OW;                           // tile = b * OH + oy: first pixel of the row
+#pragma unroll 1
+            for (int c = 0; c < args.Npad; c += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld_x16(lane_addr + (uint32_t)c, v);
+                ptx::tmem_ld_wait();
+                if (c + 16 >= args.Npad) {
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(acc_empty);
+                }
+                epilogue_chunk_bf16(v, sc, bi, stage, args.Y, nullptr, m_base + c, m_base + args.OW, args.N, quarter * 32,
+                                    args.N, args.relu, lane);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- window warps 6..9: fp32 NCHW rows -> bf16 [row][pixel][CP]
+        const int t = threadIdx.x - 192;                                       // 0..127
+        const int slots = args.WB / (CP * 2);                                   // pixel slots per window row
+        bool ok = healthy;
+        int ti = 0;
+        for (long long tile = blockIdx.x; tile < args.tiles && ok; tile += gridDim.x, ti++) {
+            ok = ptx::mbar_wait(win_empty, ((uint32_t)ti & 1u) ^ 1u, args.status);
+            if (!ok) break;
+            const int b = (int)(tile / args.OH), oy = (int)(tile - (long long)b * args.OH);
+            const float *img = args.X + (long long)b * args.C * args.H * args.W;
+            // a thread owns the slots t, t + 128, ... of every window row; the loads of four rows (up to 8 * CP values)
+            // are issued before any of them is consumed, so a tile costs a few memory round trips instead of one per slot
+            for (int r0 = 0; r0 < args.ky; r0 += 4) {
+                for (int s0 = t; s0 < slots; s0 += 256) {
+                    float f[4][2][CP];
+#pragma unroll
+                    for (int dr = 0; dr < 4; dr++)
+#pragma unroll
+                        for (int u = 0; u < 2; u++) {
+                            const int r = r0 + dr, sl = s0 + 128 * u;
+                            const int iy = oy * args.sy - args.py + r, ix = sl - args.px;
+                            const bool in = r < args.ky && sl < slots && (unsigned)iy < (unsigned)args.H && (unsigned)ix < (unsigned)args.W;
+                            const float *p = img + (long long)(in ? iy : 0) * args.W + (in ? ix : 0);
+#pragma unroll
+                            for (int c = 0; c < CP; c++) f[dr][u][c] = (in && c < args.C) ? __ldg(p + (long long)c * args.H * args.W) : 0.0f;
+                        }
+#pragma unroll
+                    for (int dr = 0; dr < 4; dr++)
+#pragma unroll
+                        for (int u = 0; u < 2; u++) {
+                            const int r = r0 + dr, sl = s0 + 128 * u;
+                            if (r < args.ky && sl < slots) {
+                                __align__(16) __nv_bfloat16 o[CP];
+#pragma unroll
+                                for (int c = 0; c < CP; c++) o[c] = __float2bfloat16_rn(f[dr][u][c]);
+                                uint8_t *dst = win + (size_t)r * args.WB + (size_t)sl * (CP * 2);
+                                if (CP == 4) *reinterpret_cast<uint2 *>(dst) = *reinterpret_cast<const uint2 *>(o);
+                                else *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(o);
+                            }
+                        }
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(win_full);
+        }
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace tmq
+
+using namespace tmq;
+
+#ifdef TMQ_SW_TRACE
+extern "C" int tmq_sw_trace_read(unsigned long long *host) {
+    return cudaMemcpyFromSymbol(host, g_sw_trace, sizeof(g_sw_trace)) == cudaSuccess ? 0 : -3;
+}
+#endif
+
+extern "C" int tmq_ternary_conv2d_s1_bf16(const void *X, const uint32_t *Wt, const float *scale, const float *bias,
+                                          const void *residual, void *Y, int B, int H, int W, int C, int N, int ky, int kx,
+                                          int py, int px, int dy, int dx, int relu, int *status, void *stream) {
+    if (!X || !Wt || !Y || !status) return TMQ_ERR_ARG;
+    if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || N <= 0 || ky <= 0 || kx <= 0 || py < 0 || px < 0 || dy <= 0 || dx <= 0)
+        return TMQ_ERR_ARG;
+    if (C % 64 != 0 || ky * kx > kSwMaxTaps) return TMQ_ERR_UNSUPPORTED;
+    const int OH = H + 2 * py - dy * (ky - 1), OW = W + 2 * px - dx * (kx - 1);
+    if (OH <= 0 || OW <= 0) return TMQ_ERR_ARG;
+    if ((long long)B * OH * OW > 0x7FFFFFFFll) return TMQ_ERR_UNSUPPORTED;
+    if (!aligned(X, 16) || !aligned(Wt, 16) || !aligned(Y, 2) || !aligned(residual, 2) || !aligned(status, 4))
+        return TMQ_ERR_ALIGN;
+    const int halo_x = dx * (kx - 1), halo_y = dy * (ky - 1);
+    if (halo_x + 16 > kSwBN) return TMQ_ERR_UNSUPPORTED;
+    SwArgs a = {};
+    a.scale = scale; a.bias = bias;
+    a.residual = reinterpret_cast<const __nv_bfloat16 *>(residual);
+    a.Y = reinterpret_cast<__nv_bfloat16 *>(Y);
+    a.B = B; a.H = H; a.W = W; a.C = C; a.OH = OH; a.OW = OW; a.N = N;
+    a.ky = ky; a.kx = kx; a.py = py; a.px = px; a.dy = dy; a.dx = dx;
+    a.relu = relu; a.status = status;
+    // tile geometry: whole output rows when a padded row fits the 128 accumulator columns, else column pieces
+    a.col_pieces = (OW + halo_x + kSwBN - 1) / kSwBN;
+    if (a.col_pieces > 1) a.col_pieces = (OW + (kSwBN - halo_x) - 1) / (kSwBN - halo_x);
+    a.Wt = (OW + a.col_pieces - 1) / a.col_pieces;
+    a.Wp = a.Wt + halo_x;
+    // sub-tiles: several images side by side when one image's rows leave most of the columns idle
+    a.nsub = 1;
+    while (a.nsub < kSwMaxSub && (long long)OH * a.Wp * (a.nsub * 2) <= kSwBN && B >= a.nsub * 2) a.nsub *= 2;
+    const int cols = kSwBN / a.nsub;
+    int rmax = cols / a.Wp;
+    if (rmax < 1) return TMQ_ERR_UNSUPPORTED;
+    a.row_tiles = (OH + rmax - 1) / rmax;
+    a.R = (OH + a.row_tiles - 1) / a.row_tiles;
+    a.Rin = a.R + halo_y;
+    if (a.Rin > 256 || a.Wp > 256) return TMQ_ERR_UNSUPPORTED;
+    a.subtiles = (long long)B * a.row_tiles * a.col_pieces;
+    a.tiles_p = (a.subtiles + a.nsub - 1) / a.nsub;
+    a.tiles_n = (N + 127) / 128;
+    // a region must hold the copied rows and everything the widest shifted read of `cols` positions can touch
+    const int reach = cols + halo_y * a.Wp + halo_x;
+    a.region_rows = a.Rin * a.Wp > reach ? a.Rin * a.Wp : reach;
+    a.region_rows = (a.region_rows + 7) / 8 * 8;                                // regions start on a swizzle-atom boundary
+    const int ntaps = ky * kx;
+    // two stages of each suffice (the MMAs of a slice take longer than its copies); what matters is staying under half an
+    // SM's shared memory so that two CTAs are resident
+    a.raw_stages = 2;
+    a.in_stages = 2;
+    const SwSmem L = sw_smem(a.region_rows, a.nsub, a.in_stages, ntaps, a.raw_stages);
+    if (L.total > 220 * 1024) return TMQ_ERR_UNSUPPORTED;
+    CUtensorMap mx, mw;
+    if (!make_map_nhwc(&mx, X, B, H, W, C, a.Wp, a.Rin)) return TMQ_ERR_LAUNCH;
+    const long long K = (long long)ntaps * C;
+    const long long KW = prepack_valid_words(K), KS = prepack_row_words(K, 0);
+    if (!make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)N, (uint64_t)KS * 4, (uint32_t)(ntaps * 4),
+                     128, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return TMQ_ERR_LAUNCH;
+    const int attr_rc = ensure_dynamic_smem(ternary_conv_sw_kernel, 220 * 1024, true);
+    if (attr_rc != TMQ_OK) return attr_rc;
+    const long long ntiles = a.tiles_p * a.tiles_n;
+    const long long resident = (L.total <= 112 * 1024 ? 2 : 1) * (long long)kNumSMs;
+    const unsigned grid = (unsigned)(ntiles < resident ? ntiles : resident);
+    ternary_conv_sw_kernel<<<grid, kSwThreads, (size_t)L.total, (cudaStream_t)stream>>>(mx, mw, a);
+    return launch_status();
+}
+
+// Few-channel convolution (image stem) with the patches read by descriptor: X fp32 NCHW, C <= 8 / sx channels, sx in {1, 2}.
+// Wt = prepack (fmt 0) of the packed weights with rows ordered (ky, [kx, CP channels] zero-padded to a multiple of 16);
+// tmq_stem_rows_k gives that row count.
+extern "C" int tmq_stem_rows_k(int C, int ky, int kx, int sx) {
+    if (C <= 0 || ky <= 0 || kx <= 0 || (sx != 1 && sx != 2)) return 0;
+    const int CP = 8 / sx;
+    if (C > CP) return 0;
+    return ky * ((kx * CP + 15) / 16) * 16;
+}
+
+extern "C" int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t *Wt, const float *scale, const float *bias,
+                                                 void *Y, int B, int C, int H, int W, int N, int ky, int kx, int sy, int sx,
+                                                 int py, int px, int relu, int *status, void *stream) {
+    if (!X || !Wt || !Y || !status) return TMQ_ERR_ARG;
+    if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || N <= 0 || ky <= 0 || kx <= 0 || sy <= 0 || sx <= 0 || py < 0 || px < 0)
+        return TMQ_ERR_ARG;
+    const int Kp = tmq_stem_rows_k(C, ky, kx, sx);
+    if (Kp == 0) return TMQ_ERR_UNSUPPORTED;
+    const int CP = 8 / sx, KR = (kx * CP + 15) / 16;
+    const int OH = (H + 2 * py - ky) / sy + 1, OW = (W + 2 * px - kx) / sx + 1;
+    if (OH <= 0 || OW <= 0) return TMQ_ERR_ARG;
+    const int Npad = (OW + 15) / 16 * 16;
+    if (ky * KR > 16 || Npad > 128 || N > 128 || (N & 7) != 0) return TMQ_ERR_UNSUPPORTED;
+    if ((long long)B * OH > 0x7FFFFFFFll) return TMQ_ERR_UNSUPPORTED;
+    if (!aligned(X, 4) || !aligned(Wt, 16) || !aligned(Y, 16) || !aligned(status, 4)) return TMQ_ERR_ALIGN;
+    StemRowsArgs a = {};
+    a.X = X; a.scale = scale; a.bias = bias;
+    a.Y = reinterpret_cast<__nv_bfloat16 *>(Y);
+    a.B = B; a.C = C; a.H = H; a.W = W; a.OH = OH; a.OW = OW; a.N = N;
+    a.ky = ky; a.kx = kx; a.sy = sy; a.sx = sx; a.py = py; a.px = px;
+    a.KR = KR;
+    a.KW = (int)prepack_valid_words(Kp);
+    // a window row must hold every byte the MMAs of one filter row read: Npad rows 16 bytes apart, KR * 32 bytes each
+    a.WB = ((Npad - 1) * 16 + KR * 32 + 15) / 16 * 16;
+    a.Npad = Npad;
+    a.tiles = (long long)B * OH;
+    a.relu = relu; a.status = status;
+    if (a.KW > 16) return TMQ_ERR_UNSUPPORTED;
+    const int win_bytes = (ky * a.WB + 127) / 128 * 128;
+    const int smem = 8192 + 128 * 64 + win_bytes + 128 + 1024;
+    if (smem > 100 * 1024) return TMQ_ERR_UNSUPPORTED;
+    CUtensorMap mw;
+    const long long KS = prepack_row_words(Kp, 0);
+    if (!make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)a.KW, (uint64_t)N, (uint64_t)KS * 4, (uint32_t)a.KW, 128,
+                     CU_TENSOR_MAP_SWIZZLE_NONE))
+        return TMQ_ERR_LAUNCH;
+    const long long want = 2LL * kNumSMs;
+    const unsigned grid = (unsigned)(a.tiles < want ? a.tiles : want);
+    int rc;
+    if (CP == 4) {
+        if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<4>, smem)) != TMQ_OK) return rc;
+        ternary_stem_rows_kernel<4><<<grid, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(mw, a);
+    } else {
+        if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<8>, smem)) != TMQ_OK) return rc;
+        ternary_stem_rows_kernel<8><<<grid, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(mw, a);
+    }
+    return launch_status();
+}

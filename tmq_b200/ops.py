@@ -692,9 +692,109 @@ def conv_rows_kkc(packed, cin, ky, kx, terms=1, pad_to=8):
     return r.contiguous()
 
 
+def conv_rows_skkc(packed, cin, ky, kx):
+    """Packed convolution weights (reference layout, rows in (c, ky, kx) order) -> rows in (64-channel slice, ky, kx,
+    channel within the slice) order: the K order of the stride-1 shifted-window kernel, which takes all taps of one
+    channel slice with a single copy."""
+    rows = packed.contiguous().view(-1, packed.shape[-1])
+    taps, cin = int(ky) * int(kx), int(cin)
+    if rows.shape[0] != cin * taps or cin % 64 != 0:
+        raise RuntimeError("conv_rows_skkc: packed weights do not match the kernel geometry (channels % 64 == 0)")
+    r = rows.view(cin // 64, 64, taps, -1).permute(0, 2, 1, 3)         # [slice, tap, c64, Q]
+    return r.reshape(-1, rows.shape[-1]).contiguous()
+
+
+def conv_rows_stem(packed, cin, ky, kx, sx):
+    """Packed weights of a few-channel convolution -> the K order of the descriptor-patch stem kernel: (filter row,
+    [kx positions x CP channels] zero-padded to a multiple of 16), CP = 8 / sx channel slots per pixel.  None when the
+    layer is outside that kernel's reach (sx not 1 or 2, more than CP channels)."""
+    cin, ky, kx, sx = int(cin), int(ky), int(kx), int(sx)
+    k_rows = int(lib().tmq_stem_rows_k(cin, ky, kx, sx))
+    if k_rows == 0:
+        return None
+    cp = 8 // sx
+    per_row = k_rows // ky
+    rows = packed.contiguous().view(-1, packed.shape[-1])
+    if rows.shape[0] != cin * ky * kx:
+        raise RuntimeError("conv_rows_stem: packed weights do not match the kernel geometry")
+    e = torch.arange(per_row, device=rows.device)
+    kxi, c = e // cp, e % cp
+    valid = (kxi < kx) & (c < cin)
+    r = torch.arange(ky, device=rows.device).view(-1, 1)
+    src = (c.clamp(max=cin - 1) * (ky * kx)).view(1, -1) + r * kx + kxi.clamp(max=kx - 1).view(1, -1)     # [ky, per_row]
+    out = rows.index_select(0, src.reshape(-1)).view(ky, per_row, -1)
+    out = torch.where(valid.view(1, -1, 1), out, torch.zeros_like(out))
+    return out.reshape(k_rows, -1).contiguous()
+
+
+def ternary_conv2d_stem_rows(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), scale=None, bias=None, relu=False):
+    """Few-channel convolution with the patches read straight out of a bf16 copy of the input rows in shared memory (no
+    patch matrix, no operand tile): x fp32 NCHW [B, C, H, W], wt = prepack(conv_rows_stem(...), FMT_BF16) -> bf16 NHWC.
+    None when the shape is outside the kernel's limits."""
+    if x.dtype != torch.float32 or x.device.type != "cuda" or x.dim() != 4:
+        raise RuntimeError("ternary_conv2d_stem_rows: expected a 4-D CUDA fp32 NCHW tensor")
+    x = x.contiguous()
+    b, c, h, w = x.shape
+    (ky, kx), (sy, sx), (py, px) = kernel, stride, padding
+    n = int(columns)
+    k_rows = int(lib().tmq_stem_rows_k(c, ky, kx, sx))
+    if k_rows == 0:
+        return None
+    if wt.dtype != torch.int32 or wt.shape[0] != n or wt.shape[1] != prepack_row_words(k_rows, FMT_BF16):
+        raise RuntimeError("ternary_conv2d_stem_rows: prepacked weights do not match the problem shape")
+    oh, ow = (h + 2 * py - ky) // sy + 1, (w + 2 * px - kx) // sx + 1
+    y = torch.empty((b, oh, ow, n), dtype=torch.bfloat16, device=x.device)
+    sc, bi = _opt_f32(scale, x.device), _opt_f32(bias, x.device)
+    st = gemm_status_word(x.device)
+    with torch.cuda.device(x.device):
+        rc = lib().tmq_ternary_conv2d_stem_rows_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
+                                                     _ptr(bi) if bi is not None else None, _ptr(y), b, c, h, w, n, ky, kx,
+                                                     sy, sx, py, px, 1 if relu else 0, _ptr(st), _stream(x))
+    if rc == -6:
+        return None
+    check(rc, "ternary_conv2d_stem_rows")
+    _launched(x.device)
+    return y
+
+
+def ternary_conv2d_s1(x, wt, columns, kernel, padding=(0, 0), dilation=(1, 1), scale=None, bias=None, relu=False,
+                      residual=None):
+    """Unit-stride implicit-GEMM convolution on bf16 NHWC activations [B, H, W, C] (C % 64 == 0) with the input tile
+    resident in shared memory for all filter taps; wt = prepack(conv_rows_skkc(...), FMT_BF16).  Returns bf16 NHWC, or
+    None when the geometry is outside this kernel's limits (the caller then takes ternary_conv2d_nhwc)."""
+    if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 4 or not x.is_contiguous():
+        raise RuntimeError("ternary_conv2d_s1: expected a contiguous 4-D CUDA bf16 NHWC tensor")
+    b, h, w, c = x.shape
+    (ky, kx), (py, px), (dy, dx) = kernel, padding, dilation
+    n = int(columns)
+    if c % 64 != 0 or ky * kx > 9:
+        return None
+    if wt.dtype != torch.int32 or wt.shape[0] != n or wt.shape[1] != prepack_row_words(ky * kx * c, FMT_BF16):
+        raise RuntimeError("ternary_conv2d_s1: prepacked weights do not match the problem shape")
+    oh, ow = h + 2 * py - dy * (ky - 1), w + 2 * px - dx * (kx - 1)
+    if oh <= 0 or ow <= 0:
+        raise RuntimeError("ternary_conv2d_s1: empty output")
+    y = torch.empty((b, oh, ow, n), dtype=torch.bfloat16, device=x.device)
+    sc, bi = _opt_f32(scale, x.device), _opt_f32(bias, x.device)
+    if residual is not None and (residual.dtype != torch.bfloat16 or tuple(residual.shape) != tuple(y.shape)
+                                 or not residual.is_contiguous()):
+        raise RuntimeError("ternary_conv2d_s1: the residual must be a contiguous bf16 tensor of the output's shape")
+    st = gemm_status_word(x.device)
+    with torch.cuda.device(x.device):
+        rc = lib().tmq_ternary_conv2d_s1_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
+                                              _ptr(bi) if bi is not None else None,
+                                              _ptr(residual) if residual is not None else None, _ptr(y), b, h, w, c, n, ky,
+                                              kx, py, px, dy, dx, 1 if relu else 0, _ptr(st), _stream(x))
+    if rc == -6:
+        return None
+    check(rc, "ternary_conv2d_s1")
+    _launched(x.device)
+    return y
+
+
 def split_f32(x2d, terms=3, kp=None):
-    """fp32 [M, K] -> bf16 [M, terms * kp]: terms = 1 rounds, terms = 3 is the exact split x = hi + mid + lo with term t
-    in columns [t * kp, t * kp + K); kp >= K pads every term with zero columns."""
+    """fp32 [M, K] -> bf16 [M, terms * kp]: terms = 1 rounds, terms = 3 is the exact split x = lo + mid + hi (smallest
+    term first) with term t in columns [t * kp, t * kp + K); kp >= K pads every term with zero columns."""
     if x2d.dtype != torch.float32 or x2d.device.type != "cuda" or x2d.dim() != 2:
         raise RuntimeError("split_f32: expected a 2-D CUDA float32 tensor")
     x2d = x2d.contiguous()

@@ -666,8 +666,6 @@ class Conv2d(nn.Module, TMQLayer):
         (ky, kx) = kernel
         terms = 3 if x.dtype == torch.float32 else 1
         fmt = ops.FMT_I8 if x.dtype == torch.int8 else ops.FMT_BF16
-        wt = self._cached_layout(("conv", fmt, terms), lambda: ops.prepack(
-            ops.conv_rows_kkc(self.weight.data, c, ky, kx, terms, pad_to=1), n_out, fmt))
         nhwc = x.permute(0, 2, 3, 1)
         if x.dtype == torch.float32:
             if nhwc.is_contiguous():                       # channels_last fp32: split the pixel rows in place
@@ -676,6 +674,15 @@ class Conv2d(nn.Module, TMQLayer):
                 xin = ops.nchw_to_nhwc_bf16(x, 3)
         else:
             xin = nhwc if nhwc.is_contiguous() else nhwc.contiguous()
+        if x.dtype == torch.bfloat16 and stride == (1, 1) and ky * kx <= 9:
+            wt1 = self._cached_layout(("conv_s1",), lambda: ops.prepack(
+                ops.conv_rows_skkc(self.weight.data, c, ky, kx), n_out, ops.FMT_BF16))
+            y = ops.ternary_conv2d_s1(xin, wt1, n_out, kernel, padding, dilation, self._epilogue_scale(n_out, x.device),
+                                      self.bias)
+            if y is not None:
+                return y.permute(0, 3, 1, 2)
+        wt = self._cached_layout(("conv", fmt, terms), lambda: ops.prepack(
+            ops.conv_rows_kkc(self.weight.data, c, ky, kx, terms, pad_to=1), n_out, fmt))
         if x.dtype == torch.int8:
             y = ops.ternary_conv2d_nhwc(xin, wt, n_out, kernel, stride, padding, dilation)
         else:
@@ -690,6 +697,15 @@ class Conv2d(nn.Module, TMQLayer):
         b, c, h, w = x.shape
         n_out = int(self.original_shape[0])
         (ky, kx) = kernel
+        def rows_layout():
+            rows = ops.conv_rows_stem(self.weight.data, c, ky, kx, stride[1])
+            return None if rows is None else ops.prepack(rows, n_out, ops.FMT_BF16)
+        wt_rows = self._cached_layout(("stem_rows",), rows_layout)
+        if wt_rows is not None:
+            y = ops.ternary_conv2d_stem_rows(x.float(), wt_rows, n_out, kernel, stride, padding,
+                                             self._epilogue_scale(n_out, x.device), self.bias)
+            if y is not None:
+                return y.permute(0, 3, 1, 2)
         wt = self._cached_layout(("stem",), lambda: ops.prepack(
             ops.conv_rows_kkc(self.weight.data, c, ky, kx, 1, pad_to=8), n_out, ops.FMT_BF16))
         y = ops.ternary_conv2d_stem(x.float(), wt, n_out, kernel, stride, padding,

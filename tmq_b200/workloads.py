@@ -89,11 +89,27 @@ class PackedConv:
         self.implicit = (self.cin % 64 == 0)
         self.wt = ops.prepack(ops.conv_rows_kkc(layer.weight.data, self.cin, self.ky, self.kx, 1, pad_to=8), self.cout,
                               ops.FMT_BF16)
+        # few-channel layers: the K order of the descriptor-patch stem kernel, where it covers the layer
+        self.wt_rows = None
+        if not self.implicit and self.dilation == (1, 1):
+            rows = ops.conv_rows_stem(layer.weight.data, self.cin, self.ky, self.kx, self.stride[1])
+            if rows is not None:
+                self.wt_rows = ops.prepack(rows, self.cout, ops.FMT_BF16)
+        # unit-stride layers also get the slice-major layout of the shifted-window kernel
+        self.wt_s1 = None
+        if self.implicit and self.stride == (1, 1) and self.ky * self.kx <= 9:
+            self.wt_s1 = ops.prepack(ops.conv_rows_skkc(layer.weight.data, self.cin, self.ky, self.kx), self.cout,
+                                     ops.FMT_BF16)
 
     def from_images(self, images, defer_relu=False):
         """Stem route: fp32 NCHW images -> bf16 NHWC feature map, patches built by a kernel (no torch glue).
         defer_relu: leave the activation to the caller (a max pooling that follows applies it for free)."""
         relu = self.relu and not defer_relu
+        if self.wt_rows is not None:
+            y = ops.ternary_conv2d_stem_rows(images, self.wt_rows, self.cout, (self.ky, self.kx), self.stride, self.padding,
+                                             self.scale, self.bias, relu=relu)
+            if y is not None:
+                return y
         if self.dilation == (1, 1):
             y = ops.ternary_conv2d_stem(images, self.wt, self.cout, (self.ky, self.kx), self.stride, self.padding,
                                         self.scale, self.bias, relu=relu)
@@ -108,6 +124,11 @@ class PackedConv:
         ReLU inside the convolution's epilogue."""
         if not self.implicit:
             raise RuntimeError("PackedConv: this layer's channel count needs the from_images() route")
+        if self.wt_s1 is not None:
+            y = ops.ternary_conv2d_s1(x_nhwc, self.wt_s1, self.cout, (self.ky, self.kx), self.padding, self.dilation,
+                                      self.scale, self.bias, relu=self.relu, residual=residual)
+            if y is not None:
+                return y
         return ops.ternary_conv2d_nhwc(x_nhwc, self.wt, self.cout, (self.ky, self.kx), self.stride, self.padding,
                                        self.dilation, self.scale, self.bias, relu=self.relu, residual=residual)
 
