@@ -31,7 +31,7 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-GEMV_ROWS_PER_PASS = 8      # activation rows one skinny-kernel launch takes
+GEMV_ROWS_PER_PASS = 16     # activation rows one skinny-kernel launch takes
 HARDNESS = [0.1, 0.5, 0.9, 1.0]
 SHARPNESS, STRENGTH, LO, HI = 5.0, 5e-4, -1.0, 1.0
 BYTES_PER_ELEM = 20
@@ -481,16 +481,17 @@ def ternary_sections(peaks):
     for i in range(NM):
         wts.append(ops.prepack(_ternary_packed(ops, N, K, 100 + i), N, ops.FMT_BF16))
     scale = torch.rand(N, device="cuda") * 0.09 + 0.01
-    for Mg in (1, 8, 32):
+    for Mg in (1, 8, 16, 32):
         X = torch.randn(Mg, K, device="cuda").to(torch.bfloat16)
         Y = torch.empty(Mg, N, device="cuda", dtype=torch.bfloat16)
         status = ops.gemm_status_word(X.device)
         stream = torch.cuda.Stream()
 
         def run(i, st):
-            for m0 in range(0, Mg, 8):
+            for m0 in range(0, Mg, GEMV_ROWS_PER_PASS):
                 rc = L.tmq_ternary_gemv_bf16(X.data_ptr() + m0 * K * 2, wts[i].data_ptr(), scale.data_ptr(), None,
-                                             Y.data_ptr() + m0 * N * 2, min(8, Mg - m0), N, K, N, 0, status.data_ptr(), st)
+                                             Y.data_ptr() + m0 * N * 2, min(GEMV_ROWS_PER_PASS, Mg - m0), N, K, N, 0,
+                                             status.data_ptr(), st)
                 assert rc == 0
         with torch.cuda.stream(stream):
             for i in range(NM):
@@ -514,13 +515,14 @@ def ternary_sections(peaks):
         res[f"gemv_bf16_M{Mg}_N11008_K4096"] = {"us_per_matrix": us, "gbs": nbytes / us / 1e3,
                                                "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"],
                                                "tops_equiv": 2 * Mg * N * K / us / 1e6, "algorithmic_bytes": nbytes,
-                                               "protocol": "32 distinct matrices in one CUDA graph, time/32"}
+                                               "protocol": "32 distinct matrices in one CUDA graph, time/32; "
+                                                           f"{(Mg + GEMV_ROWS_PER_PASS - 1) // GEMV_ROWS_PER_PASS} launch(es) per matrix"}
     # the same protocol with int8 activations (exact int32 results; byte dot products at M = 1)
     wts8 = []
     for i in range(NM):
         wts8.append(ops.prepack(_ternary_packed(ops, N, K, 100 + i), N, ops.FMT_I8))
     del wts
-    for Mg in (1, 8):
+    for Mg in (1, 8, 16):
         X8 = torch.randint(-127, 128, (Mg, K), device="cuda", dtype=torch.int8)
         Y8 = torch.empty(Mg, N, device="cuda", dtype=torch.int32)
         status = ops.gemm_status_word(X8.device)

@@ -184,8 +184,10 @@ int tmq_ternary_gemm_bf16(const void *X, const uint32_t *Wt, const float *scale,
 int tmq_ternary_gemm_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
                         int *status, void *stream);
 
-/* Skinny form for M <= 8 activation rows (decode-like GEMV): reads the packed weights once, exactly decoded operands
- * (warp-level MMA; byte dot products for int8 with M <= 2), deterministic.  Same operand conventions as the GEMM
+/* Skinny form for M <= 16 activation rows (decode-like GEMV): reads the packed weights once, exactly decoded operands
+ * (warp-level MMA, the decoded fragment shared by both 8-row tiles when M > 8; byte dot products for int8 with M <= 2),
+ * deterministic.  M > 8 needs the resident form (a status word, and one SM's share of the rows within the shared-memory
+ * budget): TMQ_ERR_UNSUPPORTED otherwise, and the caller makes two calls of up to 8 rows.  Same operand conventions as the GEMM
  * entry points above.  When one SM's share of the packed rows fits half its shared memory the rows are made
  * resident with bulk copies issued BEFORE the kernel waits for its predecessor in the stream (programmatic dependent
  * launch), so consecutive launches overlap their weight traffic with the predecessor's arithmetic; `status` (device
@@ -260,8 +262,10 @@ int tmq_ternary_conv2d_stem_bf16(const float *X, const uint32_t *Wt, const float
  * 4 channels, sx = 1: up to 8), which puts the patch rows of neighbouring output pixels 16 bytes apart - the row pitch of
  * the tensor core's unswizzled operand layout - so every MMA reads its operand straight from that window.  Wt = fmt-0
  * prepack of the packed weights with K ordered (ky, [kx, CP] zero-padded to a multiple of 16): tmq_stem_rows_k rows
- * (0 = layer not covered).  Limits: OW <= 128, N <= 128, N % 8 == 0, ky * ceil(kx * CP / 16) <= 16; TMQ_ERR_UNSUPPORTED
- * beyond (then: tmq_ternary_conv2d_stem_bf16).  replaces: Conv2d.compact_forward for such layers, tmq/tmq.py:822-871. */
+ * (0 = layer not covered).  The output pixels of a row are the MMA's M side and the (at most 64) output channels its N
+ * side, so an epilogue thread writes one pixel's channels contiguously; the window is a ring of ky + sy rows and a tile
+ * converts only the rows its predecessor did not have.  Limits: OW <= 128, N <= 64, sy < ky, ky * ceil(kx * CP / 16) <= 24;
+ * TMQ_ERR_UNSUPPORTED beyond (then: tmq_ternary_conv2d_stem_bf16).  replaces: Conv2d.compact_forward for such layers, tmq/tmq.py:822-871. */
 int tmq_stem_rows_k(int C, int ky, int kx, int sx);
 int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y,
                                       int B, int C, int H, int W, int N, int ky, int kx, int sy, int sx, int py, int px,

@@ -60,6 +60,12 @@ S1_CASES = [
     (3, 128, 9, 12, 64, (1, 1), (0, 0), (1, 1), True, True),        # 1 x 1
     (2, 64, 10, 17, 96, (3, 1), (1, 0), (1, 1), False, False),      # 3 x 1 kernel, asymmetric padding
     (2, 64, 12, 12, 64, (2, 2), (1, 0), (1, 1), False, False),      # even kernel: output larger / smaller than the input
+    # one input slice, <= 64 output channels and enough tiles for two streams per SM: the pixel-major kernel
+    (12, 64, 56, 56, 64, (3, 3), (1, 1), (1, 1), True, True),
+    (11, 64, 56, 40, 48, (3, 3), (1, 1), (1, 1), False, True),      # 48 channels
+    (16, 64, 40, 44, 36, (3, 3), (0, 0), (1, 1), True, False),      # channel count that is no multiple of 8: scalar stores
+    (5, 64, 30, 260, 64, (3, 3), (1, 1), (1, 1), False, False),     # column pieces
+    (40, 64, 24, 24, 64, (1, 1), (0, 0), (1, 1), True, True),       # 1 x 1
 ]
 
 
@@ -105,9 +111,11 @@ STEM_CASES = [
     (3, 3, 64, 64, 64, (7, 7), (2, 2), (3, 3), True),
     (2, 1, 30, 40, 32, (3, 3), (2, 2), (1, 1), False),          # one channel
     (2, 4, 33, 31, 64, (5, 5), (2, 2), (2, 2), True),           # all four channel slots used, odd sizes
-    (2, 3, 21, 50, 72, (3, 5), (1, 2), (0, 2), False),          # vertical stride 1, ragged channel count
+    (2, 3, 21, 50, 40, (3, 5), (1, 2), (0, 2), False),          # vertical stride 1, 40 channels
     (2, 8, 20, 24, 64, (3, 3), (1, 1), (1, 1), True),           # horizontal stride 1: eight channel slots
-    (1, 5, 17, 19, 128, (3, 3), (2, 1), (1, 1), False),
+    (1, 5, 17, 19, 56, (3, 3), (2, 1), (1, 1), False),
+    (7, 3, 50, 60, 64, (7, 7), (2, 2), (3, 3), True),           # several images per CTA range: refills at image boundaries
+    (300, 2, 9, 12, 20, (3, 3), (2, 2), (1, 1), False),         # many small images, channel count no multiple of 8
 ]
 
 

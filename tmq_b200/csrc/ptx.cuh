@@ -10,6 +10,19 @@ namespace ptx {
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// One lane of a converged warp (the same lane every time).  Code that only differs by this predicate stays warp-uniform
+// for the compiler, which matters for a loop that feeds tcgen05.mma: descriptors and addresses computed under a
+// threadIdx-based branch live in ordinary registers and have to be moved to uniform registers for every MMA.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ---------------------------------------------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
@@ -51,6 +64,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *s
             }
         }
     }
+}
+
+// The same wait made by a whole converged warp, with a warp-uniform verdict (one lane giving up makes every lane give up),
+// so that code after it can stay convergent (elect_one needs the full warp).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, int *status,
+                                               long long budget = kWaitBudgetCycles) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, budget) ? 1 : 0) != 0;
 }
 
 // ---------------------------------------------------------------------------------------------------- fences / TMA

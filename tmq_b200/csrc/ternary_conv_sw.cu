@@ -197,48 +197,63 @@ ternary_conv_sw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             }
         }
     } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer (one thread; keep this loop small)
+        // ---------------------------------------------------------------- MMA issuer (keep this loop small)
+        // The whole warp walks the loop - waits, stage counters and descriptor arithmetic are warp-uniform - and one elected
+        // lane issues the MMAs and commits.
+#ifdef TMQ_SW_LANE0
         if (lane == 0 && healthy) {
+#else
+        if (healthy) {
+#endif
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(nsubcols >> 3) << 17) | ((128u >> 4) << 24);
             const uint32_t sub_units = (uint32_t)(args.region_rows * 8);       // next sub-tile's region, in 16-byte units
             int si = 0, sa = 0, ka = 0;
             uint32_t in_phase = 0, a_phase = 0, acc_phase = 1;
             bool ok = true;
             for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                ok = ptx::mbar_wait(acc_empty, acc_phase, args.status);        // the epilogue has drained the accumulator
+                ok = ptx::mbar_wait_warp(acc_empty, acc_phase, args.status);        // the epilogue has drained the accumulator
                 if (!ok) break;
                 acc_phase ^= 1u;
                 ptx::tc_fence_after_sync();
                 uint32_t accum = 0u;
                 for (int sl = 0; sl < nslices && ok; sl++) {
-                    ok = ptx::mbar_wait(full_in + si, in_phase, args.status);
+                    ok = ptx::mbar_wait_warp(full_in + si, in_phase, args.status);
                     if (!ok) break;
-                    SW_TRACE(sl, 1);
+                    if (lane == 0) SW_TRACE(sl, 1);
                     const uint64_t in_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L.in_off + si * L.in_stage_bytes));
 #pragma unroll 1
                     for (int tap = 0; tap < ntaps; tap++, ka++) {
-                        ok = ptx::mbar_wait(full_a + sa, a_phase, args.status);
+                        ok = ptx::mbar_wait_warp(full_a + sa, a_phase, args.status);
                         if (!ok) break;
-                        SW_TRACE(ka, 4);
+                        if (lane == 0) SW_TRACE(ka, 4);
                         ptx::tc_fence_after_sync();
                         const uint32_t a_tmem = tmem_base + A_BASE + (uint32_t)sa * 32u;
                         uint64_t b_desc = in_desc + (uint32_t)(shtab[tap] * 8);    // the tap's row shift, in 16-byte units
                         uint32_t d_tmem = tmem_base;
-                        for (int g = 0; g < args.nsub; g++, b_desc += sub_units, d_tmem += (uint32_t)nsubcols) {
+#ifdef TMQ_SW_LANE0
+                        {
+#else
+                        if (ptx::elect_one()) {
+#endif
+                            for (int g = 0; g < args.nsub; g++, b_desc += sub_units, d_tmem += (uint32_t)nsubcols) {
 #pragma unroll
-                            for (int k4 = 0; k4 < 4; k4++)
-                                ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (accum | (uint32_t)k4) ? 1u : 0u);
+                                for (int k4 = 0; k4 < 4; k4++)
+                                    ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (accum | (uint32_t)k4) ? 1u : 0u);
+                            }
+                            ptx::umma_commit(empty_a + sa);
                         }
+                        __syncwarp();
                         accum = 1u;
-                        ptx::umma_commit(empty_a + sa);
-                        SW_TRACE(ka, 5);
+                        if (lane == 0) SW_TRACE(ka, 5);
                         sa = (sa + 1) & (kSwAStages - 1);
                         a_phase ^= (sa == 0) ? 1u : 0u;
                     }
-                    if (ok) ptx::umma_commit(empty_in + si);                   // every tap of the slice has read the region
+                    if (ok && ptx::elect_one()) ptx::umma_commit(empty_in + si);   // every tap of the slice has read the region
+                    __syncwarp();
                     if (++si == args.in_stages) { si = 0; in_phase ^= 1u; }
                 }
-                if (ok) ptx::umma_commit(acc_full);
+                if (ok && ptx::elect_one()) ptx::umma_commit(acc_full);
+                __syncwarp();
             }
         }
     } else if (warp < 6) {
@@ -399,6 +414,10 @@ typedef CUresult (*EncodeTiledFn4)(CUtensorMap *, CUtensorMapDataType, cuuint32_
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+int launch_conv_pixel_major(const void *X, const uint32_t *Wt, const float *scale, const float *bias, const void *residual,
+                            void *Y, int B, int H, int W, int C, int N, int ky, int kx, int py, int px, int dy, int dx,
+                            int relu, int *status, cudaStream_t st);   // ternary_conv_pm.cu
+
 static bool make_map_nhwc(CUtensorMap *map, const void *base, int B, int H, int W, int C, int box_w, int box_h) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
@@ -414,68 +433,90 @@ static bool make_map_nhwc(CUtensorMap *map, const void *base, int B, int H, int 
 
 // ---- few-channel layers (an image stem): patches by descriptor, no operand tile -------------------------------------
 //
-// X fp32 NCHW with C <= CP channels, horizontal stride sx, CP = 8 / sx (sx = 2: up to 4 channels, sx = 1: up to 8).  The
-// input rows an output row needs are converted once to bf16 in shared memory as [row][pixel][CP channels]: a pixel is
-// CP * 2 bytes, so the patch rows of neighbouring OUTPUT pixels start sx * CP * 2 = 16 bytes apart - exactly the row
-// pitch of the tensor core's unswizzled K-major operand layout (8 rows x 16 bytes per core matrix).  The B operand of
-// the MMAs of filter row fy is therefore that shared-memory row itself, read through a descriptor whose core matrices
-// overlap (K-neighbour 16 bytes on, next 8 pixels 128 bytes on): no patch matrix, no operand tile, nothing but the
-// window is ever written.  K runs as (filter row, [kx x CP] padded to a multiple of 16) with zero weights in the padding.
-// Persistent CTAs (two per SM) decode the weights into tensor memory once and then walk (image, output row) tiles:
-// window fill, 'ky * KR' MMAs of N = OW, epilogue (scale / bias / ReLU, NHWC bf16).
+// X fp32 NCHW with C <= CP channels, horizontal stride sx, CP = 8 / sx (sx = 2: up to 4 channels, sx = 1: up to 8), at
+// most 64 output channels.  The input rows an output row needs are kept in shared memory as bf16 [row][pixel][CP
+// channels]: a pixel is CP * 2 bytes, so the patch rows of neighbouring OUTPUT pixels start sx * CP * 2 = 16 bytes apart -
+// exactly the row pitch of the tensor core's unswizzled K-major operand layout (8 rows x 16 bytes per core matrix).  The
+// A operand (M = 128 output pixels of one output row) of the MMAs of filter row fy is therefore that shared-memory row
+// itself, read through a descriptor whose core matrices overlap (K-neighbour 16 bytes on, next 8 pixels 128 bytes on): no
+// patch matrix, no operand tile.  K runs as (filter row, [kx x CP] padded to a multiple of 16) with zero weights in the
+// padding; the decoded weights (B operand, N = 64) sit in shared memory for the life of the CTA.
+//   * the window is a RING of ky + sy input rows: consecutive tiles of a CTA are consecutive output rows of an image, so a
+//     new tile converts only the sy rows it does not share with its predecessor;
+//   * accumulator [128 pixels (lanes)] x [64 channels (columns)], double-buffered: an epilogue thread owns one pixel and
+//     writes its 64 channels (scale / bias / ReLU, bf16 NHWC) as 128 contiguous bytes while the next row is multiplied;
+//   * persistent CTAs, two per SM, each walking a contiguous range of (image, output row) tiles.
 struct StemRowsArgs {
     const float *X;
+    const uint32_t *Wt;       // prepacked weights [N][KS words], K order (ky, [kx, CP] padded to 16)
     const float *scale, *bias;
     __nv_bfloat16 *Y;
     int B, C, H, W, OH, OW, N;
     int ky, kx, sy, sx, py, px;
     int KR;          // MMAs (16 k each) per filter row
-    int KW;          // packed words per weight row
+    int KS;          // row stride of Wt in words
     int WB;          // bytes of one window row
-    int Npad;        // OW rounded up to 16: the MMA's N
+    int ring;        // window rows kept: ky + sy
     long long tiles; // B * OH
+    long long per_cta;   // tiles per CTA (contiguous)
     int relu;
     int *status;
 };
 
-constexpr int kStemRowsThreads = 320;   // warp 0: TMA, warp 1: MMA, warps 2-5: decode then epilogue, warps 6-9: window
+constexpr int kStemRowsThreads = 320;   // warp 0: spare, warp 1: MMA, warps 2-5: epilogue, warps 6-9: window
 
-__device__ __forceinline__ uint64_t desc_rows16(uint32_t addr) {
-    // unswizzled K-major: K-adjacent core matrix 16 bytes on (leading byte offset), next 8 rows 128 bytes on (stride)
+__device__ __forceinline__ uint64_t desc_k16(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    // unswizzled K-major: K-adjacent 16-byte chunk lbo_bytes on (leading byte offset), next 8 rows sbo_bytes on (stride)
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(16u >> 4) << 16;
-    d |= (uint64_t)(128u >> 4) << 32;
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
     d |= (uint64_t)1 << 46;
     return d;
 }
 
 template <int CP>
 __global__ void __launch_bounds__(kStemRowsThreads, 2)
-ternary_stem_rows_kernel(const __grid_constant__ CUtensorMap tmap_w, const StemRowsArgs args) {
+ternary_stem_rows_kernel(const StemRowsArgs args) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    float *stage_base = reinterpret_cast<float *>(smem);                       // 4 x 2 KB
-    uint8_t *raw = smem + 8192;                                                // 128 rows x KW words
-    uint8_t *win = raw + 128 * 64;                                             // ky rows x WB bytes
-    const int win_bytes = (args.ky * args.WB + 127) / 128 * 128;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(win + win_bytes);
-    uint64_t *full_raw = bars, *full_a = bars + 1, *win_full = bars + 2, *win_empty = bars + 3, *acc_full = bars + 4,
-             *acc_empty = bars + 5;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 6);
+    const int ksteps = args.ky * args.KR;
+    uint8_t *wsm = smem;                                                       // [kstep][2 chunks][64 rows x 16 B] = 2 KB each
+    uint8_t *win = wsm + ksteps * 2048;                                        // [ring][WB]
+    const int win_bytes = (args.ring * args.WB + 127) / 128 * 128;
+    float *sc_s = reinterpret_cast<float *>(win + win_bytes), *bi_s = sc_s + 64;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(bi_s + 64);
+    // every barrier exists twice, for even and odd tiles: a producer can then never complete two phases of one barrier
+    // before its consumer has looked at the first (a parity wait cannot tell phase n from phase n + 2)
+    uint64_t *win_full = bars, *win_empty = bars + 2, *acc_full = bars + 4, *acc_empty = bars + 6;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr uint32_t ACC_BASE = 128, TMEM_COLS = 256;
+    constexpr uint32_t TMEM_COLS = 128;                                        // two 64-column accumulators
 
     if (threadIdx.x == 0) {
-        ptx::mbar_init(full_raw, 1);
-        ptx::mbar_init(full_a, 4);
-        ptx::mbar_init(win_full, 4);       // the four window warps
-        ptx::mbar_init(win_empty, 1);
-        ptx::mbar_init(acc_full, 1);
-        ptx::mbar_init(acc_empty, 4);
+        for (int b = 0; b < 2; b++) {
+            ptx::mbar_init(win_full + b, 4);   // the four window warps
+            ptx::mbar_init(win_empty + b, 1);
+            ptx::mbar_init(acc_full + b, 1);
+            ptx::mbar_init(acc_empty + b, 4);
+        }
         ptx::fence_mbar_init();
-        ptx::prefetch_tensormap(&tmap_w);
     }
+    if (threadIdx.x < 64) {
+        const int n = threadIdx.x;
+        sc_s[n] = 0.5f * ((n < args.N && args.scale) ? args.scale[n] : 1.0f);  // operands carried +-2.0
+        bi_s[n] = (n < args.N && args.bias) ? args.bias[n] : 0.0f;
+    }
+    // resident weights: word ks of channel n = its 16 k of MMA step ks -> two 16-byte chunks of the unswizzled B tile
+    for (int i = threadIdx.x; i < 64 * ksteps; i += kStemRowsThreads) {
+        const int n = i / ksteps, ks = i - n * ksteps;
+        uint32_t r[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (n < args.N) decode_word_bf16(__ldg(args.Wt + (size_t)n * args.KS + ks), r);
+        uint8_t *dst = wsm + ks * 2048 + n * 16;
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(r[0], r[1], r[2], r[3]);
+        *reinterpret_cast<uint4 *>(dst + 1024) = make_uint4(r[4], r[5], r[6], r[7]);
+    }
+    ptx::fence_proxy_async_smem();
     if (warp == 1) {
         ptx::tmem_alloc(tmem_slot, TMEM_COLS);
         ptx::tmem_relinquish();
@@ -485,117 +526,122 @@ ternary_stem_rows_kernel(const __grid_constant__ CUtensorMap tmap_w, const StemR
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     const bool healthy = (*reinterpret_cast<volatile int *>(args.status) == 0);
+    const long long t_begin = (long long)blockIdx.x * args.per_cta;
+    long long t_end = t_begin + args.per_cta;
+    if (t_end > args.tiles) t_end = args.tiles;
 
-    if (warp == 0) {
-        if (lane == 0 && healthy) {
-            ptx::mbar_arrive_expect_tx(full_raw, (uint32_t)(128 * args.KW * 4));
-            ptx::tma_load_2d(raw, &tmap_w, full_raw, 0, 0);
-        }
-    } else if (warp == 1) {
+    if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0 && healthy) {
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(args.Npad >> 3) << 17) | ((128u >> 4) << 24);
-            bool ok = ptx::mbar_wait(full_a, 0u, args.status);
-            const uint64_t win_desc = desc_rows16(ptx::smem_u32(win));
-            const uint32_t row_units = (uint32_t)(args.WB >> 4);               // one window row, in descriptor units
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((128u >> 4) << 24);
+            const uint32_t win_addr = ptx::smem_u32(win);
+            const uint64_t w_desc = desc_k16(ptx::smem_u32(wsm), 1024, 128);
+            bool ok = true;
             int ti = 0;
-            for (long long tile = blockIdx.x; tile < args.tiles && ok; tile += gridDim.x, ti++) {
-                ok = ptx::mbar_wait(acc_empty, ((uint32_t)ti & 1u) ^ 1u, args.status);
-                if (ok) ok = ptx::mbar_wait(win_full, (uint32_t)ti & 1u, args.status);
+            for (long long tile = t_begin; tile < t_end && ok; tile++, ti++) {
+                const int buf = ti & 1;
+                ok = ptx::mbar_wait(acc_empty + buf, (((uint32_t)(ti >> 1)) & 1u) ^ 1u, args.status);
+                if (ok) ok = ptx::mbar_wait(win_full + buf, ((uint32_t)(ti >> 1)) & 1u, args.status);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
-                uint64_t row_desc = win_desc;
-                uint32_t a_col = tmem_base;
-                for (int r = 0; r < args.ky; r++, row_desc += row_units)
-                    for (int j = 0; j < args.KR; j++, a_col += 8u)
-                        ptx::umma_f16_ts(tmem_base + ACC_BASE, a_col, row_desc + 2u * (uint32_t)j, idesc,
-                                         (r | j) != 0 ? 1u : 0u);
-                ptx::umma_commit(win_empty);
-                ptx::umma_commit(acc_full);
-            }
-        }
-    } else if (warp < 6) {
-        // ---------------------------------------------------------------- weights -> tensor memory once, then epilogues
-        const int quarter = warp & 3;
-        const int row = quarter * 32 + lane;
-        bool ok = healthy;
-        if (ok) ok = ptx::mbar_wait(full_raw, 0u, args.status);
-        if (ok) {
-            for (int w4 = 0; w4 < args.KW; w4 += 4) {
-                const uint4 p = *reinterpret_cast<const uint4 *>(raw + (size_t)row * args.KW * 4 + w4 * 4);
-                const uint32_t words[4] = {p.x, p.y, p.z, p.w};
-                uint32_t cols[32];
-#pragma unroll
-                for (int wi = 0; wi < 4; wi++) {
-                    uint32_t r8[8];
-                    decode_word_bf16(words[wi], r8);
-#pragma unroll
-                    for (int j = 0; j < 8; j++) cols[8 * wi + j] = r8[j];
+                const int oy = (int)(tile % args.OH);
+                int slot = (oy * args.sy) % args.ring;                         // ring slot of the tile's first input row
+                uint64_t b_desc = w_desc;
+                const uint32_t d_tmem = tmem_base + (uint32_t)buf * 64u;
+#pragma unroll 1
+                for (int r = 0; r < args.ky; r++) {
+                    const uint64_t a_desc = desc_k16(win_addr + (uint32_t)(slot * args.WB), 16, 128);
+                    for (int j = 0; j < args.KR; j++, b_desc += 128)           // 2 KB per step, in 16-byte units
+                        ptx::umma_f16(d_tmem, a_desc + 2u * (uint32_t)j, b_desc, idesc, (r | j) != 0 ? 1u : 0u);
+                    if (++slot == args.ring) slot = 0;
                 }
-                ptx::tmem_st_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)w4 * 8u, cols);
+                ptx::umma_commit(win_empty + buf);
+                ptx::umma_commit(acc_full + buf);
             }
-            ptx::tmem_st_wait();
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(full_a);
         }
-        const long long n = (long long)quarter * 32 + lane;
-        float sc = 0.5f, bi = 0.0f;                   // operands carried +-2.0
-        if (n < args.N) {
-            if (args.scale) sc *= args.scale[n];
-            if (args.bias) bi = args.bias[n];
-        }
-        float *stage = stage_base + (warp - 2) * 512;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + ACC_BASE;
+    } else if (warp >= 2 && warp < 6) {
+        // ---------------------------------------------------------------- epilogue: one output pixel per thread
+        const int quarter = warp & 3;
+        const int p = quarter * 32 + lane;
+        const bool vec_ok = ((args.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(args.Y) & 15) == 0);
+        bool ok = healthy;
         int ti = 0;
-        for (long long tile = blockIdx.x; tile < args.tiles && ok; tile += gridDim.x, ti++) {
-            ok = ptx::mbar_wait(acc_full, (uint32_t)ti & 1u, args.status);
+        for (long long tile = t_begin; tile < t_end && ok; tile++, ti++) {
+            const int buf = ti & 1;
+            ok = ptx::mbar_wait(acc_full + buf, ((uint32_t)(ti >> 1)) & 1u, args.status);
             if (!ok) break;
             ptx::tc_fence_after_sync();
-            const long long m_base = tile * args.OW;                           // tile = b * OH + oy: first pixel of the row
+            const long long pix = p < args.OW ? tile * args.OW + p : -1;       // tile = b * OH + oy
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * 64u;
 #pragma unroll 1
-            for (int c = 0; c < args.Npad; c += 16) {
+            for (int c0 = 0; c0 < 64; c0 += 16) {
                 uint32_t v[16];
-                ptx::tmem_ld_x16(lane_addr + (uint32_t)c, v);
+                ptx::tmem_ld_x16(lane_addr + (uint32_t)c0, v);
                 ptx::tmem_ld_wait();
-                if (c + 16 >= args.Npad) {
+                if (c0 == 48) {
                     ptx::tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(acc_empty);
+                    if (lane == 0) ptx::mbar_arrive(acc_empty + buf);
                 }
-                epilogue_chunk_bf16(v, sc, bi, stage, args.Y, nullptr, m_base + c, m_base + args.OW, args.N, quarter * 32,
-                                    args.N, args.relu, lane);
+                if (pix >= 0 && c0 < args.N) {
+                    float f[16];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const float4 sc4 = *reinterpret_cast<const float4 *>(sc_s + c0 + 4 * q);
+                        const float4 bi4 = *reinterpret_cast<const float4 *>(bi_s + c0 + 4 * q);
+                        f[4 * q + 0] = fmaf(__uint_as_float(v[4 * q + 0]), sc4.x, bi4.x);
+                        f[4 * q + 1] = fmaf(__uint_as_float(v[4 * q + 1]), sc4.y, bi4.y);
+                        f[4 * q + 2] = fmaf(__uint_as_float(v[4 * q + 2]), sc4.z, bi4.z);
+                        f[4 * q + 3] = fmaf(__uint_as_float(v[4 * q + 3]), sc4.w, bi4.w);
+                    }
+                    const long long off = pix * args.N + c0;
+                    if (vec_ok && c0 + 16 <= args.N) {
+                        __align__(16) __nv_bfloat16 o[16];
+#pragma unroll
+                        for (int e = 0; e < 16; e++) o[e] = __float2bfloat16_rn(args.relu ? fmaxf(f[e], 0.0f) : f[e]);
+                        *reinterpret_cast<uint4 *>(args.Y + off) = *reinterpret_cast<const uint4 *>(o);
+                        *reinterpret_cast<uint4 *>(args.Y + off + 8) = *reinterpret_cast<const uint4 *>(o + 8);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 16; e++)
+                            if (c0 + e < args.N) args.Y[off + e] = __float2bfloat16_rn(args.relu ? fmaxf(f[e], 0.0f) : f[e]);
+                    }
+                }
             }
         }
-    } else {
-        // ---------------------------------------------------------------- window warps 6..9: fp32 NCHW rows -> bf16 [row][pixel][CP]
+    } else if (warp >= 6) {
+        // ---------------------------------------------------------------- window warps 6..9: fp32 NCHW rows -> bf16 ring rows
         const int t = threadIdx.x - 192;                                       // 0..127
         const int slots = args.WB / (CP * 2);                                   // pixel slots per window row
         bool ok = healthy;
         int ti = 0;
-        for (long long tile = blockIdx.x; tile < args.tiles && ok; tile += gridDim.x, ti++) {
-            ok = ptx::mbar_wait(win_empty, ((uint32_t)ti & 1u) ^ 1u, args.status);
-            if (!ok) break;
+        for (long long tile = t_begin; tile < t_end && ok; tile++, ti++) {
             const int b = (int)(tile / args.OH), oy = (int)(tile - (long long)b * args.OH);
             const float *img = args.X + (long long)b * args.C * args.H * args.W;
-            // a thread owns the slots t, t + 128, ... of every window row; the loads of four rows (up to 8 * CP values)
-            // are issued before any of them is consumed, so a tile costs a few memory round trips instead of one per slot
-            for (int r0 = 0; r0 < args.ky; r0 += 4) {
+            // first tile of this CTA or of an image: every row of the window; otherwise only the sy rows that are new
+            const bool refill = ti == 0 || oy == 0;
+            const int r_first = refill ? 0 : args.ky - args.sy;
+            // the sy new rows overwrite rows last read by the tile two back; a refill also those of the previous tile
+            if (ti >= 2) ok = ptx::mbar_wait(win_empty + (ti & 1), (((uint32_t)(ti >> 1)) & 1u) ^ 1u, args.status);
+            if (ok && refill && ti >= 1) ok = ptx::mbar_wait(win_empty + ((ti - 1) & 1), ((uint32_t)((ti - 1) >> 1)) & 1u, args.status);
+            if (!ok) break;
+            const int iy0 = oy * args.sy - args.py;
+            for (int r0 = r_first; r0 < args.ky; r0 += 2) {
                 for (int s0 = t; s0 < slots; s0 += 256) {
-                    float f[4][2][CP];
+                    float f[2][2][CP];
 #pragma unroll
-                    for (int dr = 0; dr < 4; dr++)
+                    for (int dr = 0; dr < 2; dr++)
 #pragma unroll
                         for (int u = 0; u < 2; u++) {
                             const int r = r0 + dr, sl = s0 + 128 * u;
-                            const int iy = oy * args.sy - args.py + r, ix = sl - args.px;
+                            const int iy = iy0 + r, ix = sl - args.px;
                             const bool in = r < args.ky && sl < slots && (unsigned)iy < (unsigned)args.H && (unsigned)ix < (unsigned)args.W;
                             const float *p = img + (long long)(in ? iy : 0) * args.W + (in ? ix : 0);
 #pragma unroll
                             for (int c = 0; c < CP; c++) f[dr][u][c] = (in && c < args.C) ? __ldg(p + (long long)c * args.H * args.W) : 0.0f;
                         }
 #pragma unroll
-                    for (int dr = 0; dr < 4; dr++)
+                    for (int dr = 0; dr < 2; dr++)
 #pragma unroll
                         for (int u = 0; u < 2; u++) {
                             const int r = r0 + dr, sl = s0 + 128 * u;
@@ -603,7 +649,8 @@ ternary_stem_rows_kernel(const __grid_constant__ CUtensorMap tmap_w, const StemR
                                 __align__(16) __nv_bfloat16 o[CP];
 #pragma unroll
                                 for (int c = 0; c < CP; c++) o[c] = __float2bfloat16_rn(f[dr][u][c]);
-                                uint8_t *dst = win + (size_t)r * args.WB + (size_t)sl * (CP * 2);
+                                const int slot = (oy * args.sy + r) % args.ring;
+                                uint8_t *dst = win + (size_t)slot * args.WB + (size_t)sl * (CP * 2);
                                 if (CP == 4) *reinterpret_cast<uint2 *>(dst) = *reinterpret_cast<const uint2 *>(o);
                                 else *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(o);
                             }
@@ -612,7 +659,7 @@ ternary_stem_rows_kernel(const __grid_constant__ CUtensorMap tmap_w, const StemR
             }
             ptx::fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(win_full);
+            if (lane == 0) ptx::mbar_arrive(win_full + (ti & 1));
         }
     }
     ptx::tc_fence_before_sync();
@@ -647,6 +694,11 @@ extern "C" int tmq_ternary_conv2d_s1_bf16(const void *X, const uint32_t *Wt, con
         return TMQ_ERR_ALIGN;
     const int halo_x = dx * (kx - 1), halo_y = dy * (ky - 1);
     if (halo_x + 16 > kSwBN) return TMQ_ERR_UNSUPPORTED;
+    {   // one input slice and at most 64 output channels: the pixel-major kernel, where it covers the layer
+        const int rc = launch_conv_pixel_major(X, Wt, scale, bias, residual, Y, B, H, W, C, N, ky, kx, py, px, dy, dx, relu,
+                                               status, (cudaStream_t)stream);
+        if (rc != TMQ_ERR_UNSUPPORTED) return rc;
+    }
     SwArgs a = {};
     a.scale = scale; a.bias = bias;
     a.residual = reinterpret_cast<const __nv_bfloat16 *>(residual);
@@ -720,40 +772,38 @@ extern "C" int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t 
     const int CP = 8 / sx, KR = (kx * CP + 15) / 16;
     const int OH = (H + 2 * py - ky) / sy + 1, OW = (W + 2 * px - kx) / sx + 1;
     if (OH <= 0 || OW <= 0) return TMQ_ERR_ARG;
-    const int Npad = (OW + 15) / 16 * 16;
-    if (ky * KR > 16 || Npad > 128 || N > 128 || (N & 7) != 0) return TMQ_ERR_UNSUPPORTED;
+    // one output row per tile (M = 128 pixels), all channels in one accumulator (N = 64), the ring must reuse rows
+    if (OW > 128 || N > 64 || sy >= ky || ky * KR > 24) return TMQ_ERR_UNSUPPORTED;
     if ((long long)B * OH > 0x7FFFFFFFll) return TMQ_ERR_UNSUPPORTED;
-    if (!aligned(X, 4) || !aligned(Wt, 16) || !aligned(Y, 16) || !aligned(status, 4)) return TMQ_ERR_ALIGN;
+    if (!aligned(X, 4) || !aligned(Wt, 16) || !aligned(Y, 2) || !aligned(status, 4)) return TMQ_ERR_ALIGN;
     StemRowsArgs a = {};
-    a.X = X; a.scale = scale; a.bias = bias;
+    a.X = X; a.Wt = Wt; a.scale = scale; a.bias = bias;
     a.Y = reinterpret_cast<__nv_bfloat16 *>(Y);
     a.B = B; a.C = C; a.H = H; a.W = W; a.OH = OH; a.OW = OW; a.N = N;
     a.ky = ky; a.kx = kx; a.sy = sy; a.sx = sx; a.py = py; a.px = px;
     a.KR = KR;
-    a.KW = (int)prepack_valid_words(Kp);
-    // a window row must hold every byte the MMAs of one filter row read: Npad rows 16 bytes apart, KR * 32 bytes each
-    a.WB = ((Npad - 1) * 16 + KR * 32 + 15) / 16 * 16;
-    a.Npad = Npad;
+    a.KS = (int)prepack_row_words(Kp, 0);
+    // a window row must hold every byte the MMAs of one filter row read: 128 rows 16 bytes apart, KR * 32 bytes each,
+    // and every pixel slot an output row can touch
+    const int need_mma = 127 * 16 + KR * 32, need_px = ((OW - 1) * sx + kx) * CP * 2;
+    a.WB = ((need_mma > need_px ? need_mma : need_px) + 15) / 16 * 16;
+    a.ring = ky + sy;
     a.tiles = (long long)B * OH;
     a.relu = relu; a.status = status;
-    if (a.KW > 16) return TMQ_ERR_UNSUPPORTED;
-    const int win_bytes = (ky * a.WB + 127) / 128 * 128;
-    const int smem = 8192 + 128 * 64 + win_bytes + 128 + 1024;
+    const int win_bytes = (a.ring * a.WB + 127) / 128 * 128;
+    const int smem = ky * KR * 2048 + win_bytes + 512 + 128 + 1024;
     if (smem > 100 * 1024) return TMQ_ERR_UNSUPPORTED;
-    CUtensorMap mw;
-    const long long KS = prepack_row_words(Kp, 0);
-    if (!make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)a.KW, (uint64_t)N, (uint64_t)KS * 4, (uint32_t)a.KW, 128,
-                     CU_TENSOR_MAP_SWIZZLE_NONE))
-        return TMQ_ERR_LAUNCH;
     const long long want = 2LL * kNumSMs;
-    const unsigned grid = (unsigned)(a.tiles < want ? a.tiles : want);
+    const long long grid = a.tiles < want ? a.tiles : want;
+    a.per_cta = (a.tiles + grid - 1) / grid;
+    const unsigned nblocks = (unsigned)((a.tiles + a.per_cta - 1) / a.per_cta);
     int rc;
     if (CP == 4) {
-        if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<4>, smem)) != TMQ_OK) return rc;
-        ternary_stem_rows_kernel<4><<<grid, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(mw, a);
+        if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<4>, 100 * 1024)) != TMQ_OK) return rc;   // the limit, not this call's size
+        ternary_stem_rows_kernel<4><<<nblocks, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(a);
     } else {
-        if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<8>, smem)) != TMQ_OK) return rc;
-        ternary_stem_rows_kernel<8><<<grid, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(mw, a);
+        if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<8>, 100 * 1024)) != TMQ_OK) return rc;
+        ternary_stem_rows_kernel<8><<<nblocks, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(a);
     }
     return launch_status();
 }

@@ -624,6 +624,146 @@ __global__ void __launch_bounds__(kResWarps * 32, 2) ternary_gemv_resident_dp4a_
     }
 }
 
+// 9 .. 16 activation rows in ONE pass: the decoded weight fragment of a k16 step is fed to NB = 2 MMAs (two 8-row
+// activation tiles), so the integer decode - the cost that bounds the one-tile kernel - is paid once for both.  Eight
+// warps and up to 128 registers per thread (two accumulator sets and two activation fragments per lane), two CTAs per
+// SM as above, so the next launch's rows still stream in under this launch's arithmetic.
+constexpr int kRowsWarps = 8;
+
+template <int KIND, int NB>
+__global__ void __launch_bounds__(kRowsWarps * 32, 2) ternary_gemv_resident_rows_kernel(const ResArgs a) {
+    using Acc = typename std::conditional<KIND == 0, float, int>::type;
+    constexpr int LK = (KIND == 0) ? 32 : 64;     // k per lane and slice: 2 / 4 packed words per channel
+    constexpr int LW = LK / 16;
+    extern __shared__ __align__(16) uint32_t wsm[];
+    uint64_t *bar = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(wsm) + a.bar_offset);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    int group0, G;
+    resident_groups(a, group0, G);
+    resident_prologue(a, wsm, bar, group0, G);
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // activations and outputs belong to the chain
+    __syncthreads();                                     // the barrier warp 0 initialised is visible to every warp
+
+    Acc acc[kResGroups][NB][4];
+#pragma unroll
+    for (int i = 0; i < kResGroups; i++)
+#pragma unroll
+        for (int b = 0; b < NB; b++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[i][b][j] = 0;
+
+    const int nslices = (int)((a.K + 4 * LK - 1) / (4 * LK));
+    constexpr int XR = 16;                         // 32 bf16 or 64 int8 activations of one row
+    uint32_t xr[NB][XR];
+    auto load_x = [&](int slice) {                 // rows g, g + 8, ...; zero beyond M or K
+        const long long k_lane = (long long)slice * (4 * LK) + LK * t;
+#pragma unroll
+        for (int b = 0; b < NB; b++)
+#pragma unroll
+            for (int q = 0; q < XR / 4; q++) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                const long long k = k_lane + (long long)q * (KIND == 0 ? 8 : 16);
+                const int m = 8 * b + g;
+                if (m < a.M && k < a.K) {
+                    const char *p = reinterpret_cast<const char *>(a.X) + ((long long)m * a.K + k) * (KIND == 0 ? 2 : 1);
+                    v = __ldg(reinterpret_cast<const uint4 *>(p));
+                }
+                xr[b][4 * q + 0] = v.x; xr[b][4 * q + 1] = v.y; xr[b][4 * q + 2] = v.z; xr[b][4 * q + 3] = v.w;
+            }
+    };
+    load_x(warp);
+    const bool ok = __syncthreads_and(ptx::mbar_wait(bar, 0, a.status));
+    for (int slice = warp; ok && slice < nslices; slice += kRowsWarps) {
+        if (slice != warp) load_x(slice);
+        const long long k_lane = (long long)slice * (4 * LK) + LK * t;
+        const bool k_ok = (k_lane >> 4) < a.KW;
+#pragma unroll
+        for (int i = 0; i < kResGroups; i++) {
+            if (i < G) {                            // warp-uniform: every lane takes part in the mma below
+                const uint32_t *p0 = wsm + (size_t)(i * 16 + g) * a.KS + (k_lane >> 4);
+                const uint32_t *p1 = p0 + (size_t)8 * a.KS;
+                uint32_t lo[LW], hi[LW];
+#pragma unroll
+                for (int w = 0; w < LW; w++) lo[w] = hi[w] = 0;
+                if (k_ok) {
+                    if (KIND == 0) {
+                        const uint2 u0 = *reinterpret_cast<const uint2 *>(p0), u1 = *reinterpret_cast<const uint2 *>(p1);
+                        lo[0] = u0.x; lo[1] = u0.y; hi[0] = u1.x; hi[1] = u1.y;
+                    } else {
+                        const uint4 u0 = *reinterpret_cast<const uint4 *>(p0), u1 = *reinterpret_cast<const uint4 *>(p1);
+                        lo[0] = u0.x; lo[1] = u0.y; lo[LW - 2] = u0.z; lo[LW - 1] = u0.w;
+                        hi[0] = u1.x; hi[1] = u1.y; hi[LW - 2] = u1.z; hi[LW - 1] = u1.w;
+                    }
+                }
+#pragma unroll
+                for (int w = 0; w < LW; w++) {
+                    if (KIND == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint32_t a0 = (lo[w] << (4 * j)) & 0xC000C000u, a2 = (lo[w] << (4 * j + 2)) & 0xC000C000u;
+                            const uint32_t a1 = (hi[w] << (4 * j)) & 0xC000C000u, a3 = (hi[w] << (4 * j + 2)) & 0xC000C000u;
+#pragma unroll
+                            for (int b = 0; b < NB; b++)
+                                mma_bf16(reinterpret_cast<float(&)[4]>(acc[i][b]), a0, a1, a2, a3, xr[b][8 * w + 2 * j],
+                                         xr[b][8 * w + 2 * j + 1]);
+                        }
+                    } else {
+                        const uint32_t table = 0x00FF0100u;
+                        const uint32_t l0 = lo[w] & 0x33333333u, l1 = (lo[w] >> 2) & 0x33333333u;
+                        const uint32_t h0 = hi[w] & 0x33333333u, h1 = (hi[w] >> 2) & 0x33333333u;
+                        const uint32_t e0 = __byte_perm(table, 0u, l0), e1 = __byte_perm(table, 0u, h0);
+                        const uint32_t e2 = __byte_perm(table, 0u, l1), e3 = __byte_perm(table, 0u, h1);
+                        const uint32_t f0 = __byte_perm(table, 0u, l0 >> 16), f1 = __byte_perm(table, 0u, h0 >> 16);
+                        const uint32_t f2 = __byte_perm(table, 0u, l1 >> 16), f3 = __byte_perm(table, 0u, h1 >> 16);
+#pragma unroll
+                        for (int b = 0; b < NB; b++) {
+                            mma_s8(reinterpret_cast<int(&)[4]>(acc[i][b]), e0, e1, e2, e3, xr[b][4 * w + 0], xr[b][4 * w + 1]);
+                            mma_s8(reinterpret_cast<int(&)[4]>(acc[i][b]), f0, f1, f2, f3, xr[b][4 * w + 2], xr[b][4 * w + 3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();   // every warp is done reading the packed rows: the area becomes the reduction buffer
+    if (!ok) return;   // uniform: the copies never completed and the status word says so
+    constexpr int MC = 8 * NB;                      // activation rows (columns of the reduction tile)
+    Acc *red = reinterpret_cast<Acc *>(wsm);        // [warp][group][16][MC]
+#pragma unroll
+    for (int i = 0; i < kResGroups; i++) {
+        if (i < G) {
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                Acc *r = red + ((size_t)(warp * kResGroups + i) * 16) * MC + 8 * b;
+                r[g * MC + 2 * t] = acc[i][b][0];
+                r[g * MC + 2 * t + 1] = acc[i][b][1];
+                r[(g + 8) * MC + 2 * t] = acc[i][b][2];
+                r[(g + 8) * MC + 2 * t + 1] = acc[i][b][3];
+            }
+        }
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < G * 16 * MC; o += kRowsWarps * 32) {
+        const int row = o & 15, col = (o >> 4) % MC, grp = o / (16 * MC);
+        const long long n = ((long long)group0 + grp) * 16 + row;
+        if (n < a.N && col < a.M) {
+            Acc s = 0;
+#pragma unroll
+            for (int w = 0; w < kRowsWarps; w++) s += red[((size_t)(w * kResGroups + grp) * 16 + row) * MC + col];
+            if (KIND == 1) {
+                reinterpret_cast<int *>(a.Y)[(long long)col * a.ldy + n] = (int)s;
+            } else {
+                const float sc = (a.scale ? a.scale[n] : 1.0f) * 0.5f;   // operands carried +-2.0
+                const float f = fmaf((float)s, sc, a.bias ? a.bias[n] : 0.0f);
+                if (a.out_f32) reinterpret_cast<float *>(a.Y)[(long long)col * a.ldy + n] = f;
+                else reinterpret_cast<__nv_bfloat16 *>(a.Y)[(long long)col * a.ldy + n] = __float2bfloat16_rn(f);
+            }
+        }
+    }
+}
+
 // Returns TMQ_ERR_UNSUPPORTED when the CTA's rows do not fit the shared-memory budget (the caller then streams).
 template <int KIND>
 static int launch_gemv_resident(ResArgs a, cudaStream_t st) {
@@ -632,7 +772,9 @@ static int launch_gemv_resident(ResArgs a, cudaStream_t st) {
     const long long G = (ngroups + grid - 1) / grid;
     if (G > kResGroups || ngroups > 0x7FFFFFFF || !a.status) return TMQ_ERR_UNSUPPORTED;
     long long smem = G * 16 * a.KS * 4;            // the row stride already carries the bank padding
-    const long long red_bytes = (long long)kResWarps * kResGroups * 16 * 8 * 4;
+    const bool rows16 = a.M > 8;                   // 9 .. 16 rows: the two-tile kernel (8 warps, 16 reduction columns)
+    const long long red_bytes = rows16 ? (long long)kRowsWarps * kResGroups * 16 * 16 * 4
+                                       : (long long)kResWarps * kResGroups * 16 * 8 * 4;
     if (smem < red_bytes) smem = red_bytes;
     a.bar_offset = (int)smem;                      // multiple of 16
     smem += 16;
@@ -649,6 +791,11 @@ static int launch_gemv_resident(ResArgs a, cudaStream_t st) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int rc;
+    if (rows16) {
+        cfg.blockDim = dim3(kRowsWarps * 32);
+        if ((rc = ensure_dynamic_smem(ternary_gemv_resident_rows_kernel<KIND, 2>, kResSmemMax, true)) != TMQ_OK) return rc;
+        return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_resident_rows_kernel<KIND, 2>, a));
+    }
     if (KIND == 1 && a.M == 1) {
         if ((rc = ensure_dynamic_smem(ternary_gemv_resident_dp4a_kernel<1>, kResSmemMax, true)) != TMQ_OK) return rc;
         return cuda_status(cudaLaunchKernelEx(&cfg, ternary_gemv_resident_dp4a_kernel<1>, a));
@@ -664,7 +811,7 @@ static int launch_gemv_resident(ResArgs a, cudaStream_t st) {
 static int check_gemv(const void *X, const uint32_t *Wt, const void *Y, long long M, long long N, long long K,
                       long long ldy, int elem) {
     if (!X || !Wt || !Y) return TMQ_ERR_ARG;
-    if (M <= 0 || M > 8 || N <= 0 || K <= 0 || ldy < N) return TMQ_ERR_ARG;
+    if (M <= 0 || M > 16 || N <= 0 || K <= 0 || ldy < N) return TMQ_ERR_ARG;
     if ((K * elem) % 16 != 0) return TMQ_ERR_UNSUPPORTED;
     if (!aligned(X, 16) || !aligned(Wt, 16)) return TMQ_ERR_ALIGN;
     return TMQ_OK;
@@ -683,6 +830,7 @@ extern "C" int tmq_ternary_gemv_bf16(const void *X, const uint32_t *Wt, const fl
         rc = launch_gemv_resident<0>(r, (cudaStream_t)stream);
         if (rc != TMQ_ERR_UNSUPPORTED) return rc;
     }
+    if (M > 8) return TMQ_ERR_UNSUPPORTED;   // the streaming fallback takes 8 rows per pass: the caller splits
     WideArgs a = {X, Wt, scale, bias, Y, M, N, K, prepack_valid_words(K), prepack_row_words(K, 0), ldy, 0, 0, out_f32};
     return launch_gemv_wide<0>(a, (cudaStream_t)stream);
 }
@@ -696,6 +844,7 @@ extern "C" int tmq_ternary_gemv_i8(const int8_t *X, const uint32_t *Wt, int32_t 
         rc = launch_gemv_resident<1>(r, (cudaStream_t)stream);
         if (rc != TMQ_ERR_UNSUPPORTED) return rc;
     }
+    if (M > 8) return TMQ_ERR_UNSUPPORTED;
     GemvArgs a = {X, Wt, nullptr, nullptr, Y, M, N, K, prepack_valid_words(K), prepack_row_words(K, 1), ldy, 0};
     return launch_gemv<1>(a, (cudaStream_t)stream);
 }

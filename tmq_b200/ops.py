@@ -519,14 +519,32 @@ def prepack(packed, columns, fmt=FMT_BF16):
     return out
 
 
+GEMV_ROWS = 16      # activation rows one skinny-kernel launch takes (1 .. 8: one MMA tile, 9 .. 16: two)
+
+
 def _pick_path(path, M):
-    """auto: up to 16 rows go through the skinny kernel in passes of 8 (measured faster than one 32-row tensor-core
-    tile there), anything taller through the tiled tensor-core kernel."""
+    """auto: up to 32 rows go through the skinny kernel (one or two passes of up to 16 rows), anything taller through
+    the tiled tensor-core kernel, whose single issuing thread cannot feed the tensor core on so few rows."""
     if path != "auto":
         return path
-    if M <= 16:
+    if M <= 2 * GEMV_ROWS:
         return "gemv"
     return "tiles"
+
+
+def _skinny_passes(call, M):
+    """Runs call(m0, rows) over the M rows in passes of up to GEMV_ROWS; a pass the resident kernel cannot take (one
+    SM's share of the weights beyond its shared-memory budget) is split into the 8-row passes of the streaming kernel."""
+    m0 = 0
+    while m0 < M:
+        rows = min(GEMV_ROWS, M - m0)
+        rc = call(m0, rows)
+        if rc == -6 and rows > 8:
+            rc = call(m0, 8)
+            if rc == 0:
+                rc = call(m0 + 8, rows - 8)
+        check(rc, "ternary_gemv")
+        m0 += rows
 
 
 def _check_weights(name, wt, N, K, fmt):
@@ -567,10 +585,9 @@ def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16
     with torch.cuda.device(x.device):
         if path == "gemv":
             esz = y.element_size()
-            for m0 in range(0, M, 8):
-                check(lib().tmq_ternary_gemv_bf16(ctypes.c_void_p(x.data_ptr() + m0 * K * 2), _ptr(wt), psc, pbi,
-                                                  ctypes.c_void_p(y.data_ptr() + m0 * ldy * esz), min(8, M - m0), N, K,
-                                                  ldy, f32, _ptr(st), _stream(x)), "ternary_gemv")
+            _skinny_passes(lambda m0, rows: lib().tmq_ternary_gemv_bf16(
+                ctypes.c_void_p(x.data_ptr() + m0 * K * 2), _ptr(wt), psc, pbi, ctypes.c_void_p(y.data_ptr() + m0 * ldy * esz),
+                rows, N, K, ldy, f32, _ptr(st), _stream(x)), M)
         elif path == "tiles":
             check(lib().tmq_ternary_gemm_bf16(_ptr(x), _ptr(wt), psc, pbi, _ptr(y), M, N, K, ldy, f32, _ptr(st),
                                               _stream(x)), "ternary_gemm")
@@ -595,10 +612,9 @@ def ternary_gemm_i8(x, wt, columns, path="auto"):
     st = gemm_status_word(x.device)
     with torch.cuda.device(x.device):
         if path == "gemv":
-            for m0 in range(0, M, 8):
-                check(lib().tmq_ternary_gemv_i8(ctypes.c_void_p(x.data_ptr() + m0 * K), _ptr(wt),
-                                                ctypes.c_void_p(y.data_ptr() + m0 * N * 4), min(8, M - m0), N, K, N,
-                                                _ptr(st), _stream(x)), "ternary_gemv_i8")
+            _skinny_passes(lambda m0, rows: lib().tmq_ternary_gemv_i8(
+                ctypes.c_void_p(x.data_ptr() + m0 * K), _ptr(wt), ctypes.c_void_p(y.data_ptr() + m0 * N * 4), rows, N, K, N,
+                _ptr(st), _stream(x)), M)
         elif path == "tiles":
             check(lib().tmq_ternary_gemm_i8(_ptr(x), _ptr(wt), _ptr(y), M, N, K, N, _ptr(st), _stream(x)),
                   "ternary_gemm_i8")
