@@ -132,29 +132,34 @@ ternary_conv_kernel(const __grid_constant__ CUtensorMap tmap_w, const ConvArgs a
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0 && healthy) {
+        // the whole warp walks the loop (uniform waits and descriptor arithmetic), one elected lane issues
+        if (healthy) {
             constexpr uint32_t idesc = ((KIND == CONV_BF16 ? 1u : 2u) << 4) | (1u << 7) | (1u << 10) |
                                        ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; kb++) {
                 const int s = kb % kConvStages;
                 const uint32_t ph = (uint32_t)(kb / kConvStages) & 1u;
-                ok = ptx::mbar_wait(full_a + s, ph, args.status);
-                if (ok) ok = ptx::mbar_wait(full_b + s, ph, args.status);
+                ok = ptx::mbar_wait_warp(full_a + s, ph, args.status);
+                if (ok) ok = ptx::mbar_wait_warp(full_b + s, ph, args.status);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t a_tmem = tmem_base + BN + (uint32_t)s * A_COLS;
                 const uint64_t b_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES));
+                if (ptx::elect_one()) {
 #pragma unroll
-                for (int k4 = 0; k4 < 4; k4++) {     // 32 bytes of K per instruction
-                    if (KIND == CONV_BF16)
-                        ptx::umma_f16_ts(tmem_base, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
-                    else
-                        ptx::umma_i8_ts(tmem_base, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                    for (int k4 = 0; k4 < 4; k4++) {     // 32 bytes of K per instruction
+                        if (KIND == CONV_BF16)
+                            ptx::umma_f16_ts(tmem_base, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                        else
+                            ptx::umma_i8_ts(tmem_base, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                    }
+                    ptx::umma_commit(empty + s);
                 }
-                ptx::umma_commit(empty + s);
+                __syncwarp();
             }
-            if (ok) ptx::umma_commit(acc_full);
+            if (ok && ptx::elect_one()) ptx::umma_commit(acc_full);
+            __syncwarp();
         }
     } else if (warp < 6) {
         // ---------------------------------------------------------------- decode warps, then epilogue

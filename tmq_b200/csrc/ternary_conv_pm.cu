@@ -147,7 +147,8 @@ ternary_conv_pm_kernel(const __grid_constant__ CUtensorMap tmap_x, const PmArgs 
         }
     } else if (warp <= 2) {
         // ---------------------------------------------------------------- MMA issuer of stream (warp - 1)
-        if (lane == 0 && healthy) {
+        // the whole warp walks the loop (uniform waits and descriptor arithmetic), one elected lane issues
+        if (healthy) {
             const int s = warp - 1;
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((128u >> 4) << 24);
             const uint64_t w_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L.w_off));
@@ -156,22 +157,25 @@ ternary_conv_pm_kernel(const __grid_constant__ CUtensorMap tmap_x, const PmArgs 
             for (long long tile = blockIdx.x + (long long)s * gridDim.x; tile < args.tiles && ok; tile += 2LL * gridDim.x, j++) {
                 const int buf = j & 1, slot = s * 2 + buf;                     // accumulator buffer and input stage alternate together
                 const uint32_t ph = ((uint32_t)(j >> 1)) & 1u;
-                ok = ptx::mbar_wait(acc_empty + slot, ph ^ 1u, args.status);
-                if (ok) ok = ptx::mbar_wait(full_in + slot, ph, args.status);
+                ok = ptx::mbar_wait_warp(acc_empty + slot, ph ^ 1u, args.status);
+                if (ok) ok = ptx::mbar_wait_warp(full_in + slot, ph, args.status);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const uint64_t in_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L.in_off + slot * args.region_bytes));
                 const uint32_t d_tmem = tmem_base + (uint32_t)slot * 64u;
+                if (ptx::elect_one()) {
 #pragma unroll 1
-                for (int tap = 0; tap < ntaps; tap++) {
-                    const uint64_t a_desc = in_desc + (uint32_t)(shtab[tap] * 8);   // the tap's row shift, in 16-byte units
-                    const uint64_t b_desc = w_desc + (uint32_t)(tap * 512);          // 8 KB per tap
+                    for (int tap = 0; tap < ntaps; tap++) {
+                        const uint64_t a_desc = in_desc + (uint32_t)(shtab[tap] * 8);   // the tap's row shift, in 16-byte units
+                        const uint64_t b_desc = w_desc + (uint32_t)(tap * 512);          // 8 KB per tap
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; k4++)
-                        ptx::umma_f16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (tap | k4) ? 1u : 0u);
+                        for (int k4 = 0; k4 < 4; k4++)
+                            ptx::umma_f16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (tap | k4) ? 1u : 0u);
+                    }
+                    ptx::umma_commit(empty_in + slot);
+                    ptx::umma_commit(acc_full + slot);
                 }
-                ptx::umma_commit(empty_in + slot);
-                ptx::umma_commit(acc_full + slot);
+                __syncwarp();
             }
         }
     } else {
@@ -191,11 +195,20 @@ ternary_conv_pm_kernel(const __grid_constant__ CUtensorMap tmap_x, const PmArgs 
             const int oy = oy0 + r, ox = ox0 + jj;
             const bool valid = r < args.R && jj < args.Wt_cols && oy < args.OH && ox < args.OW;
             const long long pix = valid ? ((long long)(b * args.OH + oy) * args.OW + ox) : -1;
+            // this pixel's residual row is requested before the accumulator is waited for: its latency hides under the
+            // multiplications still in flight
+            uint4 rv[8];
+            const bool pre = args.residual != nullptr && vec_ok && pix >= 0;
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                rv[q] = make_uint4(0, 0, 0, 0);
+                if (pre && 8 * q < args.N) rv[q] = __ldg(reinterpret_cast<const uint4 *>(args.residual + pix * args.N + 8 * q));
+            }
             ok = ptx::mbar_wait(acc_full + slot, ((uint32_t)(j >> 1)) & 1u, args.status);
             if (!ok) break;
             ptx::tc_fence_after_sync();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)slot * 64u;
-#pragma unroll 1
+#pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 16) {
                 uint32_t v[16];
                 ptx::tmem_ld_x16(lane_addr + (uint32_t)c0, v);
@@ -219,10 +232,8 @@ ternary_conv_pm_kernel(const __grid_constant__ CUtensorMap tmap_x, const PmArgs 
                     const long long off = pix * args.N + c0;
                     if (vec_ok && c0 + 16 <= args.N) {
                         if (args.residual) {
-                            const uint4 r0 = __ldg(reinterpret_cast<const uint4 *>(args.residual + off));
-                            const uint4 r1 = __ldg(reinterpret_cast<const uint4 *>(args.residual + off + 8));
-                            const __nv_bfloat16 *rb0 = reinterpret_cast<const __nv_bfloat16 *>(&r0);
-                            const __nv_bfloat16 *rb1 = reinterpret_cast<const __nv_bfloat16 *>(&r1);
+                            const __nv_bfloat16 *rb0 = reinterpret_cast<const __nv_bfloat16 *>(&rv[c0 / 8]);
+                            const __nv_bfloat16 *rb1 = reinterpret_cast<const __nv_bfloat16 *>(&rv[c0 / 8 + 1]);
 #pragma unroll
                             for (int e = 0; e < 8; e++) {
                                 f[e] += __bfloat162float(rb0[e]);

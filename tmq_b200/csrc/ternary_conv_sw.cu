@@ -200,11 +200,7 @@ ternary_conv_sw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         // ---------------------------------------------------------------- MMA issuer (keep this loop small)
         // The whole warp walks the loop - waits, stage counters and descriptor arithmetic are warp-uniform - and one elected
         // lane issues the MMAs and commits.
-#ifdef TMQ_SW_LANE0
-        if (lane == 0 && healthy) {
-#else
         if (healthy) {
-#endif
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(nsubcols >> 3) << 17) | ((128u >> 4) << 24);
             const uint32_t sub_units = (uint32_t)(args.region_rows * 8);       // next sub-tile's region, in 16-byte units
             int si = 0, sa = 0, ka = 0;
@@ -230,11 +226,7 @@ ternary_conv_sw_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                         const uint32_t a_tmem = tmem_base + A_BASE + (uint32_t)sa * 32u;
                         uint64_t b_desc = in_desc + (uint32_t)(shtab[tap] * 8);    // the tap's row shift, in 16-byte units
                         uint32_t d_tmem = tmem_base;
-#ifdef TMQ_SW_LANE0
-                        {
-#else
                         if (ptx::elect_one()) {
-#endif
                             for (int g = 0; g < args.nsub; g++, b_desc += sub_units, d_tmem += (uint32_t)nsubcols) {
 #pragma unroll
                                 for (int k4 = 0; k4 < 4; k4++)
@@ -531,8 +523,8 @@ ternary_stem_rows_kernel(const StemRowsArgs args) {
     if (t_end > args.tiles) t_end = args.tiles;
 
     if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0 && healthy) {
+        // ---------------------------------------------------------------- MMA issuer (whole warp walks the loop, one lane issues)
+        if (healthy) {
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((128u >> 4) << 24);
             const uint32_t win_addr = ptx::smem_u32(win);
             const uint64_t w_desc = desc_k16(ptx::smem_u32(wsm), 1024, 128);
@@ -540,23 +532,26 @@ ternary_stem_rows_kernel(const StemRowsArgs args) {
             int ti = 0;
             for (long long tile = t_begin; tile < t_end && ok; tile++, ti++) {
                 const int buf = ti & 1;
-                ok = ptx::mbar_wait(acc_empty + buf, (((uint32_t)(ti >> 1)) & 1u) ^ 1u, args.status);
-                if (ok) ok = ptx::mbar_wait(win_full + buf, ((uint32_t)(ti >> 1)) & 1u, args.status);
+                ok = ptx::mbar_wait_warp(acc_empty + buf, (((uint32_t)(ti >> 1)) & 1u) ^ 1u, args.status);
+                if (ok) ok = ptx::mbar_wait_warp(win_full + buf, ((uint32_t)(ti >> 1)) & 1u, args.status);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const int oy = (int)(tile % args.OH);
                 int slot = (oy * args.sy) % args.ring;                         // ring slot of the tile's first input row
                 uint64_t b_desc = w_desc;
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * 64u;
+                if (ptx::elect_one()) {
 #pragma unroll 1
-                for (int r = 0; r < args.ky; r++) {
-                    const uint64_t a_desc = desc_k16(win_addr + (uint32_t)(slot * args.WB), 16, 128);
-                    for (int j = 0; j < args.KR; j++, b_desc += 128)           // 2 KB per step, in 16-byte units
-                        ptx::umma_f16(d_tmem, a_desc + 2u * (uint32_t)j, b_desc, idesc, (r | j) != 0 ? 1u : 0u);
-                    if (++slot == args.ring) slot = 0;
+                    for (int r = 0; r < args.ky; r++) {
+                        const uint64_t a_desc = desc_k16(win_addr + (uint32_t)(slot * args.WB), 16, 128);
+                        for (int j = 0; j < args.KR; j++, b_desc += 128)       // 2 KB per step, in 16-byte units
+                            ptx::umma_f16(d_tmem, a_desc + 2u * (uint32_t)j, b_desc, idesc, (r | j) != 0 ? 1u : 0u);
+                        if (++slot == args.ring) slot = 0;
+                    }
+                    ptx::umma_commit(win_empty + buf);
+                    ptx::umma_commit(acc_full + buf);
                 }
-                ptx::umma_commit(win_empty + buf);
-                ptx::umma_commit(acc_full + buf);
+                __syncwarp();
             }
         }
     } else if (warp >= 2 && warp < 6) {

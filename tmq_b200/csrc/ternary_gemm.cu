@@ -169,7 +169,9 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0 && healthy) {
+        // The whole warp walks the loop - waits, stage arithmetic and descriptors are warp-uniform, which lets them live
+        // in uniform registers - and one elected lane issues the MMAs and commits.
+        if (healthy) {
             constexpr uint32_t idesc = (KT::C_FMT << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
             long long it = 0;
             int ti = 0;
@@ -178,33 +180,37 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 const int buf = ACC_BUFS == 2 ? (ti & 1) : 0;
                 const uint32_t use = (uint32_t)(ACC_BUFS == 2 ? (ti >> 1) : ti);
                 // the epilogue must have drained this accumulator (its previous use)
-                ok = ptx::mbar_wait(acc_empty + buf, (use & 1u) ^ 1u, args.status);
+                ok = ptx::mbar_wait_warp(acc_empty + buf, (use & 1u) ^ 1u, args.status);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * ACC_COLS;
                 for (int kb = 0; kb < nkb; kb++, it++) {
                     const int s = (int)(it % kStages);
                     const uint32_t ph = (uint32_t)(it / kStages) & 1u;
-                    ok = ptx::mbar_wait(full_a + s, ph, args.status);
+                    ok = ptx::mbar_wait_warp(full_a + s, ph, args.status);
                     if (!ok) break;
                     ptx::tc_fence_after_sync();
                     const uint64_t a_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::A_OFF + s * L::A_BYTES));
                     const uint64_t b_desc = ptx::umma_desc_sw128(ptx::smem_u32(smem + L::B_OFF + s * L::B_BYTES));
                     const uint32_t a_tmem = tmem_base + A_BASE + (uint32_t)s * A_COLS;
+                    if (ptx::elect_one()) {
 #pragma unroll
-                    for (int k4 = 0; k4 < kRowBytes / 32; k4++) {  // 32 bytes of K per instruction (16 bf16 / 32 int8)
-                        const uint32_t accum = (kb > 0 || k4 > 0) ? 1u : 0u;
-                        if (TA) {
-                            if (KIND == KIND_BF16) ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, accum);
-                            else ptx::umma_i8_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, accum);
-                        } else {
-                            if (KIND == KIND_BF16) ptx::umma_f16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
-                            else ptx::umma_i8(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                        for (int k4 = 0; k4 < kRowBytes / 32; k4++) {  // 32 bytes of K per instruction (16 bf16 / 32 int8)
+                            const uint32_t accum = (kb > 0 || k4 > 0) ? 1u : 0u;
+                            if (TA) {
+                                if (KIND == KIND_BF16) ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, accum);
+                                else ptx::umma_i8_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, accum);
+                            } else {
+                                if (KIND == KIND_BF16) ptx::umma_f16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                                else ptx::umma_i8(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accum);
+                            }
                         }
+                        ptx::umma_commit(empty + s);  // stage reusable once these MMAs have read it
                     }
-                    ptx::umma_commit(empty + s);  // stage reusable once these MMAs have read it
+                    __syncwarp();
                 }
-                if (ok) ptx::umma_commit(acc_full + buf);
+                if (ok && ptx::elect_one()) ptx::umma_commit(acc_full + buf);
+                __syncwarp();
             }
         }
     } else if (warp < 6) {
