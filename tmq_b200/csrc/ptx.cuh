@@ -97,6 +97,24 @@ __device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint
                  : "memory");
 }
 
+// 256-bit global accesses (32-byte aligned): a lane moves a whole 32-byte sector with one request.  An epilogue whose
+// threads each own an output row otherwise writes every sector with two 16-byte requests from two instructions.
+struct u32x8 {
+    uint32_t v[8];
+};
+__device__ __forceinline__ u32x8 ldg_v8(const void *p) {
+    u32x8 r;
+    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]), "=r"(r.v[7])
+                 : "l"(p));
+    return r;
+}
+__device__ __forceinline__ void stg_v8(void *p, const u32x8 &r) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(p), "r"(r.v[0]), "r"(r.v[1]), "r"(r.v[2]), "r"(r.v[3]), "r"(r.v[4]), "r"(r.v[5]), "r"(r.v[6]), "r"(r.v[7])
+                 : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------------- tcgen05 / TMEM
 
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_slot, uint32_t ncols) {  // whole warp

@@ -183,8 +183,9 @@ ternary_conv_pm_kernel(const __grid_constant__ CUtensorMap tmap_x, const PmArgs 
         const int s = (warp - 3) >> 2;
         const int quarter = warp & 3;
         const int p = quarter * 32 + lane;                                     // this thread's output position of the tile
-        const bool vec_ok = ((args.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(args.Y) & 15) == 0) &&
-                            ((reinterpret_cast<uintptr_t>(args.residual) & 15) == 0);
+        // a chunk of 16 channels is one 32-byte sector of the pixel's row: one 256-bit access when rows and bases allow
+        const bool vec_ok = ((args.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(args.Y) & 31) == 0) &&
+                            ((reinterpret_cast<uintptr_t>(args.residual) & 31) == 0);
         bool ok = healthy;
         int j = 0;
         for (long long tile = blockIdx.x + (long long)s * gridDim.x; tile < args.tiles && ok; tile += 2LL * gridDim.x, j++) {
@@ -197,12 +198,13 @@ ternary_conv_pm_kernel(const __grid_constant__ CUtensorMap tmap_x, const PmArgs 
             const long long pix = valid ? ((long long)(b * args.OH + oy) * args.OW + ox) : -1;
             // this pixel's residual row is requested before the accumulator is waited for: its latency hides under the
             // multiplications still in flight
-            uint4 rv[8];
+            ptx::u32x8 rv[4];
             const bool pre = args.residual != nullptr && vec_ok && pix >= 0;
 #pragma unroll
-            for (int q = 0; q < 8; q++) {
-                rv[q] = make_uint4(0, 0, 0, 0);
-                if (pre && 8 * q < args.N) rv[q] = __ldg(reinterpret_cast<const uint4 *>(args.residual + pix * args.N + 8 * q));
+            for (int q = 0; q < 4; q++) {
+#pragma unroll
+                for (int e = 0; e < 8; e++) rv[q].v[e] = 0u;
+                if (pre && 16 * q < args.N) rv[q] = ptx::ldg_v8(args.residual + pix * args.N + 16 * q);
             }
             ok = ptx::mbar_wait(acc_full + slot, ((uint32_t)(j >> 1)) & 1u, args.status);
             if (!ok) break;
@@ -232,19 +234,18 @@ ternary_conv_pm_kernel(const __grid_constant__ CUtensorMap tmap_x, const PmArgs 
                     const long long off = pix * args.N + c0;
                     if (vec_ok && c0 + 16 <= args.N) {
                         if (args.residual) {
-                            const __nv_bfloat16 *rb0 = reinterpret_cast<const __nv_bfloat16 *>(&rv[c0 / 8]);
-                            const __nv_bfloat16 *rb1 = reinterpret_cast<const __nv_bfloat16 *>(&rv[c0 / 8 + 1]);
+                            const __nv_bfloat16 *rb = reinterpret_cast<const __nv_bfloat16 *>(&rv[c0 / 16]);
 #pragma unroll
-                            for (int e = 0; e < 8; e++) {
-                                f[e] += __bfloat162float(rb0[e]);
-                                f[8 + e] += __bfloat162float(rb1[e]);
-                            }
+                            for (int e = 0; e < 16; e++) f[e] += __bfloat162float(rb[e]);
                         }
-                        __align__(16) __nv_bfloat16 o[16];
+                        ptx::u32x8 o;
 #pragma unroll
-                        for (int e = 0; e < 16; e++) o[e] = __float2bfloat16_rn(args.relu ? fmaxf(f[e], 0.0f) : f[e]);
-                        *reinterpret_cast<uint4 *>(args.Y + off) = *reinterpret_cast<const uint4 *>(o);
-                        *reinterpret_cast<uint4 *>(args.Y + off + 8) = *reinterpret_cast<const uint4 *>(o + 8);
+                        for (int e = 0; e < 8; e++) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(args.relu ? fmaxf(f[2 * e], 0.0f) : f[2 * e],
+                                                                           args.relu ? fmaxf(f[2 * e + 1], 0.0f) : f[2 * e + 1]);
+                            o.v[e] = *reinterpret_cast<const uint32_t *>(&h);
+                        }
+                        ptx::stg_v8(args.Y + off, o);
                     } else {
 #pragma unroll
                         for (int e = 0; e < 16; e++) {                         // unrolled: f stays in registers

@@ -452,10 +452,20 @@ struct StemRowsArgs {
     long long tiles; // B * OH
     long long per_cta;   // tiles per CTA (contiguous)
     int relu;
+    int use_tma;     // the sy new rows of a tile arrive by TMA in a staging ring (needs W % 4 == 0)
+    int stg_bytes;   // bytes of one staging slot: C planes x sy rows x W floats, rounded up to 128
     int *status;
 };
 
-constexpr int kStemRowsThreads = 320;   // warp 0: spare, warp 1: MMA, warps 2-5: epilogue, warps 6-9: window
+constexpr int kStemRowsThreads = 320;   // warp 0: row copies (TMA), warp 1: MMA, warps 2-5: epilogue, warps 6-9: window
+constexpr int kStemStages = 4;          // staging slots of fp32 input rows
+
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(ptx::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(ptx::smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
 
 __device__ __forceinline__ uint64_t desc_k16(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     // unswizzled K-major: K-adjacent 16-byte chunk lbo_bytes on (leading byte offset), next 8 rows sbo_bytes on (stride)
@@ -469,7 +479,7 @@ __device__ __forceinline__ uint64_t desc_k16(uint32_t addr, uint32_t lbo_bytes, 
 
 template <int CP>
 __global__ void __launch_bounds__(kStemRowsThreads, 2)
-ternary_stem_rows_kernel(const StemRowsArgs args) {
+ternary_stem_rows_kernel(const __grid_constant__ CUtensorMap tmap_x, const StemRowsArgs args) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int ksteps = args.ky * args.KR;
@@ -481,7 +491,9 @@ ternary_stem_rows_kernel(const StemRowsArgs args) {
     // every barrier exists twice, for even and odd tiles: a producer can then never complete two phases of one barrier
     // before its consumer has looked at the first (a parity wait cannot tell phase n from phase n + 2)
     uint64_t *win_full = bars, *win_empty = bars + 2, *acc_full = bars + 4, *acc_empty = bars + 6;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 8);
+    uint64_t *stg_full = bars + 8, *stg_empty = bars + 8 + kStemStages;        // staging ring of fp32 rows
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 8 + 2 * kStemStages);
+    uint8_t *stg = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(tmem_slot + 4) + 127) & ~uintptr_t(127));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr uint32_t TMEM_COLS = 128;                                        // two 64-column accumulators
 
@@ -492,7 +504,12 @@ ternary_stem_rows_kernel(const StemRowsArgs args) {
             ptx::mbar_init(acc_full + b, 1);
             ptx::mbar_init(acc_empty + b, 4);
         }
+        for (int i = 0; i < kStemStages; i++) {
+            ptx::mbar_init(stg_full + i, 1);
+            ptx::mbar_init(stg_empty + i, 4);
+        }
         ptx::fence_mbar_init();
+        if (args.use_tma) ptx::prefetch_tensormap(&tmap_x);
     }
     if (threadIdx.x < 64) {
         const int n = threadIdx.x;
@@ -522,7 +539,24 @@ ternary_stem_rows_kernel(const StemRowsArgs args) {
     long long t_end = t_begin + args.per_cta;
     if (t_end > args.tiles) t_end = args.tiles;
 
-    if (warp == 1) {
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA: the sy new input rows of every non-refill tile
+        if (lane == 0 && healthy && args.use_tma) {
+            bool ok = true;
+            int ti = 0, n = 0;                                                 // n counts the tiles that arrive by TMA
+            for (long long tile = t_begin; tile < t_end && ok; tile++, ti++) {
+                const int b = (int)(tile / args.OH), oy = (int)(tile - (long long)b * args.OH);
+                if (ti == 0 || oy == 0) continue;                              // refill: the window warps load it themselves
+                const int sg = n % kStemStages;
+                ok = ptx::mbar_wait(stg_empty + sg, (((uint32_t)(n / kStemStages)) & 1u) ^ 1u, args.status);
+                if (!ok) break;
+                ptx::mbar_arrive_expect_tx(stg_full + sg, (uint32_t)(args.C * args.sy * args.W * 4));
+                tma_load_3d(stg + (size_t)sg * args.stg_bytes, &tmap_x, stg_full + sg, 0, oy * args.sy - args.py + args.ky - args.sy,
+                            b * args.C);
+                n++;
+            }
+        }
+    } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer (whole warp walks the loop, one lane issues)
         if (healthy) {
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((128u >> 4) << 24);
@@ -558,7 +592,8 @@ ternary_stem_rows_kernel(const StemRowsArgs args) {
         // ---------------------------------------------------------------- epilogue: one output pixel per thread
         const int quarter = warp & 3;
         const int p = quarter * 32 + lane;
-        const bool vec_ok = ((args.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(args.Y) & 15) == 0);
+        // a chunk of 16 channels is one 32-byte sector of the pixel's row: one 256-bit store when rows and base allow
+        const bool vec_ok = ((args.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(args.Y) & 31) == 0);
         bool ok = healthy;
         int ti = 0;
         for (long long tile = t_begin; tile < t_end && ok; tile++, ti++) {
@@ -591,11 +626,14 @@ ternary_stem_rows_kernel(const StemRowsArgs args) {
                     }
                     const long long off = pix * args.N + c0;
                     if (vec_ok && c0 + 16 <= args.N) {
-                        __align__(16) __nv_bfloat16 o[16];
+                        ptx::u32x8 o;
 #pragma unroll
-                        for (int e = 0; e < 16; e++) o[e] = __float2bfloat16_rn(args.relu ? fmaxf(f[e], 0.0f) : f[e]);
-                        *reinterpret_cast<uint4 *>(args.Y + off) = *reinterpret_cast<const uint4 *>(o);
-                        *reinterpret_cast<uint4 *>(args.Y + off + 8) = *reinterpret_cast<const uint4 *>(o + 8);
+                        for (int e = 0; e < 8; e++) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(args.relu ? fmaxf(f[2 * e], 0.0f) : f[2 * e],
+                                                                           args.relu ? fmaxf(f[2 * e + 1], 0.0f) : f[2 * e + 1]);
+                            o.v[e] = *reinterpret_cast<const uint32_t *>(&h);
+                        }
+                        ptx::stg_v8(args.Y + off, o);
                     } else {
 #pragma unroll
                         for (int e = 0; e < 16; e++)
@@ -609,7 +647,7 @@ ternary_stem_rows_kernel(const StemRowsArgs args) {
         const int t = threadIdx.x - 192;                                       // 0..127
         const int slots = args.WB / (CP * 2);                                   // pixel slots per window row
         bool ok = healthy;
-        int ti = 0;
+        int ti = 0, n_tma = 0;
         for (long long tile = t_begin; tile < t_end && ok; tile++, ti++) {
             const int b = (int)(tile / args.OH), oy = (int)(tile - (long long)b * args.OH);
             const float *img = args.X + (long long)b * args.C * args.H * args.W;
@@ -620,14 +658,45 @@ ternary_stem_rows_kernel(const StemRowsArgs args) {
             if (ti >= 2) ok = ptx::mbar_wait(win_empty + (ti & 1), (((uint32_t)(ti >> 1)) & 1u) ^ 1u, args.status);
             if (ok && refill && ti >= 1) ok = ptx::mbar_wait(win_empty + ((ti - 1) & 1), ((uint32_t)((ti - 1) >> 1)) & 1u, args.status);
             if (!ok) break;
+            if (args.use_tma && !refill) {
+                // the new rows are already in shared memory as fp32 [channel][row][W]: convert them into the ring
+                const int sg = n_tma % kStemStages;
+                ok = ptx::mbar_wait(stg_full + sg, ((uint32_t)(n_tma / kStemStages)) & 1u, args.status);
+                if (!ok) break;
+                const float *src = reinterpret_cast<const float *>(stg + (size_t)sg * args.stg_bytes);
+                for (int i = t; i < args.sy * slots; i += 128) {
+                    const int dr = i / slots, sl = i - dr * slots;
+                    const int ix = sl - args.px;
+                    __align__(16) __nv_bfloat16 o[CP];
+#pragma unroll
+                    for (int c = 0; c < CP; c++) {
+                        const float v = ((unsigned)ix < (unsigned)args.W && c < args.C) ? src[(c * args.sy + dr) * args.W + ix] : 0.0f;
+                        o[c] = __float2bfloat16_rn(v);
+                    }
+                    const int slot = (oy * args.sy + args.ky - args.sy + dr) % args.ring;
+                    uint8_t *dst = win + (size_t)slot * args.WB + (size_t)sl * (CP * 2);
+                    if (CP == 4) *reinterpret_cast<uint2 *>(dst) = *reinterpret_cast<const uint2 *>(o);
+                    else *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(o);
+                }
+                n_tma++;
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(stg_empty + sg);
+                    ptx::mbar_arrive(win_full + (ti & 1));
+                }
+                continue;
+            }
             const int iy0 = oy * args.sy - args.py;
+            // two rows x three slots per thread in one batch: every load of a (non-refill) tile is in flight before the
+            // first value is consumed, so a tile costs one memory round trip
             for (int r0 = r_first; r0 < args.ky; r0 += 2) {
-                for (int s0 = t; s0 < slots; s0 += 256) {
-                    float f[2][2][CP];
+                for (int s0 = t; s0 < slots; s0 += 384) {
+                    float f[2][3][CP];
 #pragma unroll
                     for (int dr = 0; dr < 2; dr++)
 #pragma unroll
-                        for (int u = 0; u < 2; u++) {
+                        for (int u = 0; u < 3; u++) {
                             const int r = r0 + dr, sl = s0 + 128 * u;
                             const int iy = iy0 + r, ix = sl - args.px;
                             const bool in = r < args.ky && sl < slots && (unsigned)iy < (unsigned)args.H && (unsigned)ix < (unsigned)args.W;
@@ -638,7 +707,7 @@ ternary_stem_rows_kernel(const StemRowsArgs args) {
 #pragma unroll
                     for (int dr = 0; dr < 2; dr++)
 #pragma unroll
-                        for (int u = 0; u < 2; u++) {
+                        for (int u = 0; u < 3; u++) {
                             const int r = r0 + dr, sl = s0 + 128 * u;
                             if (r < args.ky && sl < slots) {
                                 __align__(16) __nv_bfloat16 o[CP];
@@ -786,7 +855,22 @@ extern "C" int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t 
     a.tiles = (long long)B * OH;
     a.relu = relu; a.status = status;
     const int win_bytes = (a.ring * a.WB + 127) / 128 * 128;
-    const int smem = ky * KR * 2048 + win_bytes + 512 + 128 + 1024;
+    // the new rows of a tile by TMA: X as a 3-D tensor [B*C planes][H][W] of fp32, box = C planes x sy rows x W
+    CUtensorMap mx = {};
+    a.use_tma = (W % 4 == 0 && W <= 256 && C <= 256 && sy <= 256 && aligned(X, 16)) ? 1 : 0;
+    a.stg_bytes = (C * sy * W * 4 + 127) / 128 * 128;
+    if (a.use_tma) {
+        EncodeTiledFn fn = encode_tiled();
+        cuuint64_t dims[3] = {(cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)B * C};
+        cuuint64_t strides[2] = {(cuuint64_t)W * 4, (cuuint64_t)H * W * 4};
+        cuuint32_t box[3] = {(cuuint32_t)W, (cuuint32_t)sy, (cuuint32_t)C};
+        cuuint32_t estr[3] = {1, 1, 1};
+        if (!fn || fn(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(X), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            a.use_tma = 0;
+    }
+    const int smem = ky * KR * 2048 + win_bytes + 512 + 256 + 128 + (a.use_tma ? kStemStages * a.stg_bytes : 0) + 1024;
     if (smem > 100 * 1024) return TMQ_ERR_UNSUPPORTED;
     const long long want = 2LL * kNumSMs;
     const long long grid = a.tiles < want ? a.tiles : want;
@@ -795,10 +879,10 @@ extern "C" int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t 
     int rc;
     if (CP == 4) {
         if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<4>, 100 * 1024)) != TMQ_OK) return rc;   // the limit, not this call's size
-        ternary_stem_rows_kernel<4><<<nblocks, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(a);
+        ternary_stem_rows_kernel<4><<<nblocks, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(mx, a);
     } else {
         if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<8>, 100 * 1024)) != TMQ_OK) return rc;
-        ternary_stem_rows_kernel<8><<<nblocks, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(a);
+        ternary_stem_rows_kernel<8><<<nblocks, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(mx, a);
     }
     return launch_status();
 }
