@@ -481,26 +481,15 @@ def ternary_sections(peaks):
     for i in range(NM):
         wts.append(ops.prepack(_ternary_packed(ops, N, K, 100 + i), N, ops.FMT_BF16))
     scale = torch.rand(N, device="cuda") * 0.09 + 0.01
-    for Mg in (1, 8, 16, 32):
-        X = torch.randn(Mg, K, device="cuda").to(torch.bfloat16)
-        Y = torch.empty(Mg, N, device="cuda", dtype=torch.bfloat16)
-        status = ops.gemm_status_word(X.device)
+    def graph_us_per_matrix(body):
+        """`body(stream_handle)` launches the whole set of NM matrices once; captured into a CUDA graph, replayed."""
         stream = torch.cuda.Stream()
-
-        def run(i, st):
-            for m0 in range(0, Mg, GEMV_ROWS_PER_PASS):
-                rc = L.tmq_ternary_gemv_bf16(X.data_ptr() + m0 * K * 2, wts[i].data_ptr(), scale.data_ptr(), None,
-                                             Y.data_ptr() + m0 * N * 2, min(GEMV_ROWS_PER_PASS, Mg - m0), N, K, N, 0,
-                                             status.data_ptr(), st)
-                assert rc == 0
         with torch.cuda.stream(stream):
-            for i in range(NM):
-                run(i, stream.cuda_stream)
+            body(stream.cuda_stream)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
-                for i in range(NM):
-                    run(i, stream.cuda_stream)
+                body(stream.cuda_stream)
             for _ in range(3):
                 graph.replay()
             torch.cuda.synchronize()
@@ -510,14 +499,54 @@ def ternary_sections(peaks):
                 graph.replay()
             e1.record(stream)
             torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) / 10 / NM * 1e3
+        return e0.elapsed_time(e1) / 10 / NM * 1e3
+
+    def gemv_entry(us, nbytes, Mg, protocol):
+        return {"us_per_matrix": us, "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"],
+                "tops_equiv": 2 * Mg * N * K / us / 1e6, "algorithmic_bytes": nbytes, "protocol": protocol}
+
+    def pointer_array(tensors):
+        arr = (ctypes.c_void_p * len(tensors))()
+        for i, t in enumerate(tensors):
+            arr[i] = t.data_ptr()
+        return arr
+
+    status = ops.gemm_status_word(torch.device("cuda", torch.cuda.current_device()))
+    for Mg in (1, 8, 16, 32):
+        X = torch.randn(Mg, K, device="cuda").to(torch.bfloat16)
+        Y = torch.empty(Mg, N, device="cuda", dtype=torch.bfloat16)
+
+        def body(st):
+            for i in range(NM):
+                for m0 in range(0, Mg, GEMV_ROWS_PER_PASS):
+                    rc = L.tmq_ternary_gemv_bf16(X.data_ptr() + m0 * K * 2, wts[i].data_ptr(), scale.data_ptr(), None,
+                                                 Y.data_ptr() + m0 * N * 2, min(GEMV_ROWS_PER_PASS, Mg - m0), N, K, N, 0,
+                                                 status.data_ptr(), st)
+                    assert rc == 0
         nbytes = N * K // 4 + 2 * Mg * K + 2 * Mg * N + 4 * N
-        res[f"gemv_bf16_M{Mg}_N11008_K4096"] = {"us_per_matrix": us, "gbs": nbytes / us / 1e3,
-                                               "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"],
-                                               "tops_equiv": 2 * Mg * N * K / us / 1e6, "algorithmic_bytes": nbytes,
-                                               "protocol": "32 distinct matrices in one CUDA graph, time/32; "
-                                                           f"{(Mg + GEMV_ROWS_PER_PASS - 1) // GEMV_ROWS_PER_PASS} launch(es) per matrix"}
-    # the same protocol with int8 activations (exact int32 results; byte dot products at M = 1)
+        res[f"gemv_bf16_M{Mg}_N11008_K4096"] = gemv_entry(
+            graph_us_per_matrix(body), nbytes, Mg, "32 distinct matrices in one CUDA graph, time/32; "
+            f"{(Mg + GEMV_ROWS_PER_PASS - 1) // GEMV_ROWS_PER_PASS} launch(es) per matrix")
+    # batched entry point: the same 32 matrices, `group` of them per launch sharing the activation vector (2 = gate / up,
+    # 4 ~ query / key / value / gate, 16 = the most one launch takes); every matrix writes its own result
+    X = torch.randn(1, K, device="cuda").to(torch.bfloat16)
+    Ys = [torch.empty(1, N, device="cuda", dtype=torch.bfloat16) for _ in range(NM)]
+    scales = pointer_array([scale] * NM)
+    for group in (2, 4, 16):
+        Wp = [pointer_array(wts[i:i + group]) for i in range(0, NM, group)]
+        Yp = [pointer_array(Ys[i:i + group]) for i in range(0, NM, group)]
+
+        def body(st):
+            for q in range(NM // group):
+                rc = L.tmq_ternary_gemv_batched_bf16(X.data_ptr(), 0, Wp[q], scales, None, Yp[q], group, 1, N, K, N, 0,
+                                                     status.data_ptr(), st)
+                assert rc == 0
+        nbytes = N * K // 4 + 2 * K + 2 * N + 4 * N
+        res[f"gemv_batched{group}_bf16_M1_N11008_K4096"] = gemv_entry(
+            graph_us_per_matrix(body), nbytes, 1,
+            f"32 distinct matrices in one CUDA graph, {group} per launch (tmq_ternary_gemv_batched_bf16), time/32")
+    del Ys
+    # the same protocols with int8 activations (exact int32 results; byte dot products at M = 1)
     wts8 = []
     for i in range(NM):
         wts8.append(ops.prepack(_ternary_packed(ops, N, K, 100 + i), N, ops.FMT_I8))
@@ -525,35 +554,30 @@ def ternary_sections(peaks):
     for Mg in (1, 8, 16):
         X8 = torch.randint(-127, 128, (Mg, K), device="cuda", dtype=torch.int8)
         Y8 = torch.empty(Mg, N, device="cuda", dtype=torch.int32)
-        status = ops.gemm_status_word(X8.device)
-        stream = torch.cuda.Stream()
 
-        def run8(i, st):
-            rc = L.tmq_ternary_gemv_i8(X8.data_ptr(), wts8[i].data_ptr(), Y8.data_ptr(), Mg, N, K, N, status.data_ptr(), st)
-            assert rc == 0
-        with torch.cuda.stream(stream):
+        def body8(st):
             for i in range(NM):
-                run8(i, stream.cuda_stream)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                for i in range(NM):
-                    run8(i, stream.cuda_stream)
-            for _ in range(3):
-                graph.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(10):
-                graph.replay()
-            e1.record(stream)
-            torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) / 10 / NM * 1e3
+                rc = L.tmq_ternary_gemv_i8(X8.data_ptr(), wts8[i].data_ptr(), Y8.data_ptr(), Mg, N, K, N,
+                                           status.data_ptr(), st)
+                assert rc == 0
         nbytes = N * K // 4 + Mg * K + 4 * Mg * N
-        res[f"gemv_i8_M{Mg}_N11008_K4096"] = {"us_per_matrix": us, "gbs": nbytes / us / 1e3,
-                                             "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"],
-                                             "tops_equiv": 2 * Mg * N * K / us / 1e6, "algorithmic_bytes": nbytes,
-                                             "protocol": "32 distinct matrices in one CUDA graph, time/32"}
+        res[f"gemv_i8_M{Mg}_N11008_K4096"] = gemv_entry(graph_us_per_matrix(body8), nbytes, Mg,
+                                                       "32 distinct matrices in one CUDA graph, time/32")
+    X8 = torch.randint(-127, 128, (1, K), device="cuda", dtype=torch.int8)
+    Ys8 = [torch.empty(1, N, device="cuda", dtype=torch.int32) for _ in range(NM)]
+    for group in (2, 4, 16):
+        Wp = [pointer_array(wts8[i:i + group]) for i in range(0, NM, group)]
+        Yp = [pointer_array(Ys8[i:i + group]) for i in range(0, NM, group)]
+
+        def body8b(st):
+            for q in range(NM // group):
+                rc = L.tmq_ternary_gemv_batched_i8(X8.data_ptr(), 0, Wp[q], Yp[q], group, 1, N, K, N, status.data_ptr(), st)
+                assert rc == 0
+        nbytes = N * K // 4 + K + 4 * N
+        res[f"gemv_batched{group}_i8_M1_N11008_K4096"] = gemv_entry(
+            graph_us_per_matrix(body8b), nbytes, 1,
+            f"32 distinct matrices in one CUDA graph, {group} per launch (tmq_ternary_gemv_batched_i8), time/32")
+    del Ys8
     ops.check_gemm_status()
     del wts8
     res["cpu_baselines"] = ternary_cpu_baselines()

@@ -203,6 +203,24 @@ int tmq_ternary_gemv_bf16(const void *X, const uint32_t *Wt, const float *scale,
 int tmq_ternary_gemv_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
                         int *status, void *stream);
 
+/* Batched skinny form: nmat (1 .. TMQ_GEMV_BATCH_MAX) weight matrices of ONE shape [N][K] in one launch, M <= 8
+ * activation rows each.  Projections that share their input (query / key / value, gate / up) and independent experts
+ * are not ordered among themselves, so one launch can take them all: the hand-over between two dependent kernels is
+ * paid once per group instead of once per matrix, and inside the launch the rows of matrix j + 1 stream into shared
+ * memory while matrix j is multiplied.  Same exact products as nmat calls of tmq_ternary_gemv_*: int32 results are
+ * identical, fp32 sums differ only by summation order (the K slices are spread over a different number of warps).
+ * Wt / scale / bias / Y: HOST arrays of nmat device pointers (scale, bias: NULL arrays or NULL entries allowed; Wt as
+ * for tmq_ternary_gemv_*, same early-fetch CONTRACT).  X: activations of matrix j start x_stride ELEMENTS after those
+ * of matrix j - 1 (0: all matrices share one block; otherwise a multiple of 16 bytes).  status: required.
+ * TMQ_ERR_UNSUPPORTED when one SM's share of a matrix exceeds the shared-memory budget (call the one-matrix form).
+ * extends: ternary_mvm_cuda, tmq/tmq_cuda.cu:563-603 (the reference launches one matrix per call). */
+#define TMQ_GEMV_BATCH_MAX 16
+int tmq_ternary_gemv_batched_bf16(const void *X, int64_t x_stride, const uint32_t *const *Wt, const float *const *scale,
+                                  const float *const *bias, void *const *Y, int nmat, int64_t M, int64_t N, int64_t K,
+                                  int64_t ldy, int out_f32, int *status, void *stream);
+int tmq_ternary_gemv_batched_i8(const int8_t *X, int64_t x_stride, const uint32_t *const *Wt, int32_t *const *Y, int nmat,
+                                int64_t M, int64_t N, int64_t K, int64_t ldy, int *status, void *stream);
+
 /* Ternary Conv2d as an implicit GEMM (no im2col buffer): X bf16 NHWC [B][H][W][C], C % 64 == 0; Wt = fmt-0 prepack of
  * the packed weight with its K rows reordered to (ky, kx, c); Y bf16 NHWC [B][OH][OW][N] with the output geometry of
  * F.conv2d; scale / bias per output channel (folded BatchNorm, NULL for none), optional residual (bf16, shape of Y,

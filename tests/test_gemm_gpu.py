@@ -225,3 +225,60 @@ def test_gemm_bf16_writes_a_column_block_of_a_wider_output(ops, M, n0, width):
     ops.check_gemm_status()
     assert torch.equal(wide[:, n0:n0 + N], plain)
     assert bool((wide[:, :n0] == 7.0).all()) and bool((wide[:, n0 + N:] == 7.0).all())
+
+
+# Batched skinny form: several matrices of one shape in one launch.  Shapes cover the separate and the overlaid
+# reduction area (rows + reduction beyond the shared-memory budget at M = 8 on the decode shape), ragged channel counts
+# (N % 16 != 0, fewer 16-channel groups than SMs), an odd and an even number of matrices, and more than one launch's
+# worth of matrices.
+BATCHED = [(1, 11008, 4096, 3), (2, 11008, 4096, 2), (8, 11008, 4096, 2), (5, 1000, 1088, 5), (1, 520, 256, 1),
+           (1, 4096, 4096, 18), (3, 2368, 512, 4)]
+
+
+@pytest.mark.parametrize("shared", [True, False])
+@pytest.mark.parametrize("M,N,K,nmat", BATCHED)
+def test_gemv_batched_i8_exact(ops, M, N, K, nmat, shared):
+    rng = np.random.default_rng(N + K + nmat)
+    X = rng.integers(-127, 128, (M, K) if shared else (nmat, M, K)).astype(np.int8)
+    packed = [make_weights(N, K, 31 * j + M)[1] for j in range(nmat)]
+    wts = [ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_I8) for P in packed]
+    Y = ops.ternary_gemv_batched(torch.from_numpy(X).cuda(), wts, N)
+    ops.check_gemm_status()
+    for j in range(nmat):
+        assert np.array_equal(Y[j].cpu().numpy(), T.gemm_i8_fast(X if shared else X[j], packed[j], N)), j
+
+
+@pytest.mark.parametrize("shared", [True, False])
+@pytest.mark.parametrize("M,N,K,nmat", BATCHED)
+def test_gemv_batched_bf16_matches_oracle_and_the_one_matrix_kernel(ops, M, N, K, nmat, shared):
+    gen = torch.Generator().manual_seed(N + K + nmat)
+    X = torch.randn((M, K) if shared else (nmat, M, K), generator=gen).to(torch.bfloat16)
+    packed = [make_weights(N, K, 17 * j + M)[1] for j in range(nmat)]
+    wts = [ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16) for P in packed]
+    scales = [torch.rand(N, generator=gen) * 0.09 + 0.01 if j % 2 == 0 else None for j in range(nmat)]
+    biases = [torch.randn(N, generator=gen) if j % 3 != 1 else None for j in range(nmat)]
+    Xc = X.cuda()
+    Y = ops.ternary_gemv_batched(Xc, wts, N, scales, biases, out_dtype=torch.float32)
+    ops.check_gemm_status()
+    for j in range(nmat):
+        xj = X if shared else X[j]
+        acc = T.gemm_f64_fast(xj.float().numpy(), packed[j], N)
+        ref = acc * (scales[j].double().numpy()[None, :] if scales[j] is not None else 1.0)
+        if biases[j] is not None:
+            ref = ref + biases[j].double().numpy()[None, :]
+        got = Y[j].double().cpu().numpy()
+        assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max(), j
+        one = ops.ternary_gemm(Xc if shared else Xc[j], wts[j], N, scales[j], biases[j], torch.float32, path="gemv")
+        # same products; the K slices are summed by 8 warps here and 16 there, so only fp32 summation order differs
+        assert float((one - Y[j]).abs().max()) <= 2e-6 * float(one.abs().max()), j
+
+
+def test_gemv_batched_argument_checks(ops):
+    N, K = 64, 128
+    wt = ops.prepack(torch.from_numpy(make_weights(N, K, 1)[1]).cuda(), N, ops.FMT_BF16)
+    x = torch.zeros(9, K, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        ops.ternary_gemv_batched(x, [wt], N)                       # more than 8 rows
+    with pytest.raises(RuntimeError):
+        ops.ternary_gemv_batched(x[:2].reshape(2, 1, K), [wt], N)  # two activation blocks, one matrix
+    assert ops.ternary_gemv_batched(x[:1], [], N) == []

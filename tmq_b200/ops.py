@@ -624,6 +624,82 @@ def ternary_gemm_i8(x, wt, columns, path="auto"):
     return y
 
 
+GEMV_BATCH_MAX = 16   # matrices one batched skinny launch takes (TMQ_GEMV_BATCH_MAX)
+
+
+def _pointer_array(tensors):
+    """Host array of device pointers (None -> NULL) for the batched entry points."""
+    arr = (ctypes.c_void_p * len(tensors))()
+    for i, t in enumerate(tensors):
+        arr[i] = None if t is None else t.data_ptr()
+    return arr
+
+
+def ternary_gemv_batched(x, wts, columns, scales=None, biases=None, out_dtype=torch.bfloat16, outs=None):
+    """Several ternary matrices of one shape against M <= 8 activation rows each, GEMV_BATCH_MAX matrices per launch.
+
+    x: bf16 or int8, [M, K] (all matrices share it: query / key / value, gate / up) or [len(wts), M, K] (one block per
+    matrix: experts, independent layers).  wts: prepacked weights (FMT_BF16 for bf16 x, FMT_I8 for int8 x), all
+    [columns, prepack_row_words(K)].  scales / biases: per-matrix fp32 [columns] tensors or None (bf16 only).
+    Returns the list of [M, columns] results (bf16 / fp32 for bf16 x, exact int32 for int8 x); against
+    ternary_gemm(..., path="gemv") per matrix only the fp32 summation order differs.  outs: optional preallocated contiguous results."""
+    i8 = x.dtype == torch.int8
+    if x.dtype not in (torch.bfloat16, torch.int8) or x.device.type != "cuda" or x.dim() not in (2, 3):
+        raise RuntimeError("ternary_gemv_batched: expected CUDA bf16 or int8 activations, [M, K] or [matrices, M, K]")
+    n = len(wts)
+    x = x.contiguous()
+    if x.dim() == 3 and x.shape[0] != n:
+        raise RuntimeError("ternary_gemv_batched: one activation block per matrix expected")
+    M, K = x.shape[-2:]
+    N = int(columns)
+    if M > 8:
+        raise RuntimeError("ternary_gemv_batched: at most 8 activation rows per matrix")
+    dtype = torch.int32 if i8 else out_dtype
+    if not i8 and out_dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("ternary_gemv_batched: output dtype must be bfloat16 or float32")
+    for w in wts:
+        _check_weights("ternary_gemv_batched", w, N, K, FMT_I8 if i8 else FMT_BF16)
+    if outs is None:
+        whole = torch.empty((n, M, N), dtype=dtype, device=x.device)
+        outs = list(whole.unbind(0))
+    elif len(outs) != n or any(o.dtype != dtype or tuple(o.shape) != (M, N) or not o.is_contiguous() or o.device != x.device
+                               for o in outs):
+        raise RuntimeError("ternary_gemv_batched: `outs` must be contiguous [M, N] tensors of the output dtype")
+    if n == 0 or M == 0:
+        return outs
+    def f32(ts):
+        return None if ts is None else [None if t is None else t.to(device=x.device, dtype=torch.float32).contiguous()
+                                        for t in ts]
+    scales, biases = f32(scales), f32(biases)
+    stride = M * K if x.dim() == 3 else 0
+    esz = x.element_size()
+    st = gemm_status_word(x.device)
+    with torch.cuda.device(x.device):
+        for j0 in range(0, n, GEMV_BATCH_MAX):
+            j1 = min(n, j0 + GEMV_BATCH_MAX)
+            xp = ctypes.c_void_p(x.data_ptr() + j0 * stride * esz)
+            W, Y = _pointer_array(wts[j0:j1]), _pointer_array(outs[j0:j1])
+            if i8:
+                rc = lib().tmq_ternary_gemv_batched_i8(xp, stride, W, Y, j1 - j0, M, N, K, N, _ptr(st), _stream(x))
+            else:
+                S = _pointer_array(scales[j0:j1]) if scales is not None else None
+                B = _pointer_array(biases[j0:j1]) if biases is not None else None
+                rc = lib().tmq_ternary_gemv_batched_bf16(xp, stride, W, S, B, Y, j1 - j0, M, N, K, N,
+                                                         1 if dtype == torch.float32 else 0, _ptr(st), _stream(x))
+            if rc == -6:      # one SM's share of a matrix exceeds the shared-memory budget: one launch per matrix
+                for j in range(j0, j1):
+                    xj = x[j] if x.dim() == 3 else x
+                    if i8:
+                        outs[j].copy_(ternary_gemm_i8(xj, wts[j], N, path="gemv"))
+                    else:
+                        ternary_gemm(xj, wts[j], N, None if scales is None else scales[j],
+                                     None if biases is None else biases[j], dtype, path="gemv", out=outs[j])
+            else:
+                check(rc, "ternary_gemv_batched")
+            _launched(x.device)
+    return outs
+
+
 HAVE_IMPLICIT_CONV = True
 
 
