@@ -221,6 +221,18 @@ int tmq_ternary_gemv_batched_bf16(const void *X, int64_t x_stride, const uint32_
 int tmq_ternary_gemv_batched_i8(const int8_t *X, int64_t x_stride, const uint32_t *const *Wt, int32_t *const *Y, int nmat,
                                 int64_t M, int64_t N, int64_t K, int64_t ldy, int *status, void *stream);
 
+/* Training forward of a quantisation-aware Linear layer with the soft staircase fused into the weight-operand load:
+ *   Y[m][n] = sum_k X[m][k] * S(W[n][k]; hardness) + bias[n]
+ * X bf16 [M][K] (K % 8 == 0, 16-byte aligned), W the latent fp32 weights [N][K] (16-byte aligned), bias fp32 [N] or
+ * NULL, Y fp32 [M][ldy].  S is evaluated bit-identically to tmq_softstep_fwd inside the GEMM's producer warps and fed to
+ * the tensor cores as two bf16 terms (hi + lo, ~2^-17 relative), fp32 accumulation: the staircase values are never
+ * written to memory.  Producer-bound (every weight tile is evaluated once per 128 / 256 activation rows): meant for
+ * M up to a few hundred rows; for tall activations run tmq_softstep_fwd once and a dense GEMM.
+ * hardness in [1e-3, 1e3]; status: see "Status word" above (required).
+ * replaces: SoftStep.apply + F.linear in Linear.forward, tmq/tmq.py:637-659 (:404-433 for S). */
+int tmq_qat_linear_fwd_bf16(const void *X, const float *W, const float *bias, float *Y, int64_t M, int64_t N, int64_t K,
+                            int64_t ldy, double hardness, int *status, void *stream);
+
 /* Ternary Conv2d as an implicit GEMM (no im2col buffer): X bf16 NHWC [B][H][W][C], C % 64 == 0; Wt = fmt-0 prepack of
  * the packed weight with its K rows reordered to (ky, kx, c); Y bf16 NHWC [B][OH][OW][N] with the output geometry of
  * F.conv2d; scale / bias per output channel (folded BatchNorm, NULL for none), optional residual (bf16, shape of Y,

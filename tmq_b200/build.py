@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "_build")
 LIB = os.path.join(OUT, "libtmq_b200.so")
 
-SOURCES = ["capi.cu", "softstep.cu", "pack.cu", "qloss_noalloc.cu", "ternary_gemm.cu", "ternary_gemv.cu", "ternary_conv.cu", "ternary_conv_sw.cu", "ternary_conv_pm.cu", "layout.cu", "ternary_dwconv.cu", "rangecoder.cu"]
+SOURCES = ["capi.cu", "softstep.cu", "pack.cu", "qloss_noalloc.cu", "ternary_gemm.cu", "ternary_gemv.cu", "ternary_conv.cu", "ternary_conv_sw.cu", "ternary_conv_pm.cu", "layout.cu", "qat_linear.cu", "ternary_dwconv.cu", "rangecoder.cu"]
 
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "--fmad=false",

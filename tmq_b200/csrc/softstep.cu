@@ -13,6 +13,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "softstep_math.cuh"
 
 #ifndef TMQ_SS_FASTDIV
 #define TMQ_SS_FASTDIV 1  // range-specialised division for the data-dependent quotients of the packed path
@@ -23,28 +24,6 @@ namespace tmq {
 thread_local int g_last_cuda_error = 0;
 
 // ---------------------------------------------------------------------------------------------------- constants
-
-struct Hardness {  // the fp32 scalars the formulas use for one hardness value d
-    float d;   // fp32(d)
-    float h;   // fp32(d / 2)
-    float D;   // fp32(2 * sigma(d / 2)), sigma evaluated in double (tmq/tmq.py:384-391)
-    float rD;  // fp32(1 / D), correctly rounded: operand of the constant-divisor sequence
-};
-
-static double scalar_sigmoid(double v) {
-    double x = fmin(3.0, fmax(-3.0, v));
-    double x2 = x * x;
-    return x * (x2 + 27.0) / (27.0 + x2 * 9.0);
-}
-
-static Hardness make_hardness(double d) {
-    Hardness c;
-    c.d = (float)d;
-    c.h = (float)(d / 2.0);
-    c.D = (float)(2.0 * scalar_sigmoid(d / 2.0));
-    c.rD = 1.0f / c.D;
-    return c;
-}
 
 static bool hardness_ok(double d) { return isfinite(d) && d >= 1e-3 && d <= 1e3; }
 
@@ -87,28 +66,6 @@ enum : unsigned {
 
 // ---------------------------------------------------------------------------------------------------- element math
 
-// a / D for the per-launch constant D > 0.  With rD = RN(1/D): q0 = RN(a*rD) is within an ulp of the quotient,
-// r = a - q0*D is exact in one FMA, and q0 + r*rD rounds to the correctly rounded quotient (Markstein's
-// correction step).  Valid while nothing under- or overflows, which the host guarantees before choosing FAST.
-template <bool FAST>
-__device__ __forceinline__ float div_const(float a, float D, float rD) {
-    if (FAST) {
-        float q0 = __fmul_rn(a, rD);
-        float r = __fmaf_rn(-q0, D, a);
-        return __fmaf_rn(r, rD, q0);
-    }
-    return __fdiv_rn(a, D);
-}
-
-// torch.clamp semantics: NaN stays NaN.  min/max with the .NaN qualifier propagate it in one instruction each
-// (plain fminf/fmaxf would return the bound instead).
-__device__ __forceinline__ float clamp_nan(float v, float lo, float hi) {
-    float t, c;
-    asm("max.NaN.f32 %0, %1, %2;" : "=f"(t) : "f"(v), "f"(lo));
-    asm("min.NaN.f32 %0, %1, %2;" : "=f"(c) : "f"(t), "f"(hi));
-    return c;
-}
-
 struct Out {
     float y, gw, o, wc, term;
 };
@@ -122,14 +79,7 @@ __device__ __forceinline__ Out element(float w, float g, const Args &a) {
         const float t = __fmul_rn(a.s.d, fr);
         const float x = clamp_nan(__fsub_rn(t, a.s.h), -3.0f, 3.0f);
         const float x2 = __fmul_rn(x, x);
-        if (F & F_FWD) {
-            const float p = __fadd_rn(x2, 27.0f);
-            const float q = __fmul_rn(x, p);
-            const float s = __fadd_rn(27.0f, __fmul_rn(x2, 9.0f));
-            const float z = __fdiv_rn(q, s);
-            const float u = div_const<FAST>(z, a.s.D, a.s.rD);
-            r.y = __fadd_rn(__fadd_rn(u, 0.5f), fw);
-        }
+        if (F & F_FWD) r.y = softstep_value<FAST>(x, x2, fw, a.s);
         if (F & F_BWD) {
             const float e = __fsub_rn(x2, 9.0f);
             const float n = __fmul_rn(e, e);

@@ -700,6 +700,33 @@ def ternary_gemv_batched(x, wts, columns, scales=None, biases=None, out_dtype=to
     return outs
 
 
+def qat_linear_forward(x, weight, bias, hardness):
+    """Training forward of a quantisation-aware Linear layer, x @ S(weight)^T + bias, with the soft staircase S evaluated
+    inside the tensor-core GEMM's operand producers (never materialised).  x: CUDA bf16 [..., K] with K % 8 == 0;
+    weight: the latent fp32 [N, K] tensor; bias: fp32 [N] or None.  Returns fp32 [..., N]."""
+    if x.dtype != torch.bfloat16 or x.device.type != "cuda":
+        raise RuntimeError("qat_linear_forward: expected CUDA bf16 activations")
+    if weight.dtype != torch.float32 or weight.dim() != 2 or weight.device != x.device:
+        raise RuntimeError("qat_linear_forward: expected a 2-D fp32 weight tensor on the activations' device")
+    N, K = weight.shape
+    if x.shape[-1] != K:
+        raise RuntimeError("qat_linear_forward: activation width does not match the weights")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, K).contiguous()
+    w = weight.contiguous()
+    M = x2.shape[0]
+    y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    if M == 0:
+        return y.view(*lead, N)
+    b = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
+    st = gemm_status_word(x.device)
+    with torch.cuda.device(x.device):
+        check(lib().tmq_qat_linear_fwd_bf16(_ptr(x2), _ptr(w), _ptr(b) if b is not None else None, _ptr(y), M, N, K, N,
+                                            float(hardness), _ptr(st), _stream(x)), "qat_linear_forward")
+    _launched(x.device)
+    return y.view(*lead, N)
+
+
 HAVE_IMPLICIT_CONV = True
 
 

@@ -313,6 +313,33 @@ class SoftStep(Function):
         return ops.bwd_softstep(weight.data, ctx.ctrl.digamma, ctx.scale, grad_output), None, None
 
 
+class FusedSoftLinear(Function):
+    """x @ SoftStep(weight)^T + bias for bf16 activations with the staircase fused into the GEMM's weight-operand load
+    (ops.qat_linear_forward); the two passes it replaces are SoftStep.apply + F.linear [tmq/tmq.py:637-659].  The
+    backward pass recomputes the staircase with the elementwise kernels."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, ctrl):
+        ctx.ctrl = ctrl
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(x, weight)
+        return ops.qat_linear_forward(x.data, weight.data, None if bias is None else bias.data, ctrl.digamma)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, weight = ctx.saved_tensors
+        d = ctx.ctrl.digamma
+        g = grad_output.reshape(-1, grad_output.shape[-1]).float()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = (g @ ops.fwd_softstep(weight.data, d)).to(x.dtype).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            gw = ops.bwd_softstep(weight.data, d, 1.0, g.t() @ x.reshape(-1, x.shape[-1]).float())
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = g.sum(0)
+        return gx, gw, gb, None
+
+
 class SoftStepDerivative(Function):
     """First derivative of the staircase, the integrand of the quantization loss [tmq/tmq.py:441-493]."""
 
@@ -528,6 +555,16 @@ class Linear(nn.Module, TMQLayer):
     def forward(self, x):
         if self.compact:
             return self.compact_forward(x)
+        if (x.dtype == torch.bfloat16 and x.is_cuda and self._ctrl is not None and not self._ctrl.inference_mode
+                and x.shape[-1] % 8 == 0):
+            # bf16 activations (not a reference configuration: its fp32 weights would refuse them): one fused kernel
+            self._update_scale()
+            out = FusedSoftLinear.apply(x, self.weight, None if self.post_scale_imm != 1.0 else self.bias, self._ctrl)
+            if self.post_scale_imm != 1.0:
+                out = self.post_scale * out
+                if self.bias is not None:
+                    out = self.bias + out
+            return self.bn(out) if self.bn is not None else out
         w = self._soft_weight()
         if self.post_scale_imm != 1.0:
             out = self.post_scale * torch.nn.functional.linear(x, w, None)
