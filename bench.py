@@ -580,8 +580,40 @@ def ternary_sections(peaks):
     del Ys8
     ops.check_gemm_status()
     del wts8
+    res.update(qat_linear_sections(ops))
     res["cpu_baselines"] = ternary_cpu_baselines()
     return res
+
+
+def qat_linear_sections(ops):
+    """Training forward of a QAT Linear layer (soft staircase + matmul), fused kernel against the two-pass routes.
+    16 distinct weight matrices (1 GB of fp32 latent weights > L2) so that every call reads its weights from HBM."""
+    out = {}
+    N = K = 4096
+    NW = 16
+    ws = [torch.rand(N, K, device="cuda") * 2.5 - 1.25 for _ in range(NW)]
+    bias = torch.randn(N, device="cuda")
+    for M in (64, 256, 2048):
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        xf = x.float()
+        state = {"i": 0}
+
+        def nxt():
+            state["i"] = (state["i"] + 1) % NW
+            return ws[state["i"]]
+        fused = _time_cuda(lambda: ops.qat_linear_forward(x, nxt(), bias, 5.0), 32)
+        two_pass_f32 = _time_cuda(lambda: torch.nn.functional.linear(xf, ops.fwd_softstep(nxt(), 5.0), bias), 32)
+        two_pass_bf16 = _time_cuda(lambda: torch.nn.functional.linear(x, ops.fwd_softstep(nxt(), 5.0).to(torch.bfloat16),
+                                                                      None), 32)
+        out[f"qat_linear_fwd_M{M}_N4096_K4096"] = {
+            "fused_us": fused * 1e3, "staircase_kernel_plus_fp32_linear_us": two_pass_f32 * 1e3,
+            "staircase_kernel_plus_bf16_cast_plus_bf16_linear_us": two_pass_bf16 * 1e3,
+            "fused_tflops_equiv": 2 * M * N * K / fused / 1e9,
+            "weights_per_us": N * K / (fused * 1e3),
+            "note": "fused = tmq_qat_linear_fwd_bf16 (bf16 activations, S(W) as two bf16 terms, fp32 out); the fp32 route "
+                    "is what the reference's layer does (SoftStep.apply + F.linear)"}
+    ops.check_gemm_status()
+    return out
 
 
 def ternary_cpu_baselines():

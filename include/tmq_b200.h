@@ -229,9 +229,15 @@ int tmq_ternary_gemv_batched_i8(const int8_t *X, int64_t x_stride, const uint32_
  * written to memory.  Producer-bound (every weight tile is evaluated once per 128 / 256 activation rows): meant for
  * M up to a few hundred rows; for tall activations run tmq_softstep_fwd once and a dense GEMM.
  * hardness in [1e-3, 1e3]; status: see "Status word" above (required).
+ * workspace: device scratch of tmq_qat_linear_workspace_bytes(M, N, K) bytes (16-byte aligned; 0 bytes when the problem
+ * has at least as many output tiles as SMs).  With it, K is split over several CTAs per output tile and the partial sums
+ * are combined in a fixed order by a second small kernel (deterministic); without it (NULL / too small) every output
+ * tile is one CTA's work, which leaves SMs idle on small layers.
  * replaces: SoftStep.apply + F.linear in Linear.forward, tmq/tmq.py:637-659 (:404-433 for S). */
+size_t tmq_qat_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int tmq_qat_linear_fwd_bf16(const void *X, const float *W, const float *bias, float *Y, int64_t M, int64_t N, int64_t K,
-                            int64_t ldy, double hardness, int *status, void *stream);
+                            int64_t ldy, double hardness, void *workspace, size_t workspace_bytes, int *status,
+                            void *stream);
 
 /* Ternary Conv2d as an implicit GEMM (no im2col buffer): X bf16 NHWC [B][H][W][C], C % 64 == 0; Wt = fmt-0 prepack of
  * the packed weight with its K rows reordered to (ky, kx, c); Y bf16 NHWC [B][OH][OW][N] with the output geometry of

@@ -70,8 +70,9 @@ _SIGNATURES = {
                                               c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "tmq_ternary_gemv_batched_i8": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
                                             c_int64, c_void_p, c_void_p]),
+    "tmq_qat_linear_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "tmq_qat_linear_fwd_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
-                                        ctypes.c_double, c_void_p, c_void_p]),
+                                        ctypes.c_double, c_void_p, c_size_t, c_void_p, c_void_p]),
     "tmq_ternary_conv2d_bf16": (c_int, [c_void_p] * 6 + [c_int] * 14 + [c_void_p, c_void_p]),
     "tmq_ternary_conv2d_bf16_f32out": (c_int, [c_void_p] * 6 + [c_int] * 14 + [c_void_p, c_void_p]),
     "tmq_ternary_conv2d_s1_bf16": (c_int, [c_void_p] * 6 + [c_int] * 12 + [c_void_p, c_void_p]),

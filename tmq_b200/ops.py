@@ -720,9 +720,12 @@ def qat_linear_forward(x, weight, bias, hardness):
         return y.view(*lead, N)
     b = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
     st = gemm_status_word(x.device)
+    need = int(lib().tmq_qat_linear_workspace_bytes(M, N, K))      # partial sums when K is split over several CTAs
+    ws = torch.empty(need, dtype=torch.uint8, device=x.device) if need else None   # stream-ordered caching allocator
     with torch.cuda.device(x.device):
         check(lib().tmq_qat_linear_fwd_bf16(_ptr(x2), _ptr(w), _ptr(b) if b is not None else None, _ptr(y), M, N, K, N,
-                                            float(hardness), _ptr(st), _stream(x)), "qat_linear_forward")
+                                            float(hardness), _ptr(ws) if ws is not None else None, need, _ptr(st),
+                                            _stream(x)), "qat_linear_forward")
     _launched(x.device)
     return y.view(*lead, N)
 
