@@ -18,6 +18,7 @@ the three partitionings that move data (column-sharded prefill GEMM, data-parall
 ResNet-18 inference) and reports them under `extra`.
 """
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -441,7 +442,6 @@ def measure_tensor_peaks():
 
 def ternary_sections(peaks):
     """Baseline configs 5 (prefill GEMM M=8192, K=8192, N=28672) and 3 (decode GEMV N=11008, K=4096, M in 1/8/32)."""
-    import ctypes
     from tmq_b200 import _lib, ops
     L = _lib.lib()
     res = {}
@@ -869,6 +869,52 @@ def run_workload(args):
                 "config": {"workload": f"ternary_gemv_M{Mg}_N11008_K4096", "matrices": NM,
                            "note": "stream launches (no CUDA graph): includes launch gaps; the headline GEMV number is "
                                    "the graph protocol of the default run"}}
+    elif args.workload == "gemv_batched":
+        # the same decode-like config through the batched entry point: --gemv-group matrices per launch, int8 or bf16
+        from tmq_b200 import _lib
+        Lb = _lib.lib()
+        N, K, NM, Mg, G = 11008, 4096, args.gemv_matrices, args.gemv_rows, args.gemv_group
+        i8 = args.gemv_dtype == "i8"
+        fmt = ops.FMT_I8 if i8 else ops.FMT_BF16
+        wts = [ops.prepack(_ternary_packed(ops, N, K, 100 + i), N, fmt) for i in range(NM)]
+        X = torch.randint(-127, 128, (Mg, K), device=dev, dtype=torch.int8) if i8 else torch.randn(Mg, K, device=dev).to(torch.bfloat16)
+        Ys = [torch.empty(Mg, N, device=dev, dtype=torch.int32 if i8 else torch.bfloat16) for _ in range(NM)]
+        status = ops.gemm_status_word(X.device)
+        st = torch.cuda.current_stream().cuda_stream
+
+        def parr(ts):
+            arr = (ctypes.c_void_p * len(ts))()
+            for i, t in enumerate(ts):
+                arr[i] = t.data_ptr()
+            return arr
+        groups = [(parr(wts[i:i + G]), parr(Ys[i:i + G]), len(wts[i:i + G])) for i in range(0, NM, G)]
+
+        def sweep(i):
+            for Wp, Yp, n in groups:
+                if i8:
+                    rc = Lb.tmq_ternary_gemv_batched_i8(X.data_ptr(), 0, Wp, Yp, n, Mg, N, K, N, status.data_ptr(), st)
+                else:
+                    rc = Lb.tmq_ternary_gemv_batched_bf16(X.data_ptr(), 0, Wp, None, None, Yp, n, Mg, N, K, N, 0,
+                                                          status.data_ptr(), st)
+                assert rc == 0
+        ms = timed(sweep, args.steps, args.warmup) / NM
+        nbytes = N * K // 4 + (1 if i8 else 2) * Mg * K + (4 if i8 else 2) * Mg * N
+        line = {"metric": f"ternary_gemv_batched_{args.gemv_dtype}_GBps", "value": nbytes / ms / 1e6, "unit": "GB/s",
+                "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.gemv_dtype,
+                "data": "synthetic",
+                "config": {"workload": f"ternary_gemv_batched_M{Mg}_N11008_K4096", "matrices": NM, "per_launch": G}}
+    elif args.workload == "qat_linear":
+        # training forward of a QAT Linear layer with the staircase fused into the operand load (profiling helper)
+        N = K = 4096
+        Mq = args.qat_rows
+        ws = [torch.rand(N, K, device=dev) * 2.5 - 1.25 for _ in range(8)]
+        x = torch.randn(Mq, K, device=dev).to(torch.bfloat16)
+        ms = timed(lambda i: ops.qat_linear_forward(x, ws[i % 8], None, 5.0), args.steps, args.warmup)
+        line = {"metric": "qat_linear_fwd_weights_per_us", "value": N * K / ms / 1e3, "unit": "weights/us", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"qat_linear_fwd_M{Mq}_N4096_K4096", "weights": "8 distinct fp32 matrices (537 MB)"}}
     elif args.workload in ("dwconv", "dwconvtrans"):
         # depthwise compact convolution straight from the image: MobileNet-like 3x3, fp32 NCHW, batch sharded over ranks
         Bt, C, H, W = 256 // world, 128, 56, 56
@@ -933,7 +979,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-extra", action="store_true", help="skip the ternary GEMM / GEMV sections")
-    ap.add_argument("--workload", default="softstep", choices=["softstep", "gemm", "gemv", "resnet_qat", "resnet_infer", "dwconv", "dwconvtrans", "adam"])
+    ap.add_argument("--workload", default="softstep", choices=["softstep", "gemm", "gemv", "gemv_batched", "qat_linear", "resnet_qat", "resnet_infer", "dwconv",
+                             "dwconvtrans", "adam"])
     ap.add_argument("--gemm-m", type=int, default=8192)
     ap.add_argument("--gemm-k", type=int, default=8192)
     ap.add_argument("--gemm-n", type=int, default=28672)
@@ -943,6 +990,9 @@ def main():
     ap.add_argument("--per-layer", action="store_true", help="resnet_infer: time every layer alone as well")
     ap.add_argument("--gemv-rows", type=int, default=1)
     ap.add_argument("--gemv-matrices", type=int, default=32)
+    ap.add_argument("--gemv-group", type=int, default=16, help="matrices per launch of --workload gemv_batched")
+    ap.add_argument("--gemv-dtype", default="bf16", choices=["bf16", "i8"])
+    ap.add_argument("--qat-rows", type=int, default=64, help="activation rows of --workload qat_linear")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
