@@ -184,6 +184,17 @@ int tmq_ternary_gemm_bf16(const void *X, const uint32_t *Wt, const float *scale,
 int tmq_ternary_gemm_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
                         int *status, void *stream);
 
+/* GEMM + all-gather in one kernel: tmq_ternary_gemm_bf16 (bf16 output) whose epilogue stores every output vector into
+ * ndst (1 .. 8) buffers: Ys[0] in this GPU's memory and Ys[1 ..] in OTHER GPUs' memory (peer mappings of buffers of the
+ * same shape, e.g. CUDA IPC or symmetric memory), all with row stride ldy.  A rank of a column-sharded linear passes
+ * every rank's full-width output buffer offset to its own column block: when the kernel has completed on every rank
+ * (the caller orders that with a barrier on the stream, and must not let a rank overwrite a buffer a peer still reads),
+ * each buffer holds the whole row-major result and no separate all-gather has run; the transfers over NVLink overlap
+ * the multiplication tile by tile.  Ys: HOST array of device pointers.  Plain stores only, no multicast.
+ * extends: ternary_mmm_cuda, tmq/tmq_cuda.cu:478-549 (the reference is single-GPU). */
+int tmq_ternary_gemm_bf16_bcast(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *const *Ys,
+                                int ndst, int64_t M, int64_t N, int64_t K, int64_t ldy, int *status, void *stream);
+
 /* Skinny form for M <= 16 activation rows (decode-like GEMV): reads the packed weights once, exactly decoded operands
  * (warp-level MMA, the decoded fragment shared by both 8-row tiles when M > 8; byte dot products for int8 with M <= 2),
  * deterministic.  M > 8 needs the resident form (a status word, and one SM's share of the rows within the shared-memory

@@ -62,6 +62,8 @@ _SIGNATURES = {
     "tmq_prepack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "tmq_ternary_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                       c_int64, c_int, c_void_p, c_void_p]),
+    "tmq_ternary_gemm_bf16_bcast": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64,
+                                            c_int64, c_int64, c_void_p, c_void_p]),
     "tmq_ternary_gemv_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                       c_int64, c_int, c_void_p, c_void_p]),
     "tmq_ternary_gemv_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,

@@ -55,6 +55,7 @@ struct GemmArgs {
     long long M, N, K, ldy;
     int out_f32;         // bf16 kind: write fp32 instead of bf16
     int *status;
+    PeerList peers;      // bf16 output only: the same block is also stored into these buffers (other GPUs' memory)
 };
 
 template <int KIND>
@@ -319,7 +320,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
                 if (KIND == KIND_BF16 && !args.out_f32) {
                     epilogue_chunk_bf16(v, sc, bi, stage, reinterpret_cast<__nv_bfloat16 *>(args.Y), nullptr, m0 + c, args.M,
-                                        args.ldy, n0 + quarter * 32, args.N, 0, lane);
+                                        args.ldy, n0 + quarter * 32, args.N, 0, lane, &args.peers);
                 } else if (n_ok) {
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
@@ -490,7 +491,23 @@ extern "C" int tmq_ternary_gemm_bf16(const void *X, const uint32_t *Wt, const fl
     int rc = check_gemm_common(X, Wt, Y, M, N, K, ldy, status, 2);
     if (rc != TMQ_OK) return rc;
     if (!aligned(Y, out_f32 ? 4 : 2)) return TMQ_ERR_ALIGN;
-    GemmArgs a = {scale, bias, Y, M, N, K, ldy, out_f32, status};
+    GemmArgs a = {scale, bias, Y, M, N, K, ldy, out_f32, status, {}};
+    return dispatch_gemm<KIND_BF16>(X, Wt, a, (cudaStream_t)stream);
+}
+
+extern "C" int tmq_ternary_gemm_bf16_bcast(const void *X, const uint32_t *Wt, const float *scale, const float *bias,
+                                           void *const *Ys, int ndst, int64_t M, int64_t N, int64_t K, int64_t ldy,
+                                           int *status, void *stream) {
+    if (!Ys || ndst < 1 || ndst > 1 + kMaxPeers) return TMQ_ERR_ARG;
+    int rc = check_gemm_common(X, Wt, Ys[0], M, N, K, ldy, status, 2);
+    if (rc != TMQ_OK) return rc;
+    GemmArgs a = {scale, bias, Ys[0], M, N, K, ldy, 0, status, {}};
+    for (int q = 0; q < ndst; q++) {
+        if (!Ys[q]) return TMQ_ERR_ARG;
+        if (!aligned(Ys[q], 2)) return TMQ_ERR_ALIGN;
+        if (q > 0) a.peers.y[q - 1] = reinterpret_cast<__nv_bfloat16 *>(Ys[q]);
+    }
+    a.peers.n = ndst - 1;
     return dispatch_gemm<KIND_BF16>(X, Wt, a, (cudaStream_t)stream);
 }
 
@@ -499,6 +516,6 @@ extern "C" int tmq_ternary_gemm_i8(const int8_t *X, const uint32_t *Wt, int32_t 
     int rc = check_gemm_common(X, Wt, Y, M, N, K, ldy, status, 1);
     if (rc != TMQ_OK) return rc;
     if (!aligned(Y, 4)) return TMQ_ERR_ALIGN;
-    GemmArgs a = {nullptr, nullptr, Y, M, N, K, ldy, 0, status};
+    GemmArgs a = {nullptr, nullptr, Y, M, N, K, ldy, 0, status, {}};
     return dispatch_gemm<KIND_I8>(X, Wt, a, (cudaStream_t)stream);
 }

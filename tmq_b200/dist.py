@@ -104,6 +104,45 @@ class FlatGradBucket:
         return None
 
 
+class PeerBuffer:
+    """One CUDA tensor of the same shape on every rank of a single node, each mapped into every other rank's address
+    space, so that a kernel on one GPU can store straight into the others' copies over NVLink.  `ptrs[r]` is the device
+    address of rank r's tensor as seen from THIS process.  Uses torch's symmetric memory when it is available and
+    CUDA IPC handles exchanged over the process group otherwise (`kind` says which)."""
+
+    def __init__(self, shape, dtype, device, group=None):
+        self.rank, self.world = world()
+        self.kind = None
+        self._keep = []
+        try:
+            import torch.distributed._symmetric_memory as symm
+            t = symm.empty(tuple(shape), dtype=dtype, device=device)
+            hdl = symm.rendezvous(t, dist.group.WORLD if group is None else group)
+            self.tensor = t
+            self.ptrs = [int(p) for p in hdl.buffer_ptrs]
+            self._keep.append(hdl)
+            self.kind = "symmetric_memory"
+        except Exception as err:                     # noqa: BLE001 - any failure of the optional route falls back
+            self._ipc(shape, dtype, device, group, err)
+
+    def _ipc(self, shape, dtype, device, group, why):
+        # the handle names the allocator block that holds the tensor; the offset inside it travels with it
+        self.tensor = torch.empty(tuple(shape), dtype=dtype, device=device)
+        storage = self.tensor.untyped_storage()
+        mine = (storage._share_cuda_(), self.tensor.storage_offset() * self.tensor.element_size())
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self.ptrs = []
+        for r, (handle, offset) in enumerate(everyone):
+            if r == self.rank:
+                self.ptrs.append(self.tensor.data_ptr())
+            else:
+                opened = torch.UntypedStorage._new_shared_cuda(*handle)
+                self._keep.append(opened)
+                self.ptrs.append(opened.data_ptr() + offset)
+        self.kind = f"cuda_ipc (symmetric memory unavailable: {type(why).__name__})"
+
+
 class ColumnShardedLinear:
     """y = x @ T^T for a ternary weight whose output channels are split over the ranks.
 
@@ -129,6 +168,8 @@ class ColumnShardedLinear:
         self.bias = None if bias is None else bias[n0:n1].contiguous()
         self._matmul = matmul
         self._wt = None
+        self._peer = {}              # rows -> PeerBuffer holding the full [rows, n_total] result on every rank
+        self._flag = None
 
     def _out_dtype(self, x):
         return x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.bfloat16
@@ -147,6 +188,31 @@ class ColumnShardedLinear:
             self._wt = ops.prepack(self.packed_shard, n, ops.FMT_BF16)
         return ops.ternary_gemm(x, self._wt, n, self.scale, self.bias, out_dtype=self._out_dtype(x),
                                 out=None if out is None else out[:, :n])
+
+    def fused(self, x, group=None):
+        """Full row-major [M, n_total] bf16 result on every rank with GEMM and all-gather as ONE kernel: the epilogue
+        of this rank's GEMM stores its column block into every rank's result buffer (peer mappings, plain stores over
+        NVLink), so the transfer overlaps the multiplication tile by tile and nothing is copied afterwards.  Two tiny
+        all-reduces order the ranks: before the launch (nobody still reads the previous result) and after it (every
+        block has landed everywhere).  The returned tensor is reused by the next call with the same row count."""
+        from . import ops
+        if self.world == 1:
+            return self.local(x)
+        if x.dtype != torch.bfloat16:
+            raise RuntimeError("ColumnShardedLinear.fused: bf16 activations only")
+        m = x.shape[0]
+        pb = self._peer.get(m)
+        if pb is None:
+            pb = self._peer[m] = PeerBuffer((m, self.n_total), torch.bfloat16, x.device, group)
+            self._flag = torch.zeros(1, dtype=torch.int32, device=x.device)
+        if self._wt is None:
+            self._wt = ops.prepack(self.packed_shard, self.n1 - self.n0, ops.FMT_BF16)
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        dsts = [pb.ptrs[r] + self.n0 * 2 for r in order]
+        dist.all_reduce(self._flag, group=group)
+        ops.ternary_gemm_bcast(x, self._wt, self.n1 - self.n0, dsts, self.n_total, self.scale, self.bias)
+        dist.all_reduce(self._flag, group=group)
+        return pb.tensor
 
     def __call__(self, x, group=None, chunks=1, blocked=False):
         """Full output on every rank.  chunks > 1 splits the rows so that the all-gather of one chunk runs under the

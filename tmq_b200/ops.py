@@ -597,6 +597,32 @@ def ternary_gemm(x, wt, columns, scale=None, bias=None, out_dtype=torch.bfloat16
     return y
 
 
+def ternary_gemm_bcast(x, wt, columns, dst_ptrs, ldy, scale=None, bias=None):
+    """ternary_gemm (bf16 in, bf16 out, tiled kernel) whose epilogue stores the [M, columns] block at every address of
+    `dst_ptrs` (device addresses, this GPU's buffer first, then peer mappings of other GPUs' buffers; row stride `ldy`
+    elements everywhere): GEMM and all-gather of a column-sharded linear in one kernel.  The caller orders buffer
+    reuse and completion across the ranks (see dist.ColumnShardedLinear.fused)."""
+    if x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.dim() != 2:
+        raise RuntimeError("ternary_gemm_bcast: expected a 2-D CUDA bf16 activation tensor")
+    x = x.contiguous()
+    M, K = x.shape
+    N = int(columns)
+    _check_weights("ternary_gemm_bcast", wt, N, K, FMT_BF16)
+    if not 1 <= len(dst_ptrs) <= 8 or int(ldy) < N:
+        raise RuntimeError("ternary_gemm_bcast: 1 .. 8 destinations with a row stride of at least `columns`")
+    if M == 0:
+        return
+    sc = None if scale is None else scale.to(device=x.device, dtype=torch.float32).contiguous()
+    bi = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+    st = gemm_status_word(x.device)
+    with torch.cuda.device(x.device):
+        check(lib().tmq_ternary_gemm_bf16_bcast(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
+                                                _ptr(bi) if bi is not None else None, arr, len(dst_ptrs), M, N, K, int(ldy),
+                                                _ptr(st), _stream(x)), "ternary_gemm_bcast")
+    _launched(x.device)
+
+
 def ternary_gemm_i8(x, wt, columns, path="auto"):
     """Exact int32 Y = x @ T^T with x int8 [M, K]; wt: prepack(..., FMT_I8)."""
     if x.dtype != torch.int8 or x.device.type != "cuda" or x.dim() != 2:
