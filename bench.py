@@ -750,6 +750,17 @@ def wl_gemm(ctx, steps, warmup, M=8192, K=8192, N=28672, chunks=None):
     if world > 1:
         # GEMM + all-gather as one kernel: the epilogue stores this rank's block into every rank's result buffer
         try:
+            # mapping the buffers is a collective step: go on only if it worked on EVERY rank, or the ranks would part
+            ok = torch.ones(1, dtype=torch.int32, device=dev)
+            why = ""
+            try:
+                lin.prepare_fused(M, dev)
+            except Exception as err:                       # noqa: BLE001
+                ok.zero_()
+                why = f" ({type(err).__name__}: {err})"
+            ctx.dist.all_reduce(ok, op=ctx.dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                raise RuntimeError("peer mapping unavailable on some rank" + why)
             ms_fused = ctx.timed(lambda i: lin.fused(X), steps, warmup)
             ops.check_gemm_status(dev)
             ref = lin(X)                                   # NCCL route, row-major

@@ -189,6 +189,14 @@ class ColumnShardedLinear:
         return ops.ternary_gemm(x, self._wt, n, self.scale, self.bias, out_dtype=self._out_dtype(x),
                                 out=None if out is None else out[:, :n])
 
+    def prepare_fused(self, rows, device, group=None):
+        """Result buffer of `rows` rows for fused(), mapped between the ranks on first use (a collective call)."""
+        pb = self._peer.get(rows)
+        if pb is None:
+            pb = self._peer[rows] = PeerBuffer((rows, self.n_total), torch.bfloat16, device, group)
+            self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        return pb
+
     def fused(self, x, group=None):
         """Full row-major [M, n_total] bf16 result on every rank with GEMM and all-gather as ONE kernel: the epilogue
         of this rank's GEMM stores its column block into every rank's result buffer (peer mappings, plain stores over
@@ -201,10 +209,7 @@ class ColumnShardedLinear:
         if x.dtype != torch.bfloat16:
             raise RuntimeError("ColumnShardedLinear.fused: bf16 activations only")
         m = x.shape[0]
-        pb = self._peer.get(m)
-        if pb is None:
-            pb = self._peer[m] = PeerBuffer((m, self.n_total), torch.bfloat16, x.device, group)
-            self._flag = torch.zeros(1, dtype=torch.int32, device=x.device)
+        pb = self.prepare_fused(m, x.device, group)
         if self._wt is None:
             self._wt = ops.prepack(self.packed_shard, self.n1 - self.n0, ops.FMT_BF16)
         order = [self.rank] + [r for r in range(self.world) if r != self.rank]
