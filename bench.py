@@ -659,7 +659,10 @@ def _conv_layers(net, images):
         return size_out
 
     size = add("conv1", net.conv1, size)
-    size = (size + 2 - 3) // 2 + 1                       # 3 x 3 / 2 max pooling
+    pooled = (size + 2 - 3) // 2 + 1                     # 3 x 3 / 2 max pooling, fused into the stem's epilogue:
+    name, conv, m, n, k, nbytes = out[0]                 # the stem writes the pooled map only
+    out[0] = (name, conv, m, n, k, nbytes - 2 * m * n + 2 * images * pooled * pooled * n)
+    size = pooled
     for i, (c1, c2, down) in enumerate(net.blocks):
         if down is not None:
             add(f"block{i}.down", down, size)
@@ -671,8 +674,9 @@ def _conv_layers(net, images):
 
 def _resnet_layer_roofline(net, images, peaks, measured_ms):
     """Per-layer floor of the packed ResNet-18 pass on one GPU: each convolution / linear layer can be no faster than
-    max(2*M*N*K / bf16 peak, (activations in + out at 2 bytes + packed weights) / HBM peak); the sum over the layers against
-    the measured time of the whole pass (which also holds the pooling layers and the launch gaps)."""
+    max(2*M*N*K / bf16 peak, (activations in + out at 2 bytes + packed weights) / HBM peak), the stem counted with the
+    pooled output it writes; the sum over the layers against the measured time of the whole pass (which also holds the
+    average pooling and the launch gaps)."""
     floors = [max(2.0 * m * n * k / (peaks["bf16_tflops"] * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9))
               for _, _, m, n, k, nbytes in _conv_layers(net, images)]
     ideal_ms = sum(floors) * 1e3
@@ -691,7 +695,11 @@ def _resnet_per_layer(net, x, peaks):
     for name, layer, x_in, res in captured:
         if layer is None:
             continue
-        fn = (lambda: layer.from_images(x_in, defer_relu=True)) if name == "conv1" else (lambda: layer(x_in, residual=res))
+        if name == "conv1":      # the pass runs the stem with ReLU and the max pooling fused into its epilogue
+            fn = (lambda: layer.from_images_pooled(x_in)) if layer.from_images_pooled(x_in) is not None \
+                else (lambda: layer.from_images(x_in, defer_relu=True))
+        else:
+            fn = lambda: layer(x_in, residual=res)
         ms = _time_cuda(fn, 5, warm=2)
         m, n, k, nbytes = shapes[name]
         tf = 2.0 * m * n * k / ms / 1e9

@@ -317,6 +317,15 @@ int tmq_stem_rows_k(int C, int ky, int kx, int sx);
 int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y,
                                       int B, int C, int H, int W, int N, int ky, int kx, int sy, int sx, int py, int px,
                                       int relu, int *status, void *stream);
+/* The same convolution followed by ReLU and a 3 x 3 / stride 2 / padding 1 max pooling, all in the epilogue (the ResNet
+ * stem): Y bf16 NHWC [B][OH/2][OW/2][64], 32-byte aligned; N == 64, OH and OW even.  The convolution's own output row is
+ * kept in shared memory (running maximum over the three rows of a pooling window, then over the three columns) and
+ * never written: a quarter of the output traffic and no pooling launch.  Bit-identical to the unfused sequence.
+ * TMQ_ERR_UNSUPPORTED outside those limits.
+ * replaces: conv1 + bn1 + relu + maxpool of the reference's ResNet pipelines (samples/resnet_train.py model definition). */
+int tmq_ternary_conv2d_stem_rows_pool_bf16(const float *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y,
+                                           int B, int C, int H, int W, int N, int ky, int kx, int sy, int sx, int py, int px,
+                                           int *status, void *stream);
 
 /* Max pooling between packed layers: X bf16 NHWC [B][H][W][C] (C % 8 == 0) -> Y [B][OH][OW][C], square window k, stride s,
  * padding p (positions outside the image are ignored), OH = (H + 2p - k) / s + 1; relu != 0 applies max(0, .) as well

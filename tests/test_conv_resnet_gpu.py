@@ -145,6 +145,48 @@ def test_descriptor_patch_stem_matches_conv2d(ops, case):
     assert not bool(bad.any()), (int(bad.sum()), float((got - ref).abs().max()))
 
 
+POOLED_STEM_CASES = [
+    # b, c, h, w, (ky, kx), (sy, sx), (py, px): 64 output channels, even output height and width
+    (2, 3, 224, 224, (7, 7), (2, 2), (3, 3)),        # the ResNet stem: 112 x 112 -> 56 x 56
+    (5, 3, 64, 64, (7, 7), (2, 2), (3, 3)),          # several images per CTA range: image boundaries inside a chunk
+    (300, 2, 12, 16, (3, 3), (2, 2), (1, 1)),        # 6 x 8 rows per image: chunks start inside images (recomputed halo row)
+    (3, 4, 20, 24, (3, 3), (1, 2), (1, 1)),          # vertical stride 1: 20 x 12 -> 10 x 6
+    (1, 3, 8, 8, (3, 3), (2, 2), (1, 1)),            # one tiny image, fewer rows than CTAs
+]
+
+
+@pytest.mark.parametrize("case", POOLED_STEM_CASES)
+def test_pooled_stem_equals_stem_then_relu_then_maxpool(ops, case):
+    """Convolution + ReLU + 3x3/2/1 max pooling in one kernel: bit-identical to the unfused kernels (stem without
+    ReLU, then the pooling kernel with the ReLU folded in) and to torch's max_pool2d of the stem's bf16 output."""
+    b, c, h, w, (ky, kx), (sy, sx), (py, px) = case
+    n = 64
+    gen = torch.Generator().manual_seed(b + c + h + w)
+    x = torch.randn(b, c, h, w, generator=gen).cuda()
+    wgt = torch.randint(-1, 2, (n, c, ky, kx), generator=gen).float()
+    scale = (torch.rand(n, generator=gen) * 0.09 + 0.01).cuda()
+    bias = torch.randn(n, generator=gen).cuda()
+    rows = ops.conv_rows_stem(ops.compactify_ternary(wgt.cuda()), c, ky, kx, sx)
+    wt = ops.prepack(rows, n, ops.FMT_BF16)
+    plain = ops.ternary_conv2d_stem_rows(x, wt, n, (ky, kx), (sy, sx), (py, px), scale, bias, relu=False)
+    fused = ops.ternary_conv2d_stem_rows(x, wt, n, (ky, kx), (sy, sx), (py, px), scale, bias, relu=True, pool=True)
+    ops.check_gemm_status()
+    assert plain is not None and fused is not None
+    want = ops.maxpool2d_nhwc(plain, 3, 2, 1, relu=True)
+    assert fused.shape == want.shape
+    assert torch.equal(fused, want)
+    ref = nn.functional.max_pool2d(torch.relu(plain.float()).permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1)
+    assert torch.equal(fused.float(), ref)
+
+
+def test_pooled_stem_limits(ops):
+    x = torch.randn(1, 3, 18, 18).cuda()                      # 9 x 9 output: odd
+    wgt = torch.randint(-1, 2, (64, 3, 3, 3)).float()
+    rows = ops.conv_rows_stem(ops.compactify_ternary(wgt.cuda()), 3, 3, 3, 2)
+    wt = ops.prepack(rows, 64, ops.FMT_BF16)
+    assert ops.ternary_conv2d_stem_rows(x, wt, 64, (3, 3), (2, 2), (1, 1), relu=True, pool=True) is None
+
+
 def test_residual_fusion_and_patch_kernel(ops):
     gen = torch.Generator().manual_seed(77)
     # residual + ReLU inside the epilogue equals conv, then add, then ReLU

@@ -80,6 +80,7 @@ _SIGNATURES = {
     "tmq_ternary_conv2d_s1_bf16": (c_int, [c_void_p] * 6 + [c_int] * 12 + [c_void_p, c_void_p]),
     "tmq_stem_rows_k": (c_int, [c_int, c_int, c_int, c_int]),
     "tmq_ternary_conv2d_stem_rows_bf16": (c_int, [c_void_p] * 5 + [c_int] * 12 + [c_void_p, c_void_p]),
+    "tmq_ternary_conv2d_stem_rows_pool_bf16": (c_int, [c_void_p] * 5 + [c_int] * 11 + [c_void_p, c_void_p]),
     "tmq_ternary_conv2d_i8": (c_int, [c_void_p] * 3 + [c_int] * 13 + [c_void_p, c_void_p]),
     "tmq_split_f32_bf16": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "tmq_nchw_f32_to_nhwc_bf16": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),

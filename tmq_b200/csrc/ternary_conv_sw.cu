@@ -454,11 +454,14 @@ struct StemRowsArgs {
     int relu;
     int use_tma;     // the sy new rows of a tile arrive by TMA in a staging ring (needs W % 4 == 0)
     int stg_bytes;   // bytes of one staging slot: C planes x sy rows x W floats, rounded up to 128
+    int pool;        // fuse a 3x3 / stride 2 / pad 1 max pooling behind the ReLU: Y is [B][OH/2][OW/2][64]
+    int pool_off;    // byte offset (from the staging area) of the two pooling row buffers
     int *status;
 };
 
 constexpr int kStemRowsThreads = 320;   // warp 0: row copies (TMA), warp 1: MMA, warps 2-5: epilogue, warps 6-9: window
 constexpr int kStemStages = 4;          // staging slots of fp32 input rows
+constexpr int kStemSmemMax = 112 * 1024;  // two CTAs per SM
 
 __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int x, int y, int z) {
     asm volatile(
@@ -535,9 +538,13 @@ ternary_stem_rows_kernel(const __grid_constant__ CUtensorMap tmap_x, const StemR
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     const bool healthy = (*reinterpret_cast<volatile int *>(args.status) == 0);
-    const long long t_begin = (long long)blockIdx.x * args.per_cta;
+    long long t_begin = (long long)blockIdx.x * args.per_cta;
     long long t_end = t_begin + args.per_cta;
     if (t_end > args.tiles) t_end = args.tiles;
+    // pooling: a chunk starts on an even output row (per_cta and OH are even); when that row is not the top of an image,
+    // the odd row above it - the previous CTA's last - is computed here once more, only for its part in the 3-row maximum
+    const bool pool_halo = args.pool && (t_begin % args.OH) != 0;
+    if (pool_halo) t_begin -= 1;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA: the sy new input rows of every non-refill tile
@@ -596,12 +603,17 @@ ternary_stem_rows_kernel(const __grid_constant__ CUtensorMap tmap_x, const StemR
         const bool vec_ok = ((args.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(args.Y) & 31) == 0);
         bool ok = healthy;
         int ti = 0;
+        // pooling buffers, one 128-byte row per pixel, 16-byte chunks XOR-swizzled by the pixel index (a thread walks its
+        // own row): V = running maximum over the rows of the current 3-row window, Hb = finished 3-row maxima of a pooled row
+        uint8_t *Vrow = stg + args.pool_off + p * 128, *Hb = stg + args.pool_off + 128 * 128;
         for (long long tile = t_begin; tile < t_end && ok; tile++, ti++) {
             const int buf = ti & 1;
             ok = ptx::mbar_wait(acc_full + buf, ((uint32_t)(ti >> 1)) & 1u, args.status);
             if (!ok) break;
             ptx::tc_fence_after_sync();
             const long long pix = p < args.OW ? tile * args.OW + p : -1;       // tile = b * OH + oy
+            const int oy = (int)(tile % args.OH);
+            const bool odd = (oy & 1) != 0, emit = odd && !(pool_halo && ti == 0);
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * 64u;
 #pragma unroll 1
             for (int c0 = 0; c0 < 64; c0 += 16) {
@@ -625,7 +637,31 @@ ternary_stem_rows_kernel(const __grid_constant__ CUtensorMap tmap_x, const StemR
                         f[4 * q + 3] = fmaf(__uint_as_float(v[4 * q + 3]), sc4.w, bi4.w);
                     }
                     const long long off = pix * args.N + c0;
-                    if (vec_ok && c0 + 16 <= args.N) {
+                    if (args.pool) {
+                        // rows 2p-1, 2p, 2p+1 -> pooled row p.  Even row: V = max(V, row) (top of an image: V = row, the
+                        // padding row above cannot win against values >= 0); odd row: Hb = max(V, row), then V = row
+#pragma unroll
+                        for (int hc = 0; hc < 2; hc++) {
+                            __nv_bfloat162 o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++)
+                                o[e] = __floats2bfloat162_rn(fmaxf(f[8 * hc + 2 * e], 0.0f), fmaxf(f[8 * hc + 2 * e + 1], 0.0f));
+                            const int chunk = ((c0 >> 3) + hc) ^ (p & 7);
+                            uint4 *vp = reinterpret_cast<uint4 *>(Vrow + chunk * 16);
+                            uint4 cur = *reinterpret_cast<const uint4 *>(o);
+                            if (oy != 0 && !(odd && !emit)) {
+                                const uint4 old = *vp;
+                                const __nv_bfloat162 *a2 = reinterpret_cast<const __nv_bfloat162 *>(&old);
+                                __nv_bfloat162 m[4];
+#pragma unroll
+                                for (int e = 0; e < 4; e++) m[e] = __hmax2_nan(a2[e], o[e]);
+                                const uint4 mx = *reinterpret_cast<const uint4 *>(m);
+                                if (odd) *reinterpret_cast<uint4 *>(Hb + p * 128 + chunk * 16) = mx;
+                                else cur = mx;
+                            }
+                            *vp = cur;
+                        }
+                    } else if (vec_ok && c0 + 16 <= args.N) {
                         ptx::u32x8 o;
 #pragma unroll
                         for (int e = 0; e < 8; e++) {
@@ -640,6 +676,37 @@ ternary_stem_rows_kernel(const __grid_constant__ CUtensorMap tmap_x, const StemR
                             if (c0 + e < args.N) args.Y[off + e] = __float2bfloat16_rn(args.relu ? fmaxf(f[e], 0.0f) : f[e]);
                     }
                 }
+            }
+            if (args.pool && emit) {
+                // the 3-row maxima of the whole row are in Hb: columns 2q-1, 2q, 2q+1 -> pooled pixel q.  Thread = (q, half
+                // of the channels): 64 contiguous output bytes
+                asm volatile("bar.sync 3, 128;" ::: "memory");
+                const int q = p >> 1, half = p & 1;
+                if (q < args.OW / 2) {
+                    const int b = (int)(tile / args.OH);
+                    __nv_bfloat16 *dst = args.Y + (((long long)b * (args.OH / 2) + (oy >> 1)) * (args.OW / 2) + q) * 64 + half * 32;
+                    ptx::u32x8 out[2];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        uint4 m = make_uint4(0, 0, 0, 0);                          // values are >= 0: zero is the padding
+#pragma unroll
+                        for (int dxp = -1; dxp <= 1; dxp++) {
+                            const int px = 2 * q + dxp;
+                            if (px >= 0) {
+                                const uint4 v4 = *reinterpret_cast<const uint4 *>(Hb + px * 128 + (((half * 4 + c) ^ (px & 7)) << 4));
+                                const __nv_bfloat162 *a2 = reinterpret_cast<const __nv_bfloat162 *>(&v4);
+                                __nv_bfloat162 *m2 = reinterpret_cast<__nv_bfloat162 *>(&m);
+#pragma unroll
+                                for (int e = 0; e < 4; e++) m2[e] = __hmax2_nan(m2[e], a2[e]);
+                            }
+                        }
+                        out[c >> 1].v[4 * (c & 1) + 0] = m.x; out[c >> 1].v[4 * (c & 1) + 1] = m.y;
+                        out[c >> 1].v[4 * (c & 1) + 2] = m.z; out[c >> 1].v[4 * (c & 1) + 3] = m.w;
+                    }
+                    ptx::stg_v8(dst, out[0]);
+                    ptx::stg_v8(dst + 16, out[1]);
+                }
+                asm volatile("bar.sync 3, 128;" ::: "memory");                     // Hb may be rewritten by the next odd row
             }
         }
     } else if (warp >= 6) {
@@ -825,9 +892,9 @@ extern "C" int tmq_stem_rows_k(int C, int ky, int kx, int sx) {
     return ky * ((kx * CP + 15) / 16) * 16;
 }
 
-extern "C" int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t *Wt, const float *scale, const float *bias,
-                                                 void *Y, int B, int C, int H, int W, int N, int ky, int kx, int sy, int sx,
-                                                 int py, int px, int relu, int *status, void *stream) {
+static int stem_rows_launch(const float *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int B, int C,
+                            int H, int W, int N, int ky, int kx, int sy, int sx, int py, int px, int relu, int pool,
+                            int *status, void *stream) {
     if (!X || !Wt || !Y || !status) return TMQ_ERR_ARG;
     if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || N <= 0 || ky <= 0 || kx <= 0 || sy <= 0 || sx <= 0 || py < 0 || px < 0)
         return TMQ_ERR_ARG;
@@ -854,6 +921,9 @@ extern "C" int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t 
     a.ring = ky + sy;
     a.tiles = (long long)B * OH;
     a.relu = relu; a.status = status;
+    a.pool = pool;
+    // pooling: zero stands in for the padding, so the values must be >= 0 (ReLU); row and column pairs; the vector path
+    if (pool && (!relu || N != 64 || (OH & 1) || (OW & 1) || !aligned(Y, 32))) return TMQ_ERR_UNSUPPORTED;
     const int win_bytes = (a.ring * a.WB + 127) / 128 * 128;
     // the new rows of a tile by TMA: X as a 3-D tensor [B*C planes][H][W] of fp32, box = C planes x sy rows x W
     CUtensorMap mx = {};
@@ -870,19 +940,33 @@ extern "C" int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t 
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             a.use_tma = 0;
     }
-    const int smem = ky * KR * 2048 + win_bytes + 512 + 256 + 128 + (a.use_tma ? kStemStages * a.stg_bytes : 0) + 1024;
-    if (smem > 100 * 1024) return TMQ_ERR_UNSUPPORTED;
+    a.pool_off = a.use_tma ? kStemStages * a.stg_bytes : 0;
+    const int smem = ky * KR * 2048 + win_bytes + 512 + 256 + 128 + a.pool_off + (pool ? 2 * 128 * 128 : 0) + 1024;
+    if (smem > kStemSmemMax) return TMQ_ERR_UNSUPPORTED;
     const long long want = 2LL * kNumSMs;
     const long long grid = a.tiles < want ? a.tiles : want;
     a.per_cta = (a.tiles + grid - 1) / grid;
+    if (pool) a.per_cta += a.per_cta & 1;          // chunks start on even rows
     const unsigned nblocks = (unsigned)((a.tiles + a.per_cta - 1) / a.per_cta);
     int rc;
     if (CP == 4) {
-        if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<4>, 100 * 1024)) != TMQ_OK) return rc;   // the limit, not this call's size
+        if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<4>, kStemSmemMax)) != TMQ_OK) return rc;   // the limit, not this call's size
         ternary_stem_rows_kernel<4><<<nblocks, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(mx, a);
     } else {
-        if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<8>, 100 * 1024)) != TMQ_OK) return rc;
+        if ((rc = ensure_dynamic_smem(ternary_stem_rows_kernel<8>, kStemSmemMax)) != TMQ_OK) return rc;
         ternary_stem_rows_kernel<8><<<nblocks, kStemRowsThreads, (size_t)smem, (cudaStream_t)stream>>>(mx, a);
     }
     return launch_status();
+}
+
+extern "C" int tmq_ternary_conv2d_stem_rows_bf16(const float *X, const uint32_t *Wt, const float *scale, const float *bias,
+                                                 void *Y, int B, int C, int H, int W, int N, int ky, int kx, int sy, int sx,
+                                                 int py, int px, int relu, int *status, void *stream) {
+    return stem_rows_launch(X, Wt, scale, bias, Y, B, C, H, W, N, ky, kx, sy, sx, py, px, relu, 0, status, stream);
+}
+
+extern "C" int tmq_ternary_conv2d_stem_rows_pool_bf16(const float *X, const uint32_t *Wt, const float *scale,
+                                                      const float *bias, void *Y, int B, int C, int H, int W, int N, int ky,
+                                                      int kx, int sy, int sx, int py, int px, int *status, void *stream) {
+    return stem_rows_launch(X, Wt, scale, bias, Y, B, C, H, W, N, ky, kx, sy, sx, py, px, 1, 1, status, stream);
 }

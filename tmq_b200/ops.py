@@ -875,9 +875,12 @@ def conv_rows_stem(packed, cin, ky, kx, sx):
     return out.reshape(k_rows, -1).contiguous()
 
 
-def ternary_conv2d_stem_rows(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), scale=None, bias=None, relu=False):
+def ternary_conv2d_stem_rows(x, wt, columns, kernel, stride=(1, 1), padding=(0, 0), scale=None, bias=None, relu=False,
+                             pool=False):
     """Few-channel convolution with the patches read straight out of a bf16 copy of the input rows in shared memory (no
     patch matrix, no operand tile): x fp32 NCHW [B, C, H, W], wt = prepack(conv_rows_stem(...), FMT_BF16) -> bf16 NHWC.
+    pool=True fuses ReLU and a 3 x 3 / stride 2 / padding 1 max pooling into the epilogue (64 output channels, even output
+    height and width): the convolution's own output never reaches memory and the result is [B, OH/2, OW/2, 64].
     None when the shape is outside the kernel's limits."""
     if x.dtype != torch.float32 or x.device.type != "cuda" or x.dim() != 4:
         raise RuntimeError("ternary_conv2d_stem_rows: expected a 4-D CUDA fp32 NCHW tensor")
@@ -891,13 +894,20 @@ def ternary_conv2d_stem_rows(x, wt, columns, kernel, stride=(1, 1), padding=(0, 
     if wt.dtype != torch.int32 or wt.shape[0] != n or wt.shape[1] != prepack_row_words(k_rows, FMT_BF16):
         raise RuntimeError("ternary_conv2d_stem_rows: prepacked weights do not match the problem shape")
     oh, ow = (h + 2 * py - ky) // sy + 1, (w + 2 * px - kx) // sx + 1
-    y = torch.empty((b, oh, ow, n), dtype=torch.bfloat16, device=x.device)
+    if pool and (oh % 2 or ow % 2):
+        return None
+    y = torch.empty((b, oh // 2, ow // 2, n) if pool else (b, oh, ow, n), dtype=torch.bfloat16, device=x.device)
     sc, bi = _opt_f32(scale, x.device), _opt_f32(bias, x.device)
     st = gemm_status_word(x.device)
     with torch.cuda.device(x.device):
-        rc = lib().tmq_ternary_conv2d_stem_rows_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
-                                                     _ptr(bi) if bi is not None else None, _ptr(y), b, c, h, w, n, ky, kx,
-                                                     sy, sx, py, px, 1 if relu else 0, _ptr(st), _stream(x))
+        if pool:
+            rc = lib().tmq_ternary_conv2d_stem_rows_pool_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
+                                                              _ptr(bi) if bi is not None else None, _ptr(y), b, c, h, w, n,
+                                                              ky, kx, sy, sx, py, px, _ptr(st), _stream(x))
+        else:
+            rc = lib().tmq_ternary_conv2d_stem_rows_bf16(_ptr(x), _ptr(wt), _ptr(sc) if sc is not None else None,
+                                                         _ptr(bi) if bi is not None else None, _ptr(y), b, c, h, w, n, ky,
+                                                         kx, sy, sx, py, px, 1 if relu else 0, _ptr(st), _stream(x))
     if rc == -6:
         return None
     check(rc, "ternary_conv2d_stem_rows")

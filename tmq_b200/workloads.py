@@ -101,6 +101,13 @@ class PackedConv:
             self.wt_s1 = ops.prepack(ops.conv_rows_skkc(layer.weight.data, self.cin, self.ky, self.kx), self.cout,
                                      ops.FMT_BF16)
 
+    def from_images_pooled(self, images):
+        """Stem + ReLU + 3 x 3 / 2 / 1 max pooling as one kernel, or None when the layer is outside its limits."""
+        if self.wt_rows is None or not self.relu:
+            return None
+        return ops.ternary_conv2d_stem_rows(images, self.wt_rows, self.cout, (self.ky, self.kx), self.stride, self.padding,
+                                            self.scale, self.bias, relu=True, pool=True)
+
     def from_images(self, images, defer_relu=False):
         """Stem route: fp32 NCHW images -> bf16 NHWC feature map, patches built by a kernel (no torch glue).
         defer_relu: leave the activation to the caller (a max pooling that follows applies it for free)."""
@@ -163,8 +170,10 @@ class PackedResNet18:
                 trace(name, layer, x_in, res, y)
             return y
         images = images.float()
-        x = seen("conv1", self.conv1, images, None, self.conv1.from_images(images, defer_relu=True))   # bf16 NHWC
-        x = seen("maxpool", None, x, None, ops.maxpool2d_nhwc(x, 3, 2, 1, relu=True))   # ReLU folded into the pooling
+        x = self.conv1.from_images_pooled(images) if trace is None else None      # stem, ReLU and pooling in one kernel
+        if x is None:                                                              # layerwise trace, or outside its limits
+            x = seen("conv1", self.conv1, images, None, self.conv1.from_images(images, defer_relu=True))   # bf16 NHWC
+            x = seen("maxpool", None, x, None, ops.maxpool2d_nhwc(x, 3, 2, 1, relu=True))   # ReLU folded into the pooling
         for i, (c1, c2, down) in enumerate(self.blocks):
             identity = x if down is None else seen(f"block{i}.down", down, x, None, down(x))
             mid = seen(f"block{i}.conv1", c1, x, None, c1(x))
