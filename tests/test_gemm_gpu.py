@@ -282,3 +282,25 @@ def test_gemv_batched_argument_checks(ops):
     with pytest.raises(RuntimeError):
         ops.ternary_gemv_batched(x[:2].reshape(2, 1, K), [wt], N)  # two activation blocks, one matrix
     assert ops.ternary_gemv_batched(x[:1], [], N) == []
+
+
+@pytest.mark.parametrize("M,N,K,ldy,off", [(300, 256, 1024, 512, 128), (1000, 520, 576, 520, 0), (100, 256, 1024, 256, 0),
+                                           (8192, 1024, 2048, 4096, 1024), (513, 130, 640, 130, 0)])
+def test_gemm_bcast_writes_every_destination(ops, M, N, K, ldy, off):
+    """The all-gather form of the GEMM on one GPU: the same column block goes into several buffers (here all local;
+    across GPUs they are peer mappings).  Tall, vector-friendly shapes take the kernel that parks the tile and writes
+    whole rows; the others the ordinary epilogue.  Every destination must equal the plain GEMM, other columns untouched."""
+    W, P = make_weights(N, K, M + N)
+    gen = torch.Generator().manual_seed(K)
+    X = torch.randn(M, K, generator=gen).to(torch.bfloat16).cuda()
+    scale = (torch.rand(N, generator=gen) * 0.09 + 0.01).cuda()
+    bias = torch.randn(N, generator=gen).cuda()
+    wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16)
+    want = ops.ternary_gemm(X, wt, N, scale, bias, path="tiles")
+    bufs = [torch.full((M, ldy), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    ops.ternary_gemm_bcast(X, wt, N, [b.data_ptr() + off * 2 for b in bufs], ldy, scale, bias)
+    ops.check_gemm_status()
+    for b in bufs:
+        assert torch.equal(b[:, off:off + N], want)
+        rest = torch.cat([b[:, :off], b[:, off + N:]], dim=1)
+        assert bool((rest == 7.0).all())

@@ -73,9 +73,12 @@ struct KindTraits<KIND_I8> {
     static constexpr uint32_t C_FMT = 2u;  // s32 accumulator
 };
 
-template <int KIND, int BN, bool TA>
+// BC: the all-gather form (tmq_ternary_gemm_bf16_bcast on full tiles).  The epilogue first parks the whole bf16 output tile
+// in shared memory (64 KB, paid for with two pipeline stages), hands the accumulator back, and only then writes the tile
+// out - to this GPU and to the peers - in whole 256-byte rows while the next tile is already being multiplied.
+template <int KIND, int BN, bool TA, bool BC = false>
 struct SmemLayout {
-    static constexpr int kStages = StagesFor<BN, TA>::value;
+    static constexpr int kStages = BC ? 4 : StagesFor<BN, TA>::value;
     static constexpr int A_BYTES = TA ? 0 : kTileN * kRowBytes;              // 16 KB, or none: operand in tensor memory
     static constexpr int B_BYTES = BN * kRowBytes;
     static constexpr int RAW_BYTES = kTileN * KindTraits<KIND>::RAW_ROW;     // 2 KB / 4 KB
@@ -83,7 +86,8 @@ struct SmemLayout {
     static constexpr int B_OFF = A_OFF + kStages * A_BYTES;
     static constexpr int RAW_OFF = B_OFF + kStages * B_BYTES;
     static constexpr int STAGE_OFF = RAW_OFF + kStages * RAW_BYTES;          // 4 x 2 KB transpose areas of the epilogue warps
-    static constexpr int BAR_OFF = STAGE_OFF + 4 * 2048;
+    static constexpr int OUT_OFF = STAGE_OFF + 4 * 2048;                     // BC: [BN rows][128 channels] bf16, 16-byte chunks swizzled
+    static constexpr int BAR_OFF = OUT_OFF + (BC ? BN * 256 : 0);
     static constexpr int TOTAL = BAR_OFF + 256 + 1024;                       // + barriers + alignment slack
 };
 
@@ -97,11 +101,11 @@ struct SmemLayout {
 // TA: the decoded weight tile (A operand) lives in tensor memory instead of shared memory.  Per k-block that takes the
 // 16 KB decode write and the 16 KB operand read off shared memory, whose bandwidth otherwise bounds the kernel; the
 // accumulator is then single-buffered for 256-row activation tiles (512 TMEM columns: 256 + 4 x 32 for the A ring).
-template <int KIND, int BN, bool TA>
+template <int KIND, int BN, bool TA, bool BC = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, GemmArgs args) {
     using KT = KindTraits<KIND>;
-    using L = SmemLayout<KIND, BN, TA>;
+    using L = SmemLayout<KIND, BN, TA, BC>;
     constexpr int kStages = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -318,7 +322,24 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(acc_empty + buf);
                 }
-                if (KIND == KIND_BF16 && !args.out_f32) {
+                if (BC) {
+                    // scaled chunk -> per-warp transposition area -> 16-byte vectors (8 channels of one row) -> the parked tile
+#pragma unroll
+                    for (int j = 0; j < 16; j++) stage[j * 32 + lane] = fmaf(__uint_as_float(v[j]), sc, bi);
+                    __syncwarp();
+                    uint8_t *outb = smem + L::OUT_OFF;
+#pragma unroll
+                    for (int it = 0; it < 2; it++) {
+                        const int p = it * 8 + (lane >> 2), cg = (lane & 3) * 8, row = c + p;
+                        const float4 lo = *reinterpret_cast<const float4 *>(stage + p * 32 + cg);
+                        const float4 hi = *reinterpret_cast<const float4 *>(stage + p * 32 + cg + 4);
+                        __align__(16) __nv_bfloat162 o[4] = {__floats2bfloat162_rn(lo.x, lo.y), __floats2bfloat162_rn(lo.z, lo.w),
+                                                             __floats2bfloat162_rn(hi.x, hi.y), __floats2bfloat162_rn(hi.z, hi.w)};
+                        const int chunk = (quarter * 4 + (lane & 3)) ^ (row & 7);
+                        *reinterpret_cast<uint4 *>(outb + row * 256 + chunk * 16) = *reinterpret_cast<const uint4 *>(o);
+                    }
+                    __syncwarp();
+                } else if (KIND == KIND_BF16 && !args.out_f32) {
                     epilogue_chunk_bf16(v, sc, bi, stage, reinterpret_cast<__nv_bfloat16 *>(args.Y), nullptr, m0 + c, args.M,
                                         args.ldy, n0 + quarter * 32, args.N, 0, lane, &args.peers);
                 } else if (n_ok) {
@@ -331,6 +352,27 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         }
                     }
                 }
+            }
+            if (BC) {
+                // the accumulator is back with the MMA warp; write the parked tile out in whole rows (256 bytes of one output
+                // row per half warp), once to this GPU and once to every peer.  Host-checked: N % 8 == 0, ldy % 8 == 0 and
+                // 16-byte aligned destinations, so a vector never straddles the matrix edge
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const uint8_t *outb = smem + L::OUT_OFF;
+                const int col = lane & 15;
+                const long long nn = n0 + col * 8;
+                __nv_bfloat16 *Yl = reinterpret_cast<__nv_bfloat16 *>(args.Y);
+#pragma unroll 4
+                for (int r = (warp - 6) * (BN / 4) + (lane >> 4); r < (warp - 5) * (BN / 4); r += 2) {
+                    const long long m = m0 + r;
+                    if (m < args.M && nn < args.N) {
+                        const uint4 val = *reinterpret_cast<const uint4 *>(outb + r * 256 + ((col ^ (r & 7)) << 4));
+                        const long long off = m * args.ldy + nn;
+                        *reinterpret_cast<uint4 *>(Yl + off) = val;
+                        for (int q = 0; q < args.peers.n; q++) *reinterpret_cast<uint4 *>(args.peers.y[q] + off) = val;
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");                 // the tile area is free for the next tile
             }
         }
     }
@@ -403,10 +445,10 @@ __global__ void wait_selftest_kernel(int *status, long long budget, long long *w
 
 // ---- host side --------------------------------------------------------------------------------------------------------
 
-template <int KIND, int BN, bool TA>
+template <int KIND, int BN, bool TA, bool BC = false>
 static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
     using KT = KindTraits<KIND>;
-    using L = SmemLayout<KIND, BN, TA>;
+    using L = SmemLayout<KIND, BN, TA, BC>;
     const long long KW = prepack_valid_words(a.K), KS = prepack_row_words(a.K, KIND);  // words / stride of a row
     CUtensorMap mx, mw;
     const bool okx = (KIND == KIND_BF16)
@@ -417,11 +459,11 @@ static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cud
     const bool okw = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KS * 4,
                                  KT::RAW_ROW / 4, kTileN, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!okx || !okw) return TMQ_ERR_LAUNCH;
-    const int attr_rc = ensure_dynamic_smem(ternary_gemm_kernel<KIND, BN, TA>, L::TOTAL);
+    const int attr_rc = ensure_dynamic_smem(ternary_gemm_kernel<KIND, BN, TA, BC>, L::TOTAL);
     if (attr_rc != TMQ_OK) return attr_rc;
     const long long ntiles = ((a.N + kTileN - 1) / kTileN) * ((a.M + BN - 1) / BN);
     const unsigned grid = (unsigned)(ntiles < kNumSMs ? ntiles : kNumSMs);
-    ternary_gemm_kernel<KIND, BN, TA><<<grid, kGemmThreads, L::TOTAL, st>>>(mx, mw, a);
+    ternary_gemm_kernel<KIND, BN, TA, BC><<<grid, kGemmThreads, L::TOTAL, st>>>(mx, mw, a);
     return launch_status();
 }
 
@@ -508,6 +550,11 @@ extern "C" int tmq_ternary_gemm_bf16_bcast(const void *X, const uint32_t *Wt, co
         if (q > 0) a.peers.y[q - 1] = reinterpret_cast<__nv_bfloat16 *>(Ys[q]);
     }
     a.peers.n = ndst - 1;
+    // tall problems with vector-friendly geometry: the form that parks the tile and writes whole rows under the next
+    // tile's multiplication; anything else: the ordinary epilogue, which stores to every destination as it goes
+    bool rows_ok = M > 128 && K > 512 && (N % 8) == 0 && (ldy % 8) == 0;
+    for (int q = 0; q < ndst; q++) rows_ok = rows_ok && aligned(Ys[q], 16);
+    if (rows_ok) return launch_gemm<KIND_BF16, 256, true, true>(X, Wt, a, (cudaStream_t)stream);
     return dispatch_gemm<KIND_BF16>(X, Wt, a, (cudaStream_t)stream);
 }
 
