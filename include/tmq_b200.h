@@ -184,6 +184,19 @@ int tmq_ternary_gemm_bf16(const void *X, const uint32_t *Wt, const float *scale,
 int tmq_ternary_gemm_i8(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
                         int *status, void *stream);
 
+/* Split-K forms for skinny problems (M <= 256 with fewer 128-channel output tiles than SMs, e.g. a decode batch of 32 - 256
+ * rows against an 11008 x 4096 matrix: 86 - 172 tiles on 148 SMs): K is split over up to floor(148 / tiles) CTAs per tile
+ * (at least four k-blocks each), the raw accumulators go to `workspace` and a second small kernel adds them in split
+ * order and applies scale / bias: deterministic, int32 results exact.  workspace: tmq_ternary_gemm_workspace_bytes(M, N, K,
+ * int8_activations) bytes of device scratch, 16-byte aligned; 0 bytes = the problem is not split; NULL / too small =
+ * the plain kernel runs.  Everything else as tmq_ternary_gemm_bf16 / _i8. */
+size_t tmq_ternary_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int int8_activations);
+int tmq_ternary_gemm_bf16_splitk(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y, int64_t M,
+                                 int64_t N, int64_t K, int64_t ldy, int out_f32, void *workspace, size_t workspace_bytes,
+                                 int *status, void *stream);
+int tmq_ternary_gemm_i8_splitk(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K, int64_t ldy,
+                               void *workspace, size_t workspace_bytes, int *status, void *stream);
+
 /* GEMM + all-gather in one kernel: tmq_ternary_gemm_bf16 (bf16 output) whose epilogue stores every output vector into
  * ndst (1 .. 8) buffers: Ys[0] in this GPU's memory and Ys[1 ..] in OTHER GPUs' memory (peer mappings of buffers of the
  * same shape, e.g. CUDA IPC or symmetric memory), all with row stride ldy.  A rank of a column-sharded linear passes

@@ -304,3 +304,31 @@ def test_gemm_bcast_writes_every_destination(ops, M, N, K, ldy, off):
         assert torch.equal(b[:, off:off + N], want)
         rest = torch.cat([b[:, :off], b[:, off + N:]], dim=1)
         assert bool((rest == 7.0).all())
+
+
+# Skinny problems with fewer output tiles than SMs: K is split over several CTAs per tile and a second kernel sums the
+# partial results in split order (ops takes that route on its own whenever the C library reports a workspace size).
+SPLIT_K = [(64, 4096, 4096), (17, 1000, 2048), (100, 2304, 1024), (256, 640, 8192), (1, 512, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", SPLIT_K)
+def test_split_k_gemm_matches_oracle(ops, M, N, K):
+    from tmq_b200 import _lib
+    assert _lib.lib().tmq_ternary_gemm_workspace_bytes(M, N, K, 0) > 0          # these shapes are split
+    W, P = make_weights(N, K, M + N + K)
+    rng = np.random.default_rng(K + M)
+    X8 = rng.integers(-127, 128, (M, K)).astype(np.int8)
+    wt8 = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_I8)
+    Y8 = ops.ternary_gemm_i8(torch.from_numpy(X8).cuda(), wt8, N, path="tiles")
+    assert np.array_equal(Y8.cpu().numpy(), T.gemm_i8_fast(X8, P, N))
+    gen = torch.Generator().manual_seed(K)
+    X = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    scale = torch.rand(N, generator=gen) * 0.09 + 0.01
+    bias = torch.randn(N, generator=gen)
+    wt = ops.prepack(torch.from_numpy(P).cuda(), N, ops.FMT_BF16)
+    ref = T.gemm_f64_fast(X.float().numpy(), P, N) * scale.double().numpy()[None, :] + bias.double().numpy()[None, :]
+    y32 = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.float32, path="tiles")
+    ybf = ops.ternary_gemm(X.cuda(), wt, N, scale.cuda(), bias.cuda(), out_dtype=torch.bfloat16, path="tiles")
+    ops.check_gemm_status()
+    assert np.abs(y32.double().cpu().numpy() - ref).max() <= 1e-5 * np.abs(ref).max()
+    assert torch.equal(ybf, y32.to(torch.bfloat16))

@@ -62,6 +62,11 @@ _SIGNATURES = {
     "tmq_prepack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "tmq_ternary_gemm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                       c_int64, c_int, c_void_p, c_void_p]),
+    "tmq_ternary_gemm_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int]),
+    "tmq_ternary_gemm_bf16_splitk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                             c_int64, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "tmq_ternary_gemm_i8_splitk": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
+                                           c_size_t, c_void_p, c_void_p]),
     "tmq_ternary_gemm_bf16_bcast": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64,
                                             c_int64, c_int64, c_void_p, c_void_p]),
     "tmq_ternary_gemv_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

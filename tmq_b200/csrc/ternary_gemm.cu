@@ -56,7 +56,26 @@ struct GemmArgs {
     int out_f32;         // bf16 kind: write fp32 instead of bf16
     int *status;
     PeerList peers;      // bf16 output only: the same block is also stored into these buffers (other GPUs' memory)
+    // K split over several CTAs per output tile (skinny problems with fewer tiles than SMs): raw accumulators go to
+    // partial[split][M][N] (fp32 or int32) and a second kernel sums them in split order and applies scale / bias
+    void *partial;
+    int splits;          // >= 1
+    int kb_per_split;    // k-blocks of one split
 };
+
+// Work unit u = (output tile, K split): the k-blocks [kb0, kb1) of tile u / splits.
+struct GemmUnit {
+    long long tile;
+    int split, kb0, kb1;
+};
+__device__ __forceinline__ GemmUnit gemm_unit(const GemmArgs &a, long long u, int nkb) {
+    GemmUnit q;
+    q.tile = u / a.splits;
+    q.split = (int)(u - q.tile * a.splits);
+    q.kb0 = q.split * a.kb_per_split;
+    q.kb1 = q.kb0 + a.kb_per_split < nkb ? q.kb0 + a.kb_per_split : nkb;
+    return q;
+}
 
 template <int KIND>
 struct KindTraits;
@@ -120,7 +139,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     const int nkb = (int)((args.K + KT::BK - 1) / KT::BK);
     const long long tiles_n = (args.N + kTileN - 1) / kTileN;
     const long long tiles_m = (args.M + BN - 1) / BN;
-    const long long ntiles = tiles_n * tiles_m;
+    const long long ntiles = tiles_n * tiles_m * args.splits;   // work units: (tile, K split)
     constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;
     constexpr int ACC_BUFS = (TA && BN > 128) ? 1 : 2;
     constexpr uint32_t A_COLS = kRowBytes / 4;                       // one k-block of a row: 32 columns
@@ -159,9 +178,10 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         if (lane == 0 && healthy) {
             long long it = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                const int n0 = (int)(tile % tiles_n) * kTileN, m0 = (int)(tile / tiles_n) * BN;
-                for (int kb = 0; kb < nkb; kb++, it++) {
+            for (long long u = blockIdx.x; u < ntiles && ok; u += gridDim.x) {
+                const GemmUnit q = gemm_unit(args, u, nkb);
+                const int n0 = (int)(q.tile % tiles_n) * kTileN, m0 = (int)(q.tile / tiles_n) * BN;
+                for (int kb = q.kb0; kb < q.kb1; kb++, it++) {
                     const int s = (int)(it % kStages);
                     const uint32_t ph = (uint32_t)(it / kStages) & 1u;
                     ok = ptx::mbar_wait(empty + s, ph ^ 1u, args.status);
@@ -181,7 +201,8 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             long long it = 0;
             int ti = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ti++) {
+            for (long long u = blockIdx.x; u < ntiles && ok; u += gridDim.x, ti++) {
+                const GemmUnit q = gemm_unit(args, u, nkb);
                 const int buf = ACC_BUFS == 2 ? (ti & 1) : 0;
                 const uint32_t use = (uint32_t)(ACC_BUFS == 2 ? (ti >> 1) : ti);
                 // the epilogue must have drained this accumulator (its previous use)
@@ -189,7 +210,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * ACC_COLS;
-                for (int kb = 0; kb < nkb; kb++, it++) {
+                for (int kb = q.kb0; kb < q.kb1; kb++, it++) {
                     const int s = (int)(it % kStages);
                     const uint32_t ph = (uint32_t)(it / kStages) & 1u;
                     ok = ptx::mbar_wait_warp(full_a + s, ph, args.status);
@@ -201,7 +222,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     if (ptx::elect_one()) {
 #pragma unroll
                         for (int k4 = 0; k4 < kRowBytes / 32; k4++) {  // 32 bytes of K per instruction (16 bf16 / 32 int8)
-                            const uint32_t accum = (kb > 0 || k4 > 0) ? 1u : 0u;
+                            const uint32_t accum = (kb > q.kb0 || k4 > 0) ? 1u : 0u;
                             if (TA) {
                                 if (KIND == KIND_BF16) ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, accum);
                                 else ptx::umma_i8_ts(d_tmem, a_tmem + 8 * k4, b_desc + 2 * k4, idesc, accum);
@@ -222,12 +243,13 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         // ---------------------------------------------------------------- decode warps (2..5)
         // weight row inside the tile, 0..127.  With the operand in tensor memory a warp may only touch the lane quarter
         // (warp index % 4), so rows are dealt accordingly.
-        const int row = TA ? ((warp & 3) * 32 + lane) : (threadIdx.x - 64);
+        const int row = (warp & 3) * 32 + lane;
         const int sw = row & 7;
         bool ok = healthy;
         long long it = 0;
-        for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < nkb; kb++, it++) {
+        for (long long u = blockIdx.x; u < ntiles && ok; u += gridDim.x) {
+            const GemmUnit q = gemm_unit(args, u, nkb);
+            for (int kb = q.kb0; kb < q.kb1; kb++, it++) {
                 const int s = (int)(it % kStages);
                 const uint32_t ph = (uint32_t)(it / kStages) & 1u;
                 ok = ptx::mbar_wait(full_raw + s, ph, args.status);
@@ -297,8 +319,9 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         float *stage = reinterpret_cast<float *>(smem + L::STAGE_OFF) + (warp - 6) * 512;
         bool ok = healthy;
         int ti = 0;
-        for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ti++) {
-            const long long n0 = (tile % tiles_n) * kTileN, m0 = (tile / tiles_n) * BN;
+        for (long long u = blockIdx.x; u < ntiles && ok; u += gridDim.x, ti++) {
+            const GemmUnit q = gemm_unit(args, u, nkb);
+            const long long n0 = (q.tile % tiles_n) * kTileN, m0 = (q.tile / tiles_n) * BN;
             const int buf = ACC_BUFS == 2 ? (ti & 1) : 0;
             ok = ptx::mbar_wait(acc_full + buf, (uint32_t)(ACC_BUFS == 2 ? (ti >> 1) : ti) & 1u, args.status);
             if (!ok) break;
@@ -322,7 +345,17 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(acc_empty + buf);
                 }
-                if (BC) {
+                if (args.partial) {
+                    // split K: raw accumulators of this split; a warp writes 128 contiguous bytes per output row
+                    uint32_t *part = reinterpret_cast<uint32_t *>(args.partial) + (long long)q.split * args.M * args.N;
+                    if (n_ok) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const long long m = m0 + c + j;
+                            if (m < args.M) part[m * args.N + n] = v[j];
+                        }
+                    }
+                } else if (BC) {
                     // scaled chunk -> per-warp transposition area -> 16-byte vectors (8 channels of one row) -> the parked tile
 #pragma unroll
                     for (int j = 0; j < 16; j++) stage[j * 32 + lane] = fmaf(__uint_as_float(v[j]), sc, bi);
@@ -443,12 +476,37 @@ __global__ void wait_selftest_kernel(int *status, long long budget, long long *w
     }
 }
 
+// Split-K epilogue: Y = scale * (sum over the splits, in split order) + bias.  KIND 0: fp32 partial sums of operands
+// carried as +-2 (the factor 0.5 is applied here), output bf16 or fp32; KIND 1: exact int32.
+template <int KIND>
+__global__ void __launch_bounds__(256) gemm_combine_kernel(const void *__restrict__ partial, const float *__restrict__ scale,
+                                                           const float *__restrict__ bias, void *__restrict__ Y, long long M,
+                                                           long long N, long long ldy, int splits, int out_f32) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M * N) return;
+    const long long m = i / N, n = i - m * N;
+    if (KIND == KIND_I8) {
+        const int *p = reinterpret_cast<const int *>(partial);
+        int s = p[i];
+        for (int q = 1; q < splits; q++) s += p[(long long)q * M * N + i];
+        reinterpret_cast<int *>(Y)[m * ldy + n] = s;
+    } else {
+        const float *p = reinterpret_cast<const float *>(partial);
+        float s = p[i];
+        for (int q = 1; q < splits; q++) s += p[(long long)q * M * N + i];
+        const float f = fmaf(s, 0.5f * (scale ? scale[n] : 1.0f), bias ? bias[n] : 0.0f);
+        if (out_f32) reinterpret_cast<float *>(Y)[m * ldy + n] = f;
+        else reinterpret_cast<__nv_bfloat16 *>(Y)[m * ldy + n] = __float2bfloat16_rn(f);
+    }
+}
+
 // ---- host side --------------------------------------------------------------------------------------------------------
 
 template <int KIND, int BN, bool TA, bool BC = false>
-static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
+static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a_in, cudaStream_t st) {
     using KT = KindTraits<KIND>;
     using L = SmemLayout<KIND, BN, TA, BC>;
+    GemmArgs a = a_in;
     const long long KW = prepack_valid_words(a.K), KS = prepack_row_words(a.K, KIND);  // words / stride of a row
     CUtensorMap mx, mw;
     const bool okx = (KIND == KIND_BF16)
@@ -461,10 +519,36 @@ static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cud
     if (!okx || !okw) return TMQ_ERR_LAUNCH;
     const int attr_rc = ensure_dynamic_smem(ternary_gemm_kernel<KIND, BN, TA, BC>, L::TOTAL);
     if (attr_rc != TMQ_OK) return attr_rc;
-    const long long ntiles = ((a.N + kTileN - 1) / kTileN) * ((a.M + BN - 1) / BN);
+    const long long nkb = (a.K + KT::BK - 1) / KT::BK;
+    if (a.splits < 1 || !a.partial) a.splits = 1;
+    a.kb_per_split = (int)((nkb + a.splits - 1) / a.splits);
+    a.splits = (int)((nkb + a.kb_per_split - 1) / a.kb_per_split);      // no empty split
+    if (a.splits == 1) a.partial = nullptr;
+    const long long ntiles = ((a.N + kTileN - 1) / kTileN) * ((a.M + BN - 1) / BN) * a.splits;
     const unsigned grid = (unsigned)(ntiles < kNumSMs ? ntiles : kNumSMs);
     ternary_gemm_kernel<KIND, BN, TA, BC><<<grid, kGemmThreads, L::TOTAL, st>>>(mx, mw, a);
+    int rc = launch_status();
+    if (rc != TMQ_OK || !a.partial) return rc;
+    const long long total = a.M * a.N;
+    gemm_combine_kernel<KIND><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a.partial, a.scale, a.bias, a.Y, a.M, a.N, a.ldy,
+                                                                               a.splits, a.out_f32);
     return launch_status();
+}
+
+// K splits for a problem whose output tiles do not fill the machine: as many as keep all units in ONE wave and leave
+// every split at least four k-blocks.  More splits than that do not pay: on 11008 x 4096 (86 tiles) three splits in two
+// waves measured 18.5 us against 18.7 us unsplit at 16 rows and twice the time at 256 rows (partial sums + combine).
+// 1 = do not split.
+template <int KIND>
+static int gemm_splits(long long M, long long N, long long K) {
+    if (M > 256) return 1;
+    const long long BN = M > 128 ? 256 : M > 64 ? 128 : M > 32 ? 64 : 32;
+    const long long tiles = ((N + kTileN - 1) / kTileN) * ((M + BN - 1) / BN);
+    const long long nkb = (K + KindTraits<KIND>::BK - 1) / KindTraits<KIND>::BK;
+    long long splits = kNumSMs / tiles;
+    if (splits > nkb / 4) splits = nkb / 4;
+    if (M > 128 && splits < 6) splits = 1;      // 256-row tiles: the partial sums cost more than four splits save
+    return splits < 1 ? 1 : (int)splits;
 }
 
 template <int KIND>
@@ -533,7 +617,7 @@ extern "C" int tmq_ternary_gemm_bf16(const void *X, const uint32_t *Wt, const fl
     int rc = check_gemm_common(X, Wt, Y, M, N, K, ldy, status, 2);
     if (rc != TMQ_OK) return rc;
     if (!aligned(Y, out_f32 ? 4 : 2)) return TMQ_ERR_ALIGN;
-    GemmArgs a = {scale, bias, Y, M, N, K, ldy, out_f32, status, {}};
+    GemmArgs a = {scale, bias, Y, M, N, K, ldy, out_f32, status, {}, nullptr, 1, 0};
     return dispatch_gemm<KIND_BF16>(X, Wt, a, (cudaStream_t)stream);
 }
 
@@ -543,7 +627,7 @@ extern "C" int tmq_ternary_gemm_bf16_bcast(const void *X, const uint32_t *Wt, co
     if (!Ys || ndst < 1 || ndst > 1 + kMaxPeers) return TMQ_ERR_ARG;
     int rc = check_gemm_common(X, Wt, Ys[0], M, N, K, ldy, status, 2);
     if (rc != TMQ_OK) return rc;
-    GemmArgs a = {scale, bias, Ys[0], M, N, K, ldy, 0, status, {}};
+    GemmArgs a = {scale, bias, Ys[0], M, N, K, ldy, 0, status, {}, nullptr, 1, 0};
     for (int q = 0; q < ndst; q++) {
         if (!Ys[q]) return TMQ_ERR_ARG;
         if (!aligned(Ys[q], 2)) return TMQ_ERR_ALIGN;
@@ -563,6 +647,41 @@ extern "C" int tmq_ternary_gemm_i8(const int8_t *X, const uint32_t *Wt, int32_t 
     int rc = check_gemm_common(X, Wt, Y, M, N, K, ldy, status, 1);
     if (rc != TMQ_OK) return rc;
     if (!aligned(Y, 4)) return TMQ_ERR_ALIGN;
-    GemmArgs a = {nullptr, nullptr, Y, M, N, K, ldy, 0, status, {}};
+    GemmArgs a = {nullptr, nullptr, Y, M, N, K, ldy, 0, status, {}, nullptr, 1, 0};
+    return dispatch_gemm<KIND_I8>(X, Wt, a, (cudaStream_t)stream);
+}
+
+extern "C" size_t tmq_ternary_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int int8_activations) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const int splits = int8_activations ? gemm_splits<KIND_I8>(M, N, K) : gemm_splits<KIND_BF16>(M, N, K);
+    return splits > 1 ? (size_t)splits * (size_t)M * (size_t)N * 4 : 0;
+}
+
+extern "C" int tmq_ternary_gemm_bf16_splitk(const void *X, const uint32_t *Wt, const float *scale, const float *bias, void *Y,
+                                            int64_t M, int64_t N, int64_t K, int64_t ldy, int out_f32, void *workspace,
+                                            size_t workspace_bytes, int *status, void *stream) {
+    int rc = check_gemm_common(X, Wt, Y, M, N, K, ldy, status, 2);
+    if (rc != TMQ_OK) return rc;
+    if (!aligned(Y, out_f32 ? 4 : 2) || !aligned(workspace, 16)) return TMQ_ERR_ALIGN;
+    GemmArgs a = {scale, bias, Y, M, N, K, ldy, out_f32, status, {}, nullptr, 1, 0};
+    const size_t need = tmq_ternary_gemm_workspace_bytes(M, N, K, 0);
+    if (need > 0 && workspace && workspace_bytes >= need) {
+        a.partial = workspace;
+        a.splits = gemm_splits<KIND_BF16>(M, N, K);
+    }
+    return dispatch_gemm<KIND_BF16>(X, Wt, a, (cudaStream_t)stream);
+}
+
+extern "C" int tmq_ternary_gemm_i8_splitk(const int8_t *X, const uint32_t *Wt, int32_t *Y, int64_t M, int64_t N, int64_t K,
+                                          int64_t ldy, void *workspace, size_t workspace_bytes, int *status, void *stream) {
+    int rc = check_gemm_common(X, Wt, Y, M, N, K, ldy, status, 1);
+    if (rc != TMQ_OK) return rc;
+    if (!aligned(Y, 4) || !aligned(workspace, 16)) return TMQ_ERR_ALIGN;
+    GemmArgs a = {nullptr, nullptr, Y, M, N, K, ldy, 0, status, {}, nullptr, 1, 0};
+    const size_t need = tmq_ternary_gemm_workspace_bytes(M, N, K, 1);
+    if (need > 0 && workspace && workspace_bytes >= need) {
+        a.partial = workspace;
+        a.splits = gemm_splits<KIND_I8>(M, N, K);
+    }
     return dispatch_gemm<KIND_I8>(X, Wt, a, (cudaStream_t)stream);
 }
