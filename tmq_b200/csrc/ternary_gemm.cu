@@ -68,8 +68,13 @@ struct GemmUnit {
     long long tile;
     int split, kb0, kb1;
 };
+template <bool EXT>
 __device__ __forceinline__ GemmUnit gemm_unit(const GemmArgs &a, long long u, int nkb) {
     GemmUnit q;
+    if (!EXT) {                 // the plain kernel: one unit per tile, all of K
+        q.tile = u; q.split = 0; q.kb0 = 0; q.kb1 = nkb;
+        return q;
+    }
     q.tile = u / a.splits;
     q.split = (int)(u - q.tile * a.splits);
     q.kb0 = q.split * a.kb_per_split;
@@ -120,10 +125,14 @@ struct SmemLayout {
 // TA: the decoded weight tile (A operand) lives in tensor memory instead of shared memory.  Per k-block that takes the
 // 16 KB decode write and the 16 KB operand read off shared memory, whose bandwidth otherwise bounds the kernel; the
 // accumulator is then single-buffered for 256-row activation tiles (512 TMEM columns: 256 + 4 x 32 for the A ring).
-template <int KIND, int BN, bool TA, bool BC = false>
+// MODE 0: the plain GEMM.  MODE 1 (BC): the all-gather form on full tiles.  MODE 2 (EXT): K split over CTAs (partial sums
+// to a workspace) and / or further destinations written from the ordinary epilogue.  The extras are compiled out of
+// MODE 0: with the accumulator single-buffered its epilogue is on the critical path, and carrying them cost 3 - 4 %.
+template <int KIND, int BN, bool TA, int MODE = 0>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, GemmArgs args) {
     using KT = KindTraits<KIND>;
+    constexpr bool BC = MODE == 1, EXT = MODE == 2;
     using L = SmemLayout<KIND, BN, TA, BC>;
     constexpr int kStages = L::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -139,7 +148,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     const int nkb = (int)((args.K + KT::BK - 1) / KT::BK);
     const long long tiles_n = (args.N + kTileN - 1) / kTileN;
     const long long tiles_m = (args.M + BN - 1) / BN;
-    const long long ntiles = tiles_n * tiles_m * args.splits;   // work units: (tile, K split)
+    const long long ntiles = tiles_n * tiles_m * (EXT ? args.splits : 1);   // work units: (tile, K split)
     constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;
     constexpr int ACC_BUFS = (TA && BN > 128) ? 1 : 2;
     constexpr uint32_t A_COLS = kRowBytes / 4;                       // one k-block of a row: 32 columns
@@ -179,7 +188,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             long long it = 0;
             bool ok = true;
             for (long long u = blockIdx.x; u < ntiles && ok; u += gridDim.x) {
-                const GemmUnit q = gemm_unit(args, u, nkb);
+                const GemmUnit q = gemm_unit<EXT>(args, u, nkb);
                 const int n0 = (int)(q.tile % tiles_n) * kTileN, m0 = (int)(q.tile / tiles_n) * BN;
                 for (int kb = q.kb0; kb < q.kb1; kb++, it++) {
                     const int s = (int)(it % kStages);
@@ -202,7 +211,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             int ti = 0;
             bool ok = true;
             for (long long u = blockIdx.x; u < ntiles && ok; u += gridDim.x, ti++) {
-                const GemmUnit q = gemm_unit(args, u, nkb);
+                const GemmUnit q = gemm_unit<EXT>(args, u, nkb);
                 const int buf = ACC_BUFS == 2 ? (ti & 1) : 0;
                 const uint32_t use = (uint32_t)(ACC_BUFS == 2 ? (ti >> 1) : ti);
                 // the epilogue must have drained this accumulator (its previous use)
@@ -248,7 +257,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         bool ok = healthy;
         long long it = 0;
         for (long long u = blockIdx.x; u < ntiles && ok; u += gridDim.x) {
-            const GemmUnit q = gemm_unit(args, u, nkb);
+            const GemmUnit q = gemm_unit<EXT>(args, u, nkb);
             for (int kb = q.kb0; kb < q.kb1; kb++, it++) {
                 const int s = (int)(it % kStages);
                 const uint32_t ph = (uint32_t)(it / kStages) & 1u;
@@ -320,7 +329,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         bool ok = healthy;
         int ti = 0;
         for (long long u = blockIdx.x; u < ntiles && ok; u += gridDim.x, ti++) {
-            const GemmUnit q = gemm_unit(args, u, nkb);
+            const GemmUnit q = gemm_unit<EXT>(args, u, nkb);
             const long long n0 = (q.tile % tiles_n) * kTileN, m0 = (q.tile / tiles_n) * BN;
             const int buf = ACC_BUFS == 2 ? (ti & 1) : 0;
             ok = ptx::mbar_wait(acc_full + buf, (uint32_t)(ACC_BUFS == 2 ? (ti >> 1) : ti) & 1u, args.status);
@@ -345,7 +354,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(acc_empty + buf);
                 }
-                if (args.partial) {
+                if (EXT && args.partial) {
                     // split K: raw accumulators of this split; a warp writes 128 contiguous bytes per output row
                     uint32_t *part = reinterpret_cast<uint32_t *>(args.partial) + (long long)q.split * args.M * args.N;
                     if (n_ok) {
@@ -374,7 +383,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     __syncwarp();
                 } else if (KIND == KIND_BF16 && !args.out_f32) {
                     epilogue_chunk_bf16(v, sc, bi, stage, reinterpret_cast<__nv_bfloat16 *>(args.Y), nullptr, m0 + c, args.M,
-                                        args.ldy, n0 + quarter * 32, args.N, 0, lane, &args.peers);
+                                        args.ldy, n0 + quarter * 32, args.N, 0, lane, EXT ? &args.peers : nullptr);
                 } else if (n_ok) {
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
@@ -502,10 +511,10 @@ __global__ void __launch_bounds__(256) gemm_combine_kernel(const void *__restric
 
 // ---- host side --------------------------------------------------------------------------------------------------------
 
-template <int KIND, int BN, bool TA, bool BC = false>
+template <int KIND, int BN, bool TA, int MODE = 0>
 static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a_in, cudaStream_t st) {
     using KT = KindTraits<KIND>;
-    using L = SmemLayout<KIND, BN, TA, BC>;
+    using L = SmemLayout<KIND, BN, TA, MODE == 1>;
     GemmArgs a = a_in;
     const long long KW = prepack_valid_words(a.K), KS = prepack_row_words(a.K, KIND);  // words / stride of a row
     CUtensorMap mx, mw;
@@ -517,16 +526,16 @@ static int launch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a_in, 
     const bool okw = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, Wt, (uint64_t)KW, (uint64_t)a.N, (uint64_t)KS * 4,
                                  KT::RAW_ROW / 4, kTileN, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!okx || !okw) return TMQ_ERR_LAUNCH;
-    const int attr_rc = ensure_dynamic_smem(ternary_gemm_kernel<KIND, BN, TA, BC>, L::TOTAL);
+    const int attr_rc = ensure_dynamic_smem(ternary_gemm_kernel<KIND, BN, TA, MODE>, L::TOTAL);
     if (attr_rc != TMQ_OK) return attr_rc;
     const long long nkb = (a.K + KT::BK - 1) / KT::BK;
-    if (a.splits < 1 || !a.partial) a.splits = 1;
+    if (a.splits < 1 || !a.partial || MODE != 2) a.splits = 1;
     a.kb_per_split = (int)((nkb + a.splits - 1) / a.splits);
     a.splits = (int)((nkb + a.kb_per_split - 1) / a.kb_per_split);      // no empty split
     if (a.splits == 1) a.partial = nullptr;
     const long long ntiles = ((a.N + kTileN - 1) / kTileN) * ((a.M + BN - 1) / BN) * a.splits;
     const unsigned grid = (unsigned)(ntiles < kNumSMs ? ntiles : kNumSMs);
-    ternary_gemm_kernel<KIND, BN, TA, BC><<<grid, kGemmThreads, L::TOTAL, st>>>(mx, mw, a);
+    ternary_gemm_kernel<KIND, BN, TA, MODE><<<grid, kGemmThreads, L::TOTAL, st>>>(mx, mw, a);
     int rc = launch_status();
     if (rc != TMQ_OK || !a.partial) return rc;
     const long long total = a.M * a.N;
@@ -551,18 +560,23 @@ static int gemm_splits(long long M, long long N, long long K) {
     return splits < 1 ? 1 : (int)splits;
 }
 
-template <int KIND>
-static int dispatch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
+template <int KIND, int MODE>
+static int dispatch_gemm_mode(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
     // bf16: weight operand in tensor memory (+3 .. +13 % measured); int8: in shared memory (the tensor-memory form
     // measured 20 % slower there)
     constexpr bool TA = (KIND == KIND_BF16);
     // short reductions (a handful of k-blocks per tile) are bound by the epilogue: 128-row tiles keep the accumulator
     // double-buffered in the tensor-memory-operand form, so the drain of one tile hides under the next
-    if (a.M > 128 && !(TA && a.K <= 512)) return launch_gemm<KIND, 256, TA>(X, Wt, a, st);
-    if (a.M > 128) return launch_gemm<KIND, 128, TA>(X, Wt, a, st);
-    if (a.M > 64) return launch_gemm<KIND, 128, TA>(X, Wt, a, st);
-    if (a.M > 32) return launch_gemm<KIND, 64, TA>(X, Wt, a, st);
-    return launch_gemm<KIND, 32, TA>(X, Wt, a, st);
+    if (a.M > 128 && !(TA && a.K <= 512)) return launch_gemm<KIND, 256, TA, MODE>(X, Wt, a, st);
+    if (a.M > 64) return launch_gemm<KIND, 128, TA, MODE>(X, Wt, a, st);
+    if (a.M > 32) return launch_gemm<KIND, 64, TA, MODE>(X, Wt, a, st);
+    return launch_gemm<KIND, 32, TA, MODE>(X, Wt, a, st);
+}
+
+template <int KIND>
+static int dispatch_gemm(const void *X, const uint32_t *Wt, const GemmArgs &a, cudaStream_t st) {
+    if ((a.partial && a.splits > 1) || a.peers.n > 0) return dispatch_gemm_mode<KIND, 2>(X, Wt, a, st);
+    return dispatch_gemm_mode<KIND, 0>(X, Wt, a, st);
 }
 
 static int check_gemm_common(const void *X, const uint32_t *Wt, const void *Y, long long M, long long N, long long K,
@@ -638,7 +652,7 @@ extern "C" int tmq_ternary_gemm_bf16_bcast(const void *X, const uint32_t *Wt, co
     // tile's multiplication; anything else: the ordinary epilogue, which stores to every destination as it goes
     bool rows_ok = M > 128 && K > 512 && (N % 8) == 0 && (ldy % 8) == 0;
     for (int q = 0; q < ndst; q++) rows_ok = rows_ok && aligned(Ys[q], 16);
-    if (rows_ok) return launch_gemm<KIND_BF16, 256, true, true>(X, Wt, a, (cudaStream_t)stream);
+    if (rows_ok) return launch_gemm<KIND_BF16, 256, true, 1>(X, Wt, a, (cudaStream_t)stream);
     return dispatch_gemm<KIND_BF16>(X, Wt, a, (cudaStream_t)stream);
 }
 
