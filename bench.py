@@ -774,7 +774,7 @@ def wl_gemm(ctx, steps, warmup, M=8192, K=8192, N=28672, chunks=None):
             ref = lin(X)                                   # NCCL route, row-major
             same = bool(torch.equal(ref, lin.fused(X)))
             fused = {"fused_gemm_allgather_ms": ms_fused, "fused_tops_equiv": 2 * M * N * K / ms_fused / 1e9,
-                     "fused_equals_nccl_route": same, "peer_mapping": lin._peer[M].kind}
+                     "fused_equals_nccl_route": same, "peer_mapping": lin._peer[M][0].kind}
         except Exception as err:                           # noqa: BLE001 - reported, the NCCL route stays the record
             fused = {"fused_gemm_allgather_error": f"{type(err).__name__}: {err}"[:300]}
     route = "nccl all-gather"

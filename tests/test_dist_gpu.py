@@ -45,7 +45,7 @@ def _worker(rank, world, port, M, N, K, out):
             results.append(bool(torch.equal(got, want)))
         ops.check_gemm_status(dev)
         ok = bool(torch.equal(via_nccl, whole)) and all(results)
-        out.put((rank, ok, lin._peer[M].kind))
+        out.put((rank, ok, lin._peer[M][0].kind))
     finally:
         dist.destroy_process_group()
 

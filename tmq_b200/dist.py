@@ -168,7 +168,8 @@ class ColumnShardedLinear:
         self.bias = None if bias is None else bias[n0:n1].contiguous()
         self._matmul = matmul
         self._wt = None
-        self._peer = {}              # rows -> PeerBuffer holding the full [rows, n_total] result on every rank
+        self._peer = {}              # rows -> two alternating PeerBuffers holding the full [rows, n_total] result on every rank
+        self._turn = {}
         self._flag = None
 
     def _out_dtype(self, x):
@@ -190,31 +191,36 @@ class ColumnShardedLinear:
                                 out=None if out is None else out[:, :n])
 
     def prepare_fused(self, rows, device, group=None):
-        """Result buffer of `rows` rows for fused(), mapped between the ranks on first use (a collective call)."""
-        pb = self._peer.get(rows)
-        if pb is None:
-            pb = self._peer[rows] = PeerBuffer((rows, self.n_total), torch.bfloat16, device, group)
+        """The two alternating result buffers of `rows` rows for fused(), mapped between the ranks on first use (a
+        collective call)."""
+        pair = self._peer.get(rows)
+        if pair is None:
+            pair = self._peer[rows] = [PeerBuffer((rows, self.n_total), torch.bfloat16, device, group) for _ in range(2)]
             self._flag = torch.zeros(1, dtype=torch.int32, device=device)
-        return pb
+            self._turn[rows] = 0
+        return pair
 
     def fused(self, x, group=None):
         """Full row-major [M, n_total] bf16 result on every rank with GEMM and all-gather as ONE kernel: the epilogue
         of this rank's GEMM stores its column block into every rank's result buffer (peer mappings, plain stores over
-        NVLink), so the transfer overlaps the multiplication tile by tile and nothing is copied afterwards.  Two tiny
-        all-reduces order the ranks: before the launch (nobody still reads the previous result) and after it (every
-        block has landed everywhere).  The returned tensor is reused by the next call with the same row count."""
+        NVLink), so the transfer overlaps the multiplication tile by tile and nothing is copied afterwards.  One tiny
+        all-reduce after the launch tells every rank that all blocks have landed.  Results alternate between two
+        buffers: a rank can only start call i + 1 after every rank has passed the all-reduce of call i, i.e. after every
+        rank's stream is done with result i - 1, which is the buffer call i + 1 overwrites.  The returned tensor is
+        therefore valid until the next-but-one call with the same row count."""
         from . import ops
         if self.world == 1:
             return self.local(x)
         if x.dtype != torch.bfloat16:
             raise RuntimeError("ColumnShardedLinear.fused: bf16 activations only")
         m = x.shape[0]
-        pb = self.prepare_fused(m, x.device, group)
+        pair = self.prepare_fused(m, x.device, group)
+        pb = pair[self._turn[m]]
+        self._turn[m] ^= 1                      # per row count: each pair alternates on its own
         if self._wt is None:
             self._wt = ops.prepack(self.packed_shard, self.n1 - self.n0, ops.FMT_BF16)
         order = [self.rank] + [r for r in range(self.world) if r != self.rank]
         dsts = [pb.ptrs[r] + self.n0 * 2 for r in order]
-        dist.all_reduce(self._flag, group=group)
         ops.ternary_gemm_bcast(x, self._wt, self.n1 - self.n0, dsts, self.n_total, self.scale, self.bias)
         dist.all_reduce(self._flag, group=group)
         return pb.tensor
