@@ -106,41 +106,21 @@ class FlatGradBucket:
 
 class PeerBuffer:
     """One CUDA tensor of the same shape on every rank of a single node, each mapped into every other rank's address
-    space, so that a kernel on one GPU can store straight into the others' copies over NVLink.  `ptrs[r]` is the device
-    address of rank r's tensor as seen from THIS process.  Uses torch's symmetric memory when it is available and
-    CUDA IPC handles exchanged over the process group otherwise (`kind` says which)."""
+    space (torch symmetric memory), so that a kernel on one GPU can store straight into the others' copies over NVLink.
+    `ptrs[r]` is the device address of rank r's tensor as seen from THIS process.  Raises when symmetric memory is not
+    available; callers then keep to the NCCL route.  There is deliberately no second mapping route: handles exported
+    through torch's CUDA IPC storage sharing are opened in the exporting device's context, and a kernel running on
+    another device faulted on such a pointer."""
 
     def __init__(self, shape, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm
         self.rank, self.world = world()
-        self.kind = None
-        self._keep = []
-        try:
-            import torch.distributed._symmetric_memory as symm
-            t = symm.empty(tuple(shape), dtype=dtype, device=device)
-            hdl = symm.rendezvous(t, dist.group.WORLD if group is None else group)
-            self.tensor = t
-            self.ptrs = [int(p) for p in hdl.buffer_ptrs]
-            self._keep.append(hdl)
-            self.kind = "symmetric_memory"
-        except Exception as err:                     # noqa: BLE001 - any failure of the optional route falls back
-            self._ipc(shape, dtype, device, group, err)
-
-    def _ipc(self, shape, dtype, device, group, why):
-        # the handle names the allocator block that holds the tensor; the offset inside it travels with it
-        self.tensor = torch.empty(tuple(shape), dtype=dtype, device=device)
-        storage = self.tensor.untyped_storage()
-        mine = (storage._share_cuda_(), self.tensor.storage_offset() * self.tensor.element_size())
-        everyone = [None] * self.world
-        dist.all_gather_object(everyone, mine, group=group)
-        self.ptrs = []
-        for r, (handle, offset) in enumerate(everyone):
-            if r == self.rank:
-                self.ptrs.append(self.tensor.data_ptr())
-            else:
-                opened = torch.UntypedStorage._new_shared_cuda(*handle)
-                self._keep.append(opened)
-                self.ptrs.append(opened.data_ptr() + offset)
-        self.kind = f"cuda_ipc (symmetric memory unavailable: {type(why).__name__})"
+        self.tensor = symm.empty(tuple(shape), dtype=dtype, device=device)
+        self._handle = symm.rendezvous(self.tensor, dist.group.WORLD if group is None else group)
+        self.ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        if len(self.ptrs) != self.world or self.ptrs[self.rank] != self.tensor.data_ptr():
+            raise RuntimeError("PeerBuffer: symmetric memory returned an unexpected mapping")
+        self.kind = "symmetric_memory"
 
 
 class ColumnShardedLinear:
