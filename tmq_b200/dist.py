@@ -9,7 +9,8 @@ The reference is single-device; these are the three partitionings its workloads 
   * element / batch sharding with no data-path collective: `shard_range` (soft-step over a flat tensor, inference
     over a batch); the soft-step loss scalar needs one scalar all-reduce.
 
-Nothing here launches kernels of its own; the collectives are torch.distributed's (NCCL on GPUs, gloo in CPU tests).
+The collectives are torch.distributed's (NCCL on GPUs, gloo in CPU tests); the one fused step is the column-sharded
+linear's GEMM, whose epilogue stores its block into every rank's result buffer (ColumnShardedLinear.fused).
 """
 import torch
 import torch.distributed as dist
