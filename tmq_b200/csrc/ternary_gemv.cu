@@ -462,6 +462,10 @@ struct ResMma {
     // the activations are zero beyond K, every decoded code is finite (0, +-2), and the words a lane reads past the
     // valid part of its row (at most 12: the row padding, the next row, or the slack the launcher leaves behind the
     // last row) therefore contribute exact zeros.
+    // FULL: every CTA's shared-memory area holds kResGroups groups (the launcher's per-CTA maximum), so the group loop
+    // runs without its predicate; a CTA that owns fewer groups multiplies rows nobody loaded - any bits decode to finite
+    // values - and never stores those sums.  The slowest CTA owns kResGroups groups anyway.
+    template <bool FULL>
     static __device__ __forceinline__ void slices(const uint32_t *wsm, const void *X, long long M, long long K,
                                                   long long KS, int G, int warp, int g, int t, uint32_t (&xr)[XR],
                                                   Acc (&acc)[kResGroups][4]) {
@@ -473,7 +477,7 @@ struct ResMma {
             if (slice != warp) load_x(X, M, K, slice, g, t, xr);
 #pragma unroll
             for (int i = 0; i < kResGroups; i++) {
-                if (i < G) {                            // warp-uniform: every lane takes part in the mma below
+                if (FULL || i < G) {                            // warp-uniform: every lane takes part in the mma below
                     const uint32_t p0 = addr + (uint32_t)i * (2u * hi_off), p1 = p0 + hi_off;
                     uint32_t lo[LW], hi[LW];
                     if (KIND == 0) {
@@ -535,7 +539,7 @@ struct ResMma {
     }
 };
 
-template <int KIND, int WARPS>
+template <int KIND, int WARPS, bool FULL>
 __global__ void __launch_bounds__(WARPS * 32, 2) ternary_gemv_resident_kernel(const ResArgs a) {
     using R = ResMma<KIND, WARPS>;
     using Acc = typename R::Acc;
@@ -574,7 +578,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) ternary_gemv_resident_kernel(co
     uint32_t xr[R::XR];
     R::load_x(a.X, a.M, a.K, warp, g, t, xr);      // in flight while the last packed rows land
     const bool ok = __syncthreads_and(ptx::mbar_wait(bar, 0, a.status));
-    if (ok) R::slices(wsm, a.X, a.M, a.K, a.KS, G, warp, g, t, xr, acc);
+    if (ok) R::template slices<FULL>(wsm, a.X, a.M, a.K, a.KS, G, warp, g, t, xr, acc);
     __syncthreads();   // every warp is done reading the packed rows: the area becomes the reduction buffer
     if (!ok) return;   // uniform: the copies never completed and the status word says so
     Acc *red = reinterpret_cast<Acc *>(wsm);  // [warp][group][16][8]
@@ -622,6 +626,7 @@ struct ResDp4a {
 
     // all slices of this warp (`xr` holds slice `warp` on entry), then the sum over the four t lanes of a channel;
     // no K tail handling, for the reasons given at ResMma::slices
+    template <bool FULL>
     static __device__ __forceinline__ void slices(const uint32_t *wsm, const void *X, long long M, long long K,
                                                   long long KS, int G, int warp, int g, int t, uint32_t (&xr)[MR][16],
                                                   int (&acc)[RL][MR]) {
@@ -632,7 +637,7 @@ struct ResDp4a {
             if (slice != warp) load_x(X, M, K, slice, t, xr);
 #pragma unroll
             for (int i = 0; i < RL; i++) {
-                if (i < 2 * G) {
+                if (FULL || i < 2 * G) {
                     uint32_t words[4];
                     lds_v4(addr + (uint32_t)i * row8, words[0], words[1], words[2], words[3]);
 #pragma unroll
@@ -678,7 +683,7 @@ struct ResDp4a {
     }
 };
 
-template <int MR, int WARPS>
+template <int MR, int WARPS, bool FULL>
 __global__ void __launch_bounds__(WARPS * 32, 2) ternary_gemv_resident_dp4a_kernel(const ResArgs a) {
     using R = ResDp4a<MR, WARPS>;
     extern __shared__ __align__(16) uint32_t wsm[];
@@ -700,7 +705,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) ternary_gemv_resident_dp4a_kern
     uint32_t xr[MR][16];
     R::load_x(a.X, a.M, a.K, warp, t, xr);
     const bool ok = __syncthreads_and(ptx::mbar_wait(bar, 0, a.status));
-    if (ok) R::slices(wsm, a.X, a.M, a.K, a.KS, G, warp, g, t, xr, acc);
+    if (ok) R::template slices<FULL>(wsm, a.X, a.M, a.K, a.KS, G, warp, g, t, xr, acc);
     __syncthreads();   // every warp is done reading the packed rows: the area becomes the reduction buffer
     if (!ok) return;
     int *red = reinterpret_cast<int *>(wsm);
@@ -897,7 +902,7 @@ __device__ __forceinline__ void batch_fetch(const BatchArgs &a, const BatchCta &
     ptx::bulk_load(wsm, a.Wt[j] + (long long)c.group0 * 16 * a.KS, c.bytes, bar);
 }
 
-template <int KIND, int WARPS>
+template <int KIND, int WARPS, bool FULL>
 __global__ void __launch_bounds__(WARPS * 32, 2) ternary_gemv_batched_kernel(const __grid_constant__ BatchArgs a) {
     using R = ResMma<KIND, WARPS>;
     using Acc = typename R::Acc;
@@ -942,7 +947,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) ternary_gemv_batched_kernel(con
         uint32_t xr[R::XR];
         R::load_x(X, a.M, a.K, warp, g, t, xr);
         if (!__syncthreads_and(ptx::mbar_wait(bar, phase, a.status))) return;   // uniform; the status word says why
-        R::slices(wsm, X, a.M, a.K, a.KS, c.G, warp, g, t, xr, acc);
+        R::template slices<FULL>(wsm, X, a.M, a.K, a.KS, c.G, warp, g, t, xr, acc);
         __syncthreads();                                   // every warp is done with the rows of matrix j
         const bool more = j + c.step < a.nmat;
         if (!a.red_alias && more && threadIdx.x == 0) batch_fetch(a, c, wsm, bar, j + c.step);
@@ -974,7 +979,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) ternary_gemv_batched_kernel(con
     }
 }
 
-template <int MR, int WARPS>
+template <int MR, int WARPS, bool FULL>
 __global__ void __launch_bounds__(WARPS * 32, 2) ternary_gemv_batched_dp4a_kernel(const __grid_constant__ BatchArgs a) {
     using R = ResDp4a<MR, WARPS>;
     extern __shared__ __align__(16) uint32_t wsm[];
@@ -1003,7 +1008,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) ternary_gemv_batched_dp4a_kerne
         uint32_t xr[MR][16];
         R::load_x(X, a.M, a.K, warp, t, xr);
         if (!__syncthreads_and(ptx::mbar_wait(bar, phase, a.status))) return;
-        R::slices(wsm, X, a.M, a.K, a.KS, c.G, warp, g, t, xr, acc);
+        R::template slices<FULL>(wsm, X, a.M, a.K, a.KS, c.G, warp, g, t, xr, acc);
         __syncthreads();
         const bool more = j + c.step < a.nmat;
         if (!a.red_alias && more && threadIdx.x == 0) batch_fetch(a, c, wsm, bar, j + c.step);
@@ -1066,9 +1071,14 @@ static int launch_gemv_batched(BatchArgs a, cudaStream_t st) {
     a.ngroups = (int)ngroups;
     a.nslots = (int)nslots;
     const unsigned grid = (unsigned)(nslots * (a.nmat > 1 ? 2 : 1));
-    if (dp4a && a.M == 1) return launch_resident_form(ternary_gemv_batched_dp4a_kernel<1, W>, a, grid, W, smem, st);
-    if (dp4a) return launch_resident_form(ternary_gemv_batched_dp4a_kernel<2, W>, a, grid, W, smem, st);
-    return launch_resident_form(ternary_gemv_batched_kernel<KIND, W>, a, grid, W, smem, st);
+    if (G == kResGroups) {         // every CTA's area holds the full five groups: the unpredicated group loop
+        if (dp4a && a.M == 1) return launch_resident_form(ternary_gemv_batched_dp4a_kernel<1, W, true>, a, grid, W, smem, st);
+        if (dp4a) return launch_resident_form(ternary_gemv_batched_dp4a_kernel<2, W, true>, a, grid, W, smem, st);
+        return launch_resident_form(ternary_gemv_batched_kernel<KIND, W, true>, a, grid, W, smem, st);
+    }
+    if (dp4a && a.M == 1) return launch_resident_form(ternary_gemv_batched_dp4a_kernel<1, W, false>, a, grid, W, smem, st);
+    if (dp4a) return launch_resident_form(ternary_gemv_batched_dp4a_kernel<2, W, false>, a, grid, W, smem, st);
+    return launch_resident_form(ternary_gemv_batched_kernel<KIND, W, false>, a, grid, W, smem, st);
 }
 
 // Returns TMQ_ERR_UNSUPPORTED when the CTA's rows do not fit the shared-memory budget (the caller then streams).
@@ -1092,12 +1102,20 @@ static int launch_gemv_resident(ResArgs a, cudaStream_t st) {
     a.ngroups = (int)ngroups;
     const unsigned g = (unsigned)grid;
     if (rows16) return launch_resident_form(ternary_gemv_resident_rows_kernel<KIND, 2>, a, g, warps, smem, st);
+    if (G == kResGroups) {         // every CTA's area holds the full five groups: the unpredicated group loop
+        if (KIND == 1 && a.M == 1)
+            return launch_resident_form(ternary_gemv_resident_dp4a_kernel<1, kResWarpsMany, true>, a, g, warps, smem, st);
+        if (KIND == 1 && a.M == 2)
+            return launch_resident_form(ternary_gemv_resident_dp4a_kernel<2, kResWarpsFew, true>, a, g, warps, smem, st);
+        if (KIND == 1) return launch_resident_form(ternary_gemv_resident_kernel<1, kResWarpsFew, true>, a, g, warps, smem, st);
+        return launch_resident_form(ternary_gemv_resident_kernel<0, kResWarpsMany, true>, a, g, warps, smem, st);
+    }
     if (KIND == 1 && a.M == 1)
-        return launch_resident_form(ternary_gemv_resident_dp4a_kernel<1, kResWarpsMany>, a, g, warps, smem, st);
+        return launch_resident_form(ternary_gemv_resident_dp4a_kernel<1, kResWarpsMany, false>, a, g, warps, smem, st);
     if (KIND == 1 && a.M == 2)
-        return launch_resident_form(ternary_gemv_resident_dp4a_kernel<2, kResWarpsFew>, a, g, warps, smem, st);
-    if (KIND == 1) return launch_resident_form(ternary_gemv_resident_kernel<1, kResWarpsFew>, a, g, warps, smem, st);
-    return launch_resident_form(ternary_gemv_resident_kernel<0, kResWarpsMany>, a, g, warps, smem, st);
+        return launch_resident_form(ternary_gemv_resident_dp4a_kernel<2, kResWarpsFew, false>, a, g, warps, smem, st);
+    if (KIND == 1) return launch_resident_form(ternary_gemv_resident_kernel<1, kResWarpsFew, false>, a, g, warps, smem, st);
+    return launch_resident_form(ternary_gemv_resident_kernel<0, kResWarpsMany, false>, a, g, warps, smem, st);
 }
 
 static int check_gemv(const void *X, const uint32_t *Wt, const void *Y, long long M, long long N, long long K,
