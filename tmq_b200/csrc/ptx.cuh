@@ -66,7 +66,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *s
     }
 }
 
-// The same wait made by a whole converged warp, with a warp-uniform verdict (one lane giving up makes every lane give up),
+// The same wait made by a whole converged warp, with a warp-uniform result (one lane giving up makes every lane give up),
 // so that code after it can stay convergent (elect_one needs the full warp).
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, int *status,
                                                long long budget = kWaitBudgetCycles) {
