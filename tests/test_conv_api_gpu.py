@@ -364,3 +364,18 @@ def test_second_device_gets_its_own_kernel_attributes(ops):
         refc = nn.functional.conv2d(xc.double(), wc.double(), None, 1, 1)
         assert float((yc.permute(0, 3, 1, 2).double().cpu() - refc).abs().max()) <= 1e-5 * float(refc.abs().max())
         ops.check_gemm_status(dev)
+
+
+def test_graphed_inference_replays_the_pass(tmq, ops):
+    """The packed ResNet-18 pass captured into a CUDA graph gives the bits of the launch-by-launch pass, also for a
+    second input of the same shape."""
+    from tmq_b200 import workloads
+    _, net, _ = _packed_resnet(tmq, 21)
+    x1 = torch.randn(4, 3, 64, 64, device="cuda")
+    x2 = torch.randn(4, 3, 64, 64, device="cuda")
+    g = workloads.GraphedInference(net, x1)
+    assert torch.equal(g(x1).clone(), net(x1))
+    assert torch.equal(g(x2).clone(), net(x2))
+    ops.check_gemm_status()
+    with pytest.raises(RuntimeError):
+        g(torch.randn(2, 3, 64, 64, device="cuda"))
