@@ -347,6 +347,18 @@ int tmq_ternary_conv2d_stem_rows_pool_bf16(const float *X, const uint32_t *Wt, c
 int tmq_maxpool2d_nhwc_bf16(const void *X, void *Y, int B, int H, int W, int C, int k, int s, int p, int relu,
                             void *stream);
 
+/* Max pooling for training on fp32 NHWC activations [B][H][W][C], C % 4 == 0, square window k <= 11, stride s, padding p
+ * (2p <= k), torch's max_pool2d output geometry and winner rule (first maximum in scan order; a NaN wins).  The forward
+ * pass also writes the winning window position of every output element (idx, one signed byte each, shape of Y); the
+ * backward pass gathers: every input element sums the gradients of the windows it won - deterministic, no atomics, no
+ * zero-fill pass.  16-byte aligned X / Y / gX / gY.
+ * replaces: the max_pool2d forward / backward pair between the stem and layer1 of the QAT ResNet step
+ * (samples/resnet_train.py:102-160 runs torch's own). */
+int tmq_maxpool2d_nhwc_f32_fwd(const float *X, float *Y, signed char *idx, int B, int H, int W, int C, int k, int s, int p,
+                               void *stream);
+int tmq_maxpool2d_nhwc_f32_bwd(const float *gY, const signed char *idx, float *gX, int B, int H, int W, int C, int k, int s,
+                               int p, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Depthwise ternary convolutions (groups == channels), fp32, forward and transposed.  W is the reference's packed form
  * of a [C][1][ky][kx] kernel tensor: int32 [ky*kx][ceil(C/16)].  Arithmetic: taps accumulated in (ky, kx) order from +0

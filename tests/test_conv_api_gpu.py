@@ -379,3 +379,28 @@ def test_graphed_inference_replays_the_pass(tmq, ops):
     ops.check_gemm_status()
     with pytest.raises(RuntimeError):
         g(torch.randn(2, 3, 64, 64, device="cuda"))
+
+
+@pytest.mark.parametrize("shape,k,s,p", [((8, 64, 112, 112), 3, 2, 1), ((3, 8, 17, 23), 3, 2, 1), ((2, 4, 9, 9), 2, 2, 0),
+                                         ((2, 12, 10, 14), 3, 1, 1), ((1, 4, 5, 5), 5, 3, 2)])
+def test_training_maxpool_matches_torch(ops, shape, k, s, p):
+    """Forward values and winners, and the gathered backward, against torch's max_pool2d on the same channels-last
+    fp32 tensor: inputs with many exact ties (a ReLU's zeros) and a NaN."""
+    gen = torch.Generator().manual_seed(sum(shape) + k)
+    x = torch.relu(torch.randn(shape, generator=gen)).cuda()             # about half the values are exactly zero: ties
+    x[0, 0, 0, 0] = float("nan")
+    x = x.contiguous(memory_format=torch.channels_last)
+    xa = x.clone().requires_grad_(True)
+    xb = x.clone().requires_grad_(True)
+    ya = ops.maxpool2d_train(xa, k, s, p)
+    yb = torch.nn.functional.max_pool2d(xb, k, s, p)
+    assert ya.shape == yb.shape
+    assert torch.equal(torch.nan_to_num(ya.detach(), nan=-7.0), torch.nan_to_num(yb.detach(), nan=-7.0))
+    g = torch.randn(ya.shape, generator=gen).cuda().contiguous(memory_format=torch.channels_last)
+    ya.backward(g)
+    yb.backward(g)
+    assert xa.grad.shape == xb.grad.shape
+    assert float((xa.grad - xb.grad).abs().max()) <= 1e-6 * float(xb.grad.abs().max())
+    # anything the kernels do not cover falls back to torch's pooling
+    z = torch.randn(2, 3, 8, 8, device="cuda")                           # 3 channels, not channels-last
+    assert torch.equal(ops.maxpool2d_train(z, 3, 2, 1), torch.nn.functional.max_pool2d(z, 3, 2, 1))

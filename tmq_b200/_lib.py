@@ -51,6 +51,8 @@ _SIGNATURES = {
     "tmq_ternary_conv2d_stem_bf16": (c_int, [c_void_p] * 5 + [c_int] * 13 + [c_void_p, c_void_p]),
     "tmq_maxpool2d_nhwc_bf16": (c_int, [c_void_p, c_void_p] + [c_int] * 8 + [c_void_p]),
     "tmq_ternary_dwconv2d_f32": (c_int, [c_void_p] * 5 + [c_int] * 12 + [c_void_p]),
+    "tmq_maxpool2d_nhwc_f32_fwd": (c_int, [c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p]),
+    "tmq_maxpool2d_nhwc_f32_bwd": (c_int, [c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p]),
     "tmq_ternary_dwconvtrans2d_f32": (c_int, [c_void_p] * 5 + [c_int] * 14 + [c_void_p]),
     "tmq_ternary_dwconv_patches_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "tmq_ternary_dwconvtrans_patches_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),

@@ -100,6 +100,73 @@ __global__ void __launch_bounds__(128) avgpool_nhwc_kernel(const __nv_bfloat162 
 
 using namespace tmq;
 
+// Max pooling for TRAINING on fp32 NHWC activations (the pooling behind the stem of a ResNet under quantisation-aware
+// training): the forward pass also records, per output element, which window position won (first maximum in (ky, kx)
+// scan order, NaN wins: torch's rule), and the backward pass GATHERS - every input element adds the gradients of the
+// windows it won - so it needs neither atomics nor a zero-fill pass and is deterministic.  Four channels per thread.
+__global__ void __launch_bounds__(256) maxpool_f32_fwd_kernel(const float4 *__restrict__ X, float4 *__restrict__ Y,
+                                                              char4 *__restrict__ idx, int B, int H, int W, int C4, int OH,
+                                                              int OW, int k, int s, int p) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)B * OH * OW * C4) return;
+    const int c = (int)(i % C4);
+    long long r = i / C4;
+    const int ox = (int)(r % OW); r /= OW;
+    const int oy = (int)(r % OH);
+    const int b = (int)(r / OH);
+    float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    int w[4] = {-1, -1, -1, -1};
+    for (int fy = 0; fy < k; fy++) {
+        const int y = oy * s - p + fy;
+        if (y < 0 || y >= H) continue;
+        for (int fx = 0; fx < k; fx++) {
+            const int x = ox * s - p + fx;
+            if (x < 0 || x >= W) continue;
+            const float4 v = X[(((long long)b * H + y) * W + x) * C4 + c];
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+                if (w[q] < 0 || e[q] > m[q] || e[q] != e[q]) {     // first element of the window, a larger one, or a NaN
+                    m[q] = e[q];
+                    w[q] = fy * k + fx;
+                }
+        }
+    }
+    Y[i] = make_float4(m[0], m[1], m[2], m[3]);
+    idx[i] = make_char4((signed char)w[0], (signed char)w[1], (signed char)w[2], (signed char)w[3]);
+}
+
+__global__ void __launch_bounds__(256) maxpool_f32_bwd_kernel(const float4 *__restrict__ gY, const char4 *__restrict__ idx,
+                                                              float4 *__restrict__ gX, int B, int H, int W, int C4, int OH,
+                                                              int OW, int k, int s, int p) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)B * H * W * C4) return;
+    const int c = (int)(i % C4);
+    long long r = i / C4;
+    const int x = (int)(r % W); r /= W;
+    const int y = (int)(r % H);
+    const int b = (int)(r / H);
+    float g[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // windows that contain (y, x): oy * s - p <= y < oy * s - p + k
+    int oy0 = y + p - k + 1;
+    oy0 = oy0 <= 0 ? 0 : (oy0 + s - 1) / s;
+    int ox0 = x + p - k + 1;
+    ox0 = ox0 <= 0 ? 0 : (ox0 + s - 1) / s;
+    const int oy1 = min((y + p) / s, OH - 1), ox1 = min((x + p) / s, OW - 1);
+    for (int oy = oy0; oy <= oy1; oy++)
+        for (int ox = ox0; ox <= ox1; ox++) {
+            const int off = (y - (oy * s - p)) * k + (x - (ox * s - p));
+            const long long o = (((long long)b * OH + oy) * OW + ox) * C4 + c;
+            const char4 w = idx[o];
+            const float4 v = gY[o];
+            if (w.x == off) g[0] += v.x;
+            if (w.y == off) g[1] += v.y;
+            if (w.z == off) g[2] += v.z;
+            if (w.w == off) g[3] += v.w;
+        }
+    gX[i] = make_float4(g[0], g[1], g[2], g[3]);
+}
+
 extern "C" int tmq_split_f32_bf16(const float *X, void *out, int64_t M, int64_t K, int64_t Kp, int terms, void *stream) {
     if (!X || !out || M <= 0 || K <= 0 || Kp < K || (terms != 1 && terms != 3)) return TMQ_ERR_ARG;
     if (!aligned(X, 4) || !aligned(out, 2)) return TMQ_ERR_ALIGN;
@@ -129,5 +196,40 @@ extern "C" int tmq_avgpool_nhwc_bf16(const void *X, void *Y, int B, int P, int C
     if (total > 0x7FFFFFFF) return TMQ_ERR_UNSUPPORTED;
     avgpool_nhwc_kernel<<<(unsigned)((total + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<const __nv_bfloat162 *>(X), reinterpret_cast<__nv_bfloat162 *>(Y), B, P, C / 2);
+    return launch_status();
+}
+
+static int maxpool_train_check(const void *a, const void *b, const void *c, int B, int H, int W, int C, int k, int s, int p) {
+    if (!a || !b || !c) return TMQ_ERR_ARG;
+    if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || k <= 0 || s <= 0 || p < 0) return TMQ_ERR_ARG;
+    if (C % 4 != 0 || k > 11 || 2 * p > k) return TMQ_ERR_UNSUPPORTED;        // window positions fit a signed byte
+    if (H + 2 * p < k || W + 2 * p < k) return TMQ_ERR_ARG;
+    if (!aligned(a, 16) || !aligned(b, 16) || !aligned(c, 4)) return TMQ_ERR_ALIGN;
+    return TMQ_OK;
+}
+
+extern "C" int tmq_maxpool2d_nhwc_f32_fwd(const float *X, float *Y, signed char *idx, int B, int H, int W, int C, int k, int s,
+                                          int p, void *stream) {
+    int rc = maxpool_train_check(X, Y, idx, B, H, W, C, k, s, p);
+    if (rc != TMQ_OK) return rc;
+    const int OH = (H + 2 * p - k) / s + 1, OW = (W + 2 * p - k) / s + 1;
+    const long long total = (long long)B * OH * OW * (C / 4);
+    if ((total + 255) / 256 > 0x7FFFFFFFll) return TMQ_ERR_UNSUPPORTED;
+    maxpool_f32_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const float4 *>(X), reinterpret_cast<float4 *>(Y), reinterpret_cast<char4 *>(idx), B, H, W, C / 4, OH, OW,
+        k, s, p);
+    return launch_status();
+}
+
+extern "C" int tmq_maxpool2d_nhwc_f32_bwd(const float *gY, const signed char *idx, float *gX, int B, int H, int W, int C, int k,
+                                          int s, int p, void *stream) {
+    int rc = maxpool_train_check(gY, gX, idx, B, H, W, C, k, s, p);
+    if (rc != TMQ_OK) return rc;
+    const int OH = (H + 2 * p - k) / s + 1, OW = (W + 2 * p - k) / s + 1;
+    const long long total = (long long)B * H * W * (C / 4);
+    if ((total + 255) / 256 > 0x7FFFFFFFll) return TMQ_ERR_UNSUPPORTED;
+    maxpool_f32_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const float4 *>(gY), reinterpret_cast<const char4 *>(idx), reinterpret_cast<float4 *>(gX), B, H, W, C / 4,
+        OH, OW, k, s, p);
     return launch_status();
 }

@@ -1048,6 +1048,47 @@ def maxpool2d_nhwc(x, kernel, stride, padding, relu=False):
     return y
 
 
+class MaxPool2dTrain(torch.autograd.Function):
+    """max_pool2d (square window, no dilation, floor mode) for fp32 CUDA activations in channels-last layout, forward and
+    backward as two streaming kernels (the backward gathers: deterministic, no atomics).  Same values, winners and
+    gradients as torch's."""
+
+    @staticmethod
+    def forward(ctx, x, k, s, p):
+        b, c, h, w = x.shape
+        xn = x.permute(0, 2, 3, 1)                                   # NHWC view of the channels-last tensor
+        oh, ow = (h + 2 * p - k) // s + 1, (w + 2 * p - k) // s + 1
+        y = torch.empty((b, c, oh, ow), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
+        idx = torch.empty((b, oh, ow, c), dtype=torch.int8, device=x.device)
+        with torch.cuda.device(x.device):
+            check(lib().tmq_maxpool2d_nhwc_f32_fwd(_ptr(xn), _ptr(y), _ptr(idx), b, h, w, c, k, s, p, _stream(x)),
+                  "maxpool2d_train")
+        ctx.save_for_backward(idx)
+        ctx.geom = (b, c, h, w, k, s, p)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        (idx,) = ctx.saved_tensors
+        b, c, h, w, k, s, p = ctx.geom
+        gy = gy.contiguous(memory_format=torch.channels_last)
+        gx = torch.empty((b, c, h, w), dtype=torch.float32, device=gy.device, memory_format=torch.channels_last)
+        with torch.cuda.device(gy.device):
+            check(lib().tmq_maxpool2d_nhwc_f32_bwd(_ptr(gy), _ptr(idx), _ptr(gx), b, h, w, c, k, s, p, _stream(gy)),
+                  "maxpool2d_train")
+        return gx, None, None, None
+
+
+def maxpool2d_train(x, kernel, stride, padding):
+    """Training max pooling: the library's kernels for fp32 CUDA tensors in channels-last layout with C % 4 == 0, torch's
+    own max_pool2d for anything else."""
+    k, s, p = int(kernel), int(stride), int(padding)
+    if (x.dim() == 4 and x.is_cuda and x.dtype == torch.float32 and x.shape[1] % 4 == 0 and k <= 11 and 2 * p <= k
+            and x.is_contiguous(memory_format=torch.channels_last) and x.shape[2] + 2 * p >= k and x.shape[3] + 2 * p >= k):
+        return MaxPool2dTrain.apply(x, k, s, p)
+    return torch.nn.functional.max_pool2d(x, k, s, p)
+
+
 # ---- depthwise convolutions ------------------------------------------------------------------------------------------
 
 def _dw_args(name, x, weights):

@@ -16,6 +16,18 @@ from . import ops
 from . import tmq as api
 
 
+class TrainMaxPool(nn.Module):
+    """nn.MaxPool2d(kernel, stride, padding) whose forward / backward run the library's streaming kernels on fp32
+    channels-last CUDA activations (torch's own otherwise)."""
+
+    def __init__(self, kernel_size, stride, padding):
+        super().__init__()
+        self.kernel_size, self.stride, self.padding = kernel_size, stride, padding
+
+    def forward(self, x):
+        return ops.maxpool2d_train(x, self.kernel_size, self.stride, self.padding)
+
+
 def build_resnet18(num_classes=101, ctrl=None, max_epochs=50, qpenalty_range=(0.0, 1e-3)):
     import torchvision
     model = torchvision.models.resnet18(num_classes=num_classes)
@@ -23,6 +35,7 @@ def build_resnet18(num_classes=101, ctrl=None, max_epochs=50, qpenalty_range=(0.
         ctrl = api.QuantizationControl(epoch_knots=api.QuantizationScheduleBuilder.default_schedule(max_epochs),
                                        qpenalty_range=qpenalty_range)
     api.quantize_model(model, ctrl)
+    model.maxpool = TrainMaxPool(3, 2, 1)        # same layer, faster kernels when the activations are channels-last
     model.fc.disable_bias()
     model.fc.implicit_bn()
     return model, ctrl
